@@ -1,0 +1,197 @@
+/*
+ * turboloader_b200 -- C ABI of the B200 (sm_100a) fused image-transform path.
+ *
+ * One fused operation replaces TurboLoader's GPU transform entry points:
+ *
+ *   per-sample crop box -> horizontal flip -> bilinear resize (half-pixel centres,
+ *   result truncated to an 8-bit code as the CPU path does) -> per-channel
+ *   mean/std normalize -> HWC->NCHW (or NHWC) -> fp32 or bf16,
+ *   optionally gathering the source image through a device index array.
+ *
+ * Every function is plain C: raw pointers, sizes, int status codes.  No torch
+ * or pybind types cross this boundary.  Work is enqueued on the caller's
+ * stream and the call returns without synchronising unless stated otherwise.
+ * Citations name the TurboLoader interface each entry point stands in for
+ * (paths inside the TurboLoader tree).
+ */
+#ifndef TURBOLOADER_B200_H
+#define TURBOLOADER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TLB_API __attribute__((visibility("default")))
+
+/* ---- status codes (0 = ok) -------------------------------------------------------- */
+enum {
+    TLB_OK = 0,
+    TLB_ERR_INVALID_ARG = 1,   /* null pointer, non-positive size, unknown enum           */
+    TLB_ERR_BAD_BOX = 2,       /* a crop box leaves its image (host-validated calls)       */
+    TLB_ERR_BAD_INDEX = 3,     /* a gather index is outside [0, n_src)                     */
+    TLB_ERR_TOO_WIDE = 4,      /* crop wider than the staging capacity (see max_crop_w)    */
+    TLB_ERR_CUDA = 5,          /* a CUDA runtime call failed; see tlb_last_error()         */
+    TLB_ERR_NO_DEVICE = 6,     /* no CUDA device / not an sm_100 device                    */
+    TLB_ERR_TOO_LARGE = 7,     /* size beyond a fixed capacity (allocation-free entry)     */
+};
+
+/* Bits of the optional device status word written by the kernel (never traps). */
+enum {
+    TLB_DEV_BAD_INDEX = 1u,    /* sample skipped (output zero-filled): gather index invalid */
+    TLB_DEV_BAD_BOX = 2u,      /* sample skipped (output zero-filled): box leaves the image */
+    TLB_DEV_TOO_WIDE = 4u,     /* sample skipped (output zero-filled): crop exceeds staging */
+    TLB_DEV_COPY_TIMEOUT = 8u, /* a bounded wait on an async copy gave up                   */
+};
+
+enum { TLB_F32 = 0, TLB_BF16 = 1 };
+enum { TLB_NCHW = 0, TLB_NHWC = 1 };
+
+/*
+ * Descriptor of one fused batch.  All pointers are DEVICE pointers unless the
+ * field says otherwise.  "Dataset image" = an image stored in `src`; "sample"
+ * = one output slot of this batch.  Sample k reads dataset image
+ * s = sel ? sel[k] : k.
+ */
+typedef struct tlb_transform_desc {
+    /* -- source pixels: uint8, HWC, RGB, tightly packed rows ------------------------ */
+    const uint8_t* src;        /* base of the readable region                              */
+    uint64_t src_bytes;        /* readable bytes at src (no load ever leaves this range)   */
+    int64_t n_src;             /* number of dataset images described below                 */
+    const int64_t* src_offsets;/* [n_src] byte offset of each image, or NULL: uniform      */
+                               /*   layout, image s at s * src_h * src_w * 3               */
+    const int32_t* src_sizes;  /* [n_src][2] (w, h) per image, or NULL: all src_w x src_h  */
+    int32_t src_w, src_h;      /* uniform size (used when src_sizes == NULL)               */
+
+    /* -- per-sample parameters ------------------------------------------------------- */
+    int32_t n;                 /* samples in this batch                                    */
+    const int64_t* sel;        /* [n] gather indices into the dataset, or NULL             */
+    const int32_t* boxes;      /* [n][4] crop (x, y, w, h) in source pixels, or NULL       */
+    int32_t uniform_box[4];    /* used when boxes == NULL; w == 0 means the whole image    */
+    const uint8_t* flips;      /* [n] non-zero = mirror the RESIZED image, or NULL         */
+
+    /* -- output ---------------------------------------------------------------------- */
+    int32_t dst_h, dst_w;
+    void* out;                 /* n*3*dst_h*dst_w elements                                 */
+    int32_t out_dtype;         /* TLB_F32 | TLB_BF16 (bf16 = RNE of the fp32 result)       */
+    int32_t out_layout;        /* TLB_NCHW | TLB_NHWC                                      */
+    int64_t* out_indices;      /* [n] receives s for every sample (bit-exact), or NULL     */
+    const int64_t* labels_in;  /* [n_src] per-dataset-image labels, or NULL                */
+    int64_t* labels_out;       /* [n] receives labels_in[s], or NULL                       */
+
+    /* -- normalization: (u8 * (normalize_01 ? 1/255 : 1) - mean[c]) * (1.0f / std[c]) -- */
+    float mean[3];
+    float std[3];
+    int32_t normalize_01;
+
+    /* -- capacity hint ---------------------------------------------------------------- */
+    int32_t max_crop_w;        /* upper bound of any crop width in this batch; 0 = derive  */
+                               /*   (uniform box width, else src_w, which must then be set */
+                               /*   to the widest image)                                   */
+    uint32_t* status;          /* device word OR-ed with TLB_DEV_* bits, or NULL           */
+} tlb_transform_desc;
+
+/* ---- capability ----------------------------------------------------------------------
+ * Replace turboloader::cuda::available / device_name
+ * (src/cuda/cuda_transforms.hpp:19-22, src/cuda/cuda_transforms.cu:270-286). */
+TLB_API int tlb_available(void);
+TLB_API int tlb_device_name(int device, char* buf, size_t cap);
+TLB_API const char* tlb_version(void);
+/* Message of the last failing call on this thread ("" when none). */
+TLB_API const char* tlb_last_error(void);
+
+/* ---- the fused operation ---------------------------------------------------------------
+ * Replaces the kernels and launch loops behind
+ *   turboloader::cuda::resize_normalize_batch          (cuda_transforms.hpp:41-42,  .cu:288-314)
+ *   turboloader::cuda::crop_resize_normalize_batch     (cuda_transforms.hpp:117-119, .cu:316-347)
+ *   turboloader::cuda::normalize_resident_batch        (cuda_transforms.hpp:49-50,  .cu:475-507)
+ *   turboloader::cuda::normalize_resident_gather_batch (cuda_transforms.hpp:54-55,  .cu:511-544)
+ *   turboloader::cuda::resize_normalize_device_batch   (cuda_transforms.hpp:141-144, .cu:1008-1046)
+ * with ONE launch per batch on `stream` (a cudaStream_t passed as void*; NULL =
+ * the legacy default stream), on the current device, with no synchronisation and
+ * no allocation.  Parameters that live on the device cannot be checked by the
+ * host: the kernel checks them, zero-fills an invalid sample and reports
+ * through desc->status. */
+TLB_API int tlb_fused_transform(const tlb_transform_desc* desc, void* stream);
+
+/* Same operation, with the per-sample tables given as HOST arrays.  Boxes and
+ * indices are validated on the host first (TLB_ERR_BAD_BOX / TLB_ERR_BAD_INDEX,
+ * nothing is launched), then copied to a library-owned device ring on `stream`.
+ * In `desc`, sel / boxes / flips / src_offsets / src_sizes are HOST pointers here;
+ * src, out, out_indices, labels_* and status stay device pointers.  May allocate
+ * (ring growth) on first use. */
+TLB_API int tlb_fused_transform_host_params(const tlb_transform_desc* desc, void* stream);
+
+/* ---- host-image convenience forms (synchronous, like the functions they replace) ----- */
+typedef struct tlb_image_ref {  /* turboloader::cuda::ImageRef, cuda_transforms.hpp:25-29 */
+    const uint8_t* data;        /* HOST pointer, HWC uint8 RGB */
+    int32_t w, h;
+} tlb_image_ref;
+
+typedef struct tlb_crop_params { /* turboloader::cuda::CropParams, cuda_transforms.hpp:32-38 */
+    float x, y, w, h;            /* must be whole numbers: the parity target is the CPU  */
+    int32_t flip;                /* path, whose crop rects are integers                   */
+} tlb_crop_params;
+
+/* resize_normalize_batch (cuda_transforms.hpp:41-42): N host images -> host fp32
+ * NCHW [n,3,dst_h,dst_w]; mean/std in [0,1] units.  Uploads, runs, downloads, syncs. */
+TLB_API int tlb_resize_normalize_batch(const tlb_image_ref* imgs, int32_t n, int32_t dst_h,
+                                       int32_t dst_w, const float mean[3], const float std_[3],
+                                       float* out_host);
+/* crop_resize_normalize_batch (cuda_transforms.hpp:117-119). */
+TLB_API int tlb_crop_resize_normalize_batch(const tlb_image_ref* imgs, const tlb_crop_params* crops,
+                                            int32_t n, int32_t dst_h, int32_t dst_w,
+                                            const float mean[3], const float std_[3], float* out_host);
+
+/* Host images in, DEVICE batch out: packs the crop rows of every image into a pinned
+ * staging ring, uploads them on `stream`, runs the fused kernel into `out_dev`
+ * (dtype/layout as given) and returns without synchronising.  The streaming
+ * counterpart of CudaStreamCore's H2D + kernel slot (cuda_transforms.cu:629-780)
+ * for the crop/resize path. */
+TLB_API int tlb_crop_resize_normalize_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crops,
+                                                int32_t n, int32_t dst_h, int32_t dst_w,
+                                                const float mean[3], const float std_[3],
+                                                int32_t normalize_01, void* out_dev, int32_t out_dtype,
+                                                int32_t out_layout, uint32_t* status_dev, void* stream);
+
+/* ---- resident-dataset forms returning a library-owned device pointer -------------------
+ * normalize_resident_batch / normalize_resident_gather_batch
+ * (cuda_transforms.hpp:49-55): src_dev = [N,H,W,3] uint8 on the device; returns the
+ * device address of an [N,3,H,W] fp32 batch from a 4-deep ring (valid until the
+ * 4th-next call), or 0 on error.  Synchronises its stream before returning, as the
+ * functions it replaces do. */
+TLB_API uintptr_t tlb_normalize_resident_batch(uintptr_t src_dev, int32_t n, int32_t h, int32_t w,
+                                               const float mean[3], const float std_[3]);
+TLB_API uintptr_t tlb_normalize_resident_gather_batch(uintptr_t src_dev, uintptr_t sel_dev, int32_t n,
+                                                      int32_t h, int32_t w, const float mean[3],
+                                                      const float std_[3]);
+
+/* ---- introspection ---------------------------------------------------------------------
+ * Launch geometry the fused kernel would use for `desc` (for tests and the
+ * benchmark's launch/byte accounting).  Any out pointer may be NULL. */
+TLB_API int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block,
+                           int32_t* smem_bytes, int32_t* tile_rows, int32_t* tile_cols);
+/* Number of kernels this library has launched in this process (all entry points). */
+TLB_API uint64_t tlb_launch_count(void);
+
+/* ---- shard index math (host only, no CUDA) ---------------------------------------------
+ * kind 0/1/2 = ContiguousSharding / InterleavedSharding / HashBasedSharding
+ * (src/distributed/sharding_strategies.hpp:150-316).  Returns the shard size (or -1
+ * for world == 0 / rank >= world) and writes min(size, cap) indices. */
+TLB_API int64_t tlb_shard_indices(int32_t kind, int64_t total, int64_t world, int64_t rank,
+                                  int64_t* out, int64_t cap);
+/* DistributedSampler::get_indices (src/distributed/distributed_dataloader.hpp:111-149). */
+TLB_API int64_t tlb_sampler_indices(int64_t total, int32_t world, int32_t rank, int32_t shuffle,
+                                    uint64_t seed, uint64_t epoch, int32_t drop_last, int64_t* out,
+                                    int64_t cap);
+/* DirectBatchCore::build_order (src/pipeline/direct_batch_loader.hpp:116-135). */
+TLB_API int64_t tlb_direct_order(int64_t total, int32_t shuffle, int32_t seed, int32_t epoch,
+                                 int32_t distributed, int32_t rank, int32_t world, int64_t* out,
+                                 int64_t cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURBOLOADER_B200_H */

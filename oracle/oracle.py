@@ -1,0 +1,205 @@
+"""TEST INFRASTRUCTURE ONLY: ctypes front end of the CPU parity oracle.
+
+Two implementations sit behind the same call:
+
+* ``port``  -- ``oracle/libtl_oracle.so``, the plain-C restatement in ``fused_ref.c``
+  (built by ``make -C oracle port``; needs only gcc).
+* ``ref``   -- ``oracle/_ref/libtl_ref_<flavour>.so``, the TurboLoader headers themselves
+  compiled in place from the reference tree (``make -C oracle ref``).  Flavours:
+  ``parity`` (no FMA contraction; what parity is pinned to), ``avx2fma`` and ``avx512``
+  (timed CPU baselines).
+
+Only tests, the smoke check and the benchmark's CPU legs may import this module; the
+package itself never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PORT_SO = os.path.join(HERE, "libtl_oracle.so")
+REF_DIR = os.path.join(HERE, "_ref")
+
+_u8p = C.POINTER(C.c_uint8)
+_i64p = C.POINTER(C.c_int64)
+_i32p = C.POINTER(C.c_int32)
+_f32p = C.POINTER(C.c_float)
+
+_libs: dict[str, C.CDLL] = {}
+
+
+def build_port(force: bool = False) -> str:
+    """Compile the C restatement if it is missing (gcc only, no reference tree needed)."""
+    src = os.path.join(HERE, "fused_ref.c")
+    if force or not os.path.exists(PORT_SO) or os.path.getmtime(PORT_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", HERE, "port"], stdout=subprocess.DEVNULL)
+    return PORT_SO
+
+
+def build_ref(ref_root: str = "/root/reference") -> bool:
+    """Compile the reference headers in place; returns False when the tree is absent."""
+    if not os.path.isdir(os.path.join(ref_root, "src", "transforms")):
+        return False
+    subprocess.check_call(["make", "-C", HERE, "ref", f"REF={ref_root}"], stdout=subprocess.DEVNULL)
+    return True
+
+
+def _cpu_flags() -> set[str]:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    return set(line.split(":", 1)[1].split())
+    except OSError:
+        pass
+    return set()
+
+
+def ref_available(flavour: str = "parity") -> bool:
+    path = os.path.join(REF_DIR, f"libtl_ref_{flavour}.so")
+    if not os.path.exists(path):
+        return False
+    flags = _cpu_flags()
+    need = {"parity": {"avx2"}, "avx2fma": {"avx2", "fma"},
+            "avx512": {"avx2", "fma", "avx512f", "avx512bw", "avx512vl", "avx512dq"}}[flavour]
+    return need <= flags
+
+
+def _load(impl: str) -> C.CDLL:
+    if impl in _libs:
+        return _libs[impl]
+    if impl == "port":
+        lib = C.CDLL(build_port())
+        lib.tlo_fused_batch.restype = C.c_int
+        lib.tlo_fused_batch.argtypes = [_u8p, _i64p, _i32p, C.c_int64, _i64p, _i32p, _u8p, C.c_int,
+                                        C.c_int, C.c_int, _f32p, _f32p, C.c_int, _f32p]
+        lib.tlo_resize_bilinear_u8.restype = None
+        lib.tlo_resize_bilinear_u8.argtypes = [_u8p, _u8p, C.c_int, C.c_int, C.c_int, C.c_int]
+        lib.tlo_f32_to_bf16_array.restype = None
+        lib.tlo_f32_to_bf16_array.argtypes = [_f32p, C.POINTER(C.c_uint16), C.c_size_t]
+        lib.tlo_nchw_to_nhwc.restype = None
+        lib.tlo_nchw_to_nhwc.argtypes = [_f32p, _f32p, C.c_int, C.c_int, C.c_int]
+    else:
+        flavour = impl.split("-", 1)[1] if "-" in impl else "parity"
+        if not ref_available(flavour):
+            raise FileNotFoundError(f"reference harness flavour {flavour!r} is not usable on this host")
+        lib = C.CDLL(os.path.join(REF_DIR, f"libtl_ref_{flavour}.so"))
+        lib.tlref_fused_batch.restype = C.c_int
+        lib.tlref_fused_batch.argtypes = [_u8p, _i64p, _i32p, C.c_int64, _i64p, _i32p, _u8p, C.c_int,
+                                          C.c_int, C.c_int, _f32p, _f32p, C.c_int, _f32p, C.c_int]
+        lib.tlref_resize_bilinear.restype = None
+        lib.tlref_resize_bilinear.argtypes = [_u8p, _u8p, C.c_int, C.c_int, C.c_int, C.c_int]
+        lib.tlref_threads.restype = C.c_int
+        lib.tlref_simd_branch.restype = C.c_char_p
+        lib.tlref_shard_indices.restype = C.c_int64
+        lib.tlref_shard_indices.argtypes = [C.c_int, C.c_int64, C.c_int64, C.c_int64, _i64p, C.c_int64]
+        lib.tlref_sampler_indices.restype = C.c_int64
+        lib.tlref_sampler_indices.argtypes = [C.c_int64, C.c_int, C.c_int, C.c_int, C.c_uint64,
+                                              C.c_uint64, C.c_int, _i64p, C.c_int64]
+        lib.tlref_direct_order.restype = C.c_int64
+        lib.tlref_direct_order.argtypes = [C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                           C.c_int, _i64p, C.c_int64]
+    _libs[impl] = lib
+    return lib
+
+
+def _ptr(a, ty):
+    return a.ctypes.data_as(ty) if a is not None else None
+
+
+def fused_batch(src, offsets, sizes, sel, boxes, flips, dst_h, dst_w, mean, std, normalize_01=True,
+                impl="port", threads=1, out=None):
+    """fp32 NCHW result of crop -> bilinear(u8, truncating) -> flip -> normalize.
+
+    ``src`` packed uint8, ``offsets`` int64[n_src], ``sizes`` int32[n_src,2] as (w,h),
+    ``sel`` int64[n] or None, ``boxes`` int32[n,4] (x,y,w,h) or None, ``flips`` uint8[n] or None.
+    Raises IndexError naming the first invalid sample.
+    """
+    src = np.ascontiguousarray(src, dtype=np.uint8).reshape(-1)
+    offsets = np.ascontiguousarray(offsets, dtype=np.int64)
+    sizes = np.ascontiguousarray(sizes, dtype=np.int32).reshape(-1, 2)
+    n_src = sizes.shape[0]
+    sel = None if sel is None else np.ascontiguousarray(sel, dtype=np.int64)
+    boxes = None if boxes is None else np.ascontiguousarray(boxes, dtype=np.int32).reshape(-1, 4)
+    flips = None if flips is None else np.ascontiguousarray(flips, dtype=np.uint8)
+    n = len(sel) if sel is not None else (len(boxes) if boxes is not None else n_src)
+    mean = np.asarray(mean, dtype=np.float32)
+    std = np.asarray(std, dtype=np.float32)
+    if out is None:
+        out = np.empty((n, 3, dst_h, dst_w), dtype=np.float32)
+    lib = _load(impl)
+    args = [_ptr(src, _u8p), _ptr(offsets, _i64p), _ptr(sizes, _i32p), n_src, _ptr(sel, _i64p),
+            _ptr(boxes, _i32p), _ptr(flips, _u8p), n, dst_h, dst_w, _ptr(mean, _f32p),
+            _ptr(std, _f32p), int(bool(normalize_01)), _ptr(out, _f32p)]
+    rc = lib.tlo_fused_batch(*args) if impl == "port" else lib.tlref_fused_batch(*args, int(threads))
+    if rc != 0:
+        raise IndexError(f"sample {-rc - 1}: index or crop box out of range")
+    return out
+
+
+def resize_bilinear_u8(img, dst_h, dst_w, impl="port"):
+    img = np.ascontiguousarray(img, dtype=np.uint8)
+    sh, sw = img.shape[:2]
+    out = np.empty((dst_h, dst_w, 3), dtype=np.uint8)
+    lib = _load(impl)
+    fn = lib.tlo_resize_bilinear_u8 if impl == "port" else lib.tlref_resize_bilinear
+    fn(_ptr(img, _u8p), _ptr(out, _u8p), sw, sh, dst_w, dst_h)
+    return out
+
+
+def bf16_bits(x):
+    """Round-to-nearest-even bf16 bit patterns (uint16) of an fp32 array."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    _load("port").tlo_f32_to_bf16_array(_ptr(x, _f32p), out.ctypes.data_as(C.POINTER(C.c_uint16)), x.size)
+    return out
+
+
+def nchw_to_nhwc(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n, c, h, w = x.shape
+    assert c == 3
+    out = np.empty((n, h, w, 3), dtype=np.float32)
+    _load("port").tlo_nchw_to_nhwc(_ptr(x, _f32p), _ptr(out, _f32p), n, h, w)
+    return out
+
+
+def ref_threads(flavour="parity"):
+    return int(_load(f"ref-{flavour}").tlref_threads())
+
+
+def ref_branch(flavour="parity"):
+    return _load(f"ref-{flavour}").tlref_simd_branch().decode()
+
+
+# ---- sharding (reference index math through the compiled headers) -----------------------
+
+def ref_shard_indices(kind, total, world, rank):
+    lib = _load("ref-parity")
+    out = np.empty(max(int(total), 1), dtype=np.int64)
+    k = lib.tlref_shard_indices(int(kind), int(total), int(world), int(rank), _ptr(out, _i64p), out.size)
+    if k < 0:
+        raise ValueError("reference constructor rejected the arguments")
+    return out[:k].copy()
+
+
+def ref_sampler_indices(total, world, rank, shuffle, seed, epoch, drop_last):
+    lib = _load("ref-parity")
+    out = np.empty(int(total) + int(world) + 1, dtype=np.int64)
+    k = lib.tlref_sampler_indices(int(total), int(world), int(rank), int(shuffle), int(seed), int(epoch),
+                                  int(drop_last), _ptr(out, _i64p), out.size)
+    if k < 0:
+        raise ValueError("reference constructor rejected the arguments")
+    return out[:k].copy()
+
+
+def ref_direct_order(total, shuffle, seed, epoch, distributed, rank, world):
+    lib = _load("ref-parity")
+    out = np.empty(max(int(total), 1), dtype=np.int64)
+    k = lib.tlref_direct_order(int(total), int(shuffle), int(seed), int(epoch), int(distributed),
+                               int(rank), int(world), _ptr(out, _i64p), out.size)
+    return out[:k].copy()

@@ -1,0 +1,651 @@
+// Host side of the C ABI declared in include/turboloader_b200.h: argument validation,
+// launch planning, the library-owned staging/param/output rings and the host-image
+// convenience forms.  C++20, CUDA runtime only; no torch or pybind types appear here.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <condition_variable>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../../include/turboloader_b200.h"
+#include "fused_params.h"
+
+namespace {
+
+thread_local std::string t_err;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    t_err = buf;
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(TLB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define TLB_CUDA(call)                                      \
+    do {                                                    \
+        cudaError_t e__ = (call);                           \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+    } while (0)
+
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+int env_int(const char* name, int dflt) {
+    const char* s = std::getenv(name);
+    if (!s || !*s) return dflt;
+    return std::atoi(s);
+}
+
+// ---- per-device state ---------------------------------------------------------------
+struct Buffer {
+    void* host = nullptr;   // pinned
+    void* dev = nullptr;
+    size_t cap = 0;
+    cudaEvent_t done = nullptr;  // recorded after the last upload from `host`
+    bool pending = false;
+};
+
+struct DeviceState {
+    std::mutex mu;
+    bool prepared = false;
+    Buffer params[4];  // ring for host-supplied per-sample tables
+    int params_next = 0;
+    Buffer images[2];  // ring for host-image batches (pixels + tables)
+    int images_next = 0;
+    void* out_ring[4] = {nullptr, nullptr, nullptr, nullptr};  // legacy pointer-returning forms
+    size_t out_cap[4] = {0, 0, 0, 0};
+    int out_next = 0;
+    void* sync_out = nullptr;  // device result of the synchronous host-image forms
+    size_t sync_out_cap = 0;
+    cudaStream_t stream = nullptr;  // private stream of the synchronous forms
+};
+
+constexpr int kMaxDevices = 64;
+DeviceState g_dev[kMaxDevices];
+
+int current_device(int* dev) {
+    cudaError_t e = cudaGetDevice(dev);
+    if (e != cudaSuccess) return fail(TLB_ERR_NO_DEVICE, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (*dev < 0 || *dev >= kMaxDevices) return fail(TLB_ERR_NO_DEVICE, "device ordinal %d unsupported", *dev);
+    return TLB_OK;
+}
+
+int ensure_prepared(DeviceState& st) {
+    if (st.prepared) return TLB_OK;
+    std::lock_guard<std::mutex> lk(st.mu);
+    if (st.prepared) return TLB_OK;
+    cudaError_t e = static_cast<cudaError_t>(tlb::prepare_device());
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
+    st.prepared = true;
+    return TLB_OK;
+}
+
+int grow(Buffer& b, size_t need) {
+    if (b.pending) {  // the previous upload from this pinned buffer must have left the host
+        TLB_CUDA(cudaEventSynchronize(b.done));
+        b.pending = false;
+    }
+    if (need <= b.cap) return TLB_OK;
+    size_t cap = std::max<size_t>(need + need / 4, 1 << 16);
+    if (b.host) cudaFreeHost(b.host);
+    if (b.dev) cudaFree(b.dev);
+    b.host = b.dev = nullptr;
+    b.cap = 0;
+    TLB_CUDA(cudaMallocHost(&b.host, cap));
+    TLB_CUDA(cudaMalloc(&b.dev, cap));
+    if (!b.done) TLB_CUDA(cudaEventCreateWithFlags(&b.done, cudaEventDisableTiming));
+    b.cap = cap;
+    return TLB_OK;
+}
+
+// ---- planning ------------------------------------------------------------------------
+int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl) {
+    const int W = d.dst_w, H = d.dst_h;
+    const int esz = d.out_dtype == TLB_F32 ? 4 : 2;
+    const int V = 16 / esz;
+    pl.n_col_tiles = (W + tlb::kMaxTileCols - 1) / tlb::kMaxTileCols;
+    pl.tile_cols = std::min(tlb::kMaxTileCols, round_up((W + pl.n_col_tiles - 1) / pl.n_col_tiles, 16));
+    pl.n_col_tiles = (W + pl.tile_cols - 1) / pl.tile_cols;
+    pl.tile_rows = std::clamp(env_int("TLB_TILE_ROWS", 16), 1, 1 << 20);
+    pl.tile_rows = std::min(pl.tile_rows, H);
+    pl.n_row_tiles = (H + pl.tile_rows - 1) / pl.tile_rows;
+    // Widest source footprint of one column tile (crop-local columns).
+    long long fw = std::min<long long>(max_crop_w, (static_cast<long long>(pl.tile_cols) * max_crop_w + W - 1) / W + 3);
+    pl.pitch = round_up(static_cast<int>(fw) * 3 + 30, 16);
+    pl.hpitch = 3 * pl.tile_cols;
+    const int per_row = pl.pitch + pl.hpitch * 4;
+    const int budget = std::clamp(env_int("TLB_SMEM_BUDGET", 48 * 1024), 8 * 1024, 200 * 1024);
+    int R = env_int("TLB_STAGED_ROWS", 0);
+    if (R <= 0) R = budget / per_row;
+    R = std::clamp(R, 2, tlb::kMaxStagedRows);
+    pl.staged_rows = R;
+    pl.smem_bytes = tlb::smem_layout(pl.tile_cols, R, pl.pitch, pl.hpitch).total;
+    if (pl.smem_bytes > 227 * 1024)
+        return fail(TLB_ERR_TOO_WIDE, "crop width %d needs %d bytes of shared memory per CTA (limit 232448)",
+                    max_crop_w, pl.smem_bytes);
+    const bool base_ok = (reinterpret_cast<uintptr_t>(d.out) & 15u) == 0;
+    if (d.out_layout == TLB_NCHW)
+        pl.vec_ok = base_ok && (W % V == 0);
+    else
+        pl.vec_ok = base_ok && ((3ll * W * esz) % 16 == 0);
+    pl.grid = static_cast<long long>(d.n) * pl.n_row_tiles * pl.n_col_tiles;
+    if (pl.grid > 0x7fffffffll) return fail(TLB_ERR_INVALID_ARG, "batch needs %lld CTAs (limit 2^31-1)", pl.grid);
+    return TLB_OK;
+}
+
+int check_common(const tlb_transform_desc* d) {
+    if (!d) return fail(TLB_ERR_INVALID_ARG, "desc is NULL");
+    if (d->n < 0) return fail(TLB_ERR_INVALID_ARG, "n = %d is negative", d->n);
+    if (d->dst_h <= 0 || d->dst_w <= 0) return fail(TLB_ERR_INVALID_ARG, "dst size %dx%d must be positive", d->dst_w, d->dst_h);
+    if (3ll * d->dst_h * d->dst_w > 0x3fffffffll) return fail(TLB_ERR_INVALID_ARG, "dst size %dx%d too large", d->dst_w, d->dst_h);
+    if (d->out_dtype != TLB_F32 && d->out_dtype != TLB_BF16) return fail(TLB_ERR_INVALID_ARG, "unknown out_dtype %d", d->out_dtype);
+    if (d->out_layout != TLB_NCHW && d->out_layout != TLB_NHWC) return fail(TLB_ERR_INVALID_ARG, "unknown out_layout %d", d->out_layout);
+    if (d->n == 0) return TLB_OK;
+    if (!d->src || !d->out) return fail(TLB_ERR_INVALID_ARG, "src and out must be non-NULL");
+    if (d->n_src <= 0) return fail(TLB_ERR_INVALID_ARG, "n_src = %lld must be positive", static_cast<long long>(d->n_src));
+    if (!d->src_sizes && (d->src_w <= 0 || d->src_h <= 0))
+        return fail(TLB_ERR_INVALID_ARG, "uniform source size %dx%d must be positive", d->src_w, d->src_h);
+    if (!d->sel && d->n > d->n_src) return fail(TLB_ERR_BAD_INDEX, "n = %d exceeds n_src = %lld without a gather index", d->n, static_cast<long long>(d->n_src));
+    for (int c = 0; c < 3; ++c)
+        if (!(d->std[c] != 0.0f)) return fail(TLB_ERR_INVALID_ARG, "std[%d] must be non-zero", c);
+    if (d->labels_out && !d->labels_in) return fail(TLB_ERR_INVALID_ARG, "labels_out given without labels_in");
+    if (!d->boxes && d->uniform_box[2] != 0) {
+        const int* b = d->uniform_box;
+        if (b[2] < 0 || b[3] <= 0 || b[0] < 0 || b[1] < 0) return fail(TLB_ERR_BAD_BOX, "uniform box (%d,%d,%d,%d) invalid", b[0], b[1], b[2], b[3]);
+        if (!d->src_sizes && (b[0] > d->src_w - b[2] || b[1] > d->src_h - b[3]))
+            return fail(TLB_ERR_BAD_BOX, "uniform box (%d,%d,%d,%d) leaves the %dx%d image", b[0], b[1], b[2], b[3], d->src_w, d->src_h);
+    }
+    return TLB_OK;
+}
+
+void fill_params(const tlb_transform_desc& d, tlb::FusedParams& p) {
+    p.src = d.src;
+    p.src_bytes = d.src_bytes;
+    p.n_src = d.n_src;
+    p.src_offsets = reinterpret_cast<const long long*>(d.src_offsets);
+    p.src_sizes = d.src_sizes;
+    p.src_w = d.src_w;
+    p.src_h = d.src_h;
+    p.n = d.n;
+    p.sel = reinterpret_cast<const long long*>(d.sel);
+    p.boxes = d.boxes;
+    for (int i = 0; i < 4; ++i) p.ubox[i] = d.uniform_box[i];
+    p.flips = d.flips;
+    p.dst_h = d.dst_h;
+    p.dst_w = d.dst_w;
+    p.out = d.out;
+    p.out_indices = reinterpret_cast<long long*>(d.out_indices);
+    p.labels_in = reinterpret_cast<const long long*>(d.labels_in);
+    p.labels_out = reinterpret_cast<long long*>(d.labels_out);
+    for (int c = 0; c < 3; ++c) {
+        p.mean[c] = d.mean[c];
+        p.inv_std[c] = 1.0f / d.std[c];
+    }
+    p.pre_scale = d.normalize_01 ? (1.0f / 255.0f) : 1.0f;
+    p.status = d.status;
+}
+
+int derive_max_crop_w(const tlb_transform_desc& d) {
+    if (d.max_crop_w > 0) return d.max_crop_w;
+    if (!d.boxes && d.uniform_box[2] > 0) return d.uniform_box[2];
+    return d.src_w;
+}
+
+int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream) {
+    int dev;
+    if (int rc = current_device(&dev)) return rc;
+    if (int rc = ensure_prepared(g_dev[dev])) return rc;
+    tlb::FusedParams p{};
+    fill_params(d, p);
+    if (int rc = make_plan(d, max_crop_w, p.plan)) return rc;
+    cudaError_t e = static_cast<cudaError_t>(tlb::launch_fused(p, d.out_dtype, d.out_layout, stream));
+    if (e != cudaSuccess) return cuda_fail(e, "fused_transform_kernel launch");
+    return TLB_OK;
+}
+
+// ---- small persistent worker pool for host-side packing ---------------------------------
+class Pool {
+public:
+    static Pool& get() {
+        static Pool p;
+        return p;
+    }
+    void run(size_t n, const std::function<void(size_t)>& fn) {
+        if (n == 0) return;
+        if (workers_.empty() || n == 1) {
+            for (size_t i = 0; i < n; ++i) fn(i);
+            return;
+        }
+        std::lock_guard<std::mutex> serial(run_mu_);
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            fn_ = &fn;
+            n_ = n;
+            next_.store(0);
+            busy_ = workers_.size();
+            ++epoch_;
+        }
+        cv_.notify_all();
+        drain();
+        std::unique_lock<std::mutex> lk(mu_);
+        done_cv_.wait(lk, [this] { return busy_ == 0; });
+    }
+    size_t threads() const { return workers_.size() + 1; }
+
+private:
+    Pool() {
+        unsigned hc = std::thread::hardware_concurrency();
+        unsigned want = std::min<unsigned>(hc > 1 ? hc - 1 : 0, 31);
+        int cap = env_int("TLB_PACK_THREADS", 0);
+        if (cap > 0) want = std::min<unsigned>(want, cap - 1);
+        for (unsigned i = 0; i < want; ++i) workers_.emplace_back([this] { loop(); });
+    }
+    ~Pool() {
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            stop_ = true;
+        }
+        cv_.notify_all();
+        for (auto& t : workers_) t.join();
+    }
+    void drain() {
+        for (;;) {
+            size_t i = next_.fetch_add(1);
+            if (i >= n_) break;
+            (*fn_)(i);
+        }
+    }
+    void loop() {
+        unsigned long long seen = 0;
+        for (;;) {
+            {
+                std::unique_lock<std::mutex> lk(mu_);
+                cv_.wait(lk, [&] { return stop_ || epoch_ != seen; });
+                if (stop_) return;
+                seen = epoch_;
+            }
+            drain();
+            std::lock_guard<std::mutex> lk(mu_);
+            if (--busy_ == 0) done_cv_.notify_one();
+        }
+    }
+    std::vector<std::thread> workers_;
+    std::mutex run_mu_, mu_;
+    std::condition_variable cv_, done_cv_;
+    const std::function<void(size_t)>* fn_ = nullptr;
+    size_t n_ = 0, busy_ = 0;
+    std::atomic<size_t> next_{0};
+    unsigned long long epoch_ = 0;
+    bool stop_ = false;
+};
+
+struct IntBox {
+    int x, y, w, h, flip;
+};
+
+int to_int_boxes(const tlb_image_ref* imgs, const tlb_crop_params* crops, int n, std::vector<IntBox>& out) {
+    out.resize(n);
+    for (int i = 0; i < n; ++i) {
+        if (!imgs[i].data || imgs[i].w <= 0 || imgs[i].h <= 0)
+            return fail(TLB_ERR_INVALID_ARG, "image %d: NULL data or non-positive size", i);
+        IntBox b{0, 0, imgs[i].w, imgs[i].h, 0};
+        if (crops) {
+            const tlb_crop_params& c = crops[i];
+            if (c.x != std::floor(c.x) || c.y != std::floor(c.y) || c.w != std::floor(c.w) || c.h != std::floor(c.h))
+                return fail(TLB_ERR_INVALID_ARG, "crop %d: (%g,%g,%g,%g) must be whole pixels", i, c.x, c.y, c.w, c.h);
+            b = IntBox{static_cast<int>(c.x), static_cast<int>(c.y), static_cast<int>(c.w), static_cast<int>(c.h), c.flip != 0};
+            if (b.w <= 0 || b.h <= 0 || b.x < 0 || b.y < 0 || b.x > imgs[i].w - b.w || b.y > imgs[i].h - b.h)
+                return fail(TLB_ERR_BAD_BOX, "crop %d: (%d,%d,%d,%d) leaves the %dx%d image", i, b.x, b.y, b.w, b.h, imgs[i].w, imgs[i].h);
+        }
+        out[i] = b;
+    }
+    return TLB_OK;
+}
+
+// Packs the crop rectangle of every host image (rows of cw*3 bytes, 16-byte aligned starts)
+// plus the per-sample tables into one pinned buffer, uploads it with ONE copy and launches.
+int host_images_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crops, int n, int dst_h, int dst_w,
+                          const float mean[3], const float std_[3], int normalize_01, void* out_dev, int out_dtype,
+                          int out_layout, uint32_t* status_dev, cudaStream_t stream) {
+    if (n <= 0) return fail(TLB_ERR_INVALID_ARG, "empty image list");
+    if (!imgs || !mean || !std_ || !out_dev) return fail(TLB_ERR_INVALID_ARG, "NULL argument");
+    int dev;
+    if (int rc = current_device(&dev)) return rc;
+    DeviceState& st = g_dev[dev];
+    std::vector<IntBox> boxes;
+    if (int rc = to_int_boxes(imgs, crops, n, boxes)) return rc;
+
+    std::vector<long long> offs(n);
+    size_t pix = 0;
+    int max_cw = 1;
+    for (int i = 0; i < n; ++i) {
+        offs[i] = static_cast<long long>(pix);
+        pix += (static_cast<size_t>(boxes[i].w) * boxes[i].h * 3 + 15) & ~static_cast<size_t>(15);
+        max_cw = std::max(max_cw, boxes[i].w);
+    }
+    const size_t off_tab = pix;                       // int64 offsets[n]
+    const size_t size_tab = off_tab + 8 * size_t(n);  // int32 sizes[n][2]
+    const size_t box_tab = size_tab + 8 * size_t(n);  // int32 boxes[n][4]
+    const size_t flip_tab = box_tab + 16 * size_t(n); // u8 flips[n]
+    const size_t total = (flip_tab + n + 15) & ~static_cast<size_t>(15);
+
+    std::unique_lock<std::mutex> lk(st.mu);
+    Buffer& buf = st.images[st.images_next];
+    st.images_next ^= 1;
+    if (int rc = grow(buf, total)) return rc;
+    lk.unlock();
+
+    auto* base = static_cast<unsigned char*>(buf.host);
+    auto* h_off = reinterpret_cast<long long*>(base + off_tab);
+    auto* h_size = reinterpret_cast<int*>(base + size_tab);
+    auto* h_box = reinterpret_cast<int*>(base + box_tab);
+    auto* h_flip = base + flip_tab;
+    for (int i = 0; i < n; ++i) {
+        h_off[i] = offs[i];
+        h_size[2 * i] = boxes[i].w;
+        h_size[2 * i + 1] = boxes[i].h;
+        h_box[4 * i] = 0;
+        h_box[4 * i + 1] = 0;
+        h_box[4 * i + 2] = boxes[i].w;
+        h_box[4 * i + 3] = boxes[i].h;
+        h_flip[i] = static_cast<unsigned char>(boxes[i].flip);
+    }
+    Pool::get().run(static_cast<size_t>(n), [&](size_t i) {
+        const IntBox& b = boxes[i];
+        const unsigned char* s = imgs[i].data + (static_cast<size_t>(b.y) * imgs[i].w + b.x) * 3;
+        unsigned char* d = base + offs[i];
+        const size_t row = static_cast<size_t>(b.w) * 3, pitch = static_cast<size_t>(imgs[i].w) * 3;
+        if (b.w == imgs[i].w) {
+            std::memcpy(d, s, row * b.h);
+        } else {
+            for (int y = 0; y < b.h; ++y) std::memcpy(d + y * row, s + y * pitch, row);
+        }
+    });
+    TLB_CUDA(cudaMemcpyAsync(buf.dev, buf.host, total, cudaMemcpyHostToDevice, stream));
+
+    tlb_transform_desc d{};
+    auto* dbase = static_cast<unsigned char*>(buf.dev);
+    d.src = dbase;
+    d.src_bytes = pix;
+    d.n_src = n;
+    d.src_offsets = reinterpret_cast<const int64_t*>(dbase + off_tab);
+    d.src_sizes = reinterpret_cast<const int32_t*>(dbase + size_tab);
+    d.n = n;
+    d.boxes = reinterpret_cast<const int32_t*>(dbase + box_tab);
+    d.flips = dbase + flip_tab;
+    d.dst_h = dst_h;
+    d.dst_w = dst_w;
+    d.out = out_dev;
+    d.out_dtype = out_dtype;
+    d.out_layout = out_layout;
+    for (int c = 0; c < 3; ++c) {
+        d.mean[c] = mean[c];
+        d.std[c] = std_[c];
+    }
+    d.normalize_01 = normalize_01;
+    d.max_crop_w = max_cw;
+    d.status = status_dev;
+    if (int rc = check_common(&d)) return rc;
+    const int rc = launch_desc(d, max_cw, stream);
+    // The buffer pair is reusable once the kernel that reads the device half has finished.
+    TLB_CUDA(cudaEventRecord(buf.done, stream));
+    buf.pending = true;
+    return rc;
+}
+
+int sync_host_form(const tlb_image_ref* imgs, const tlb_crop_params* crops, int n, int dst_h, int dst_w,
+                   const float mean[3], const float std_[3], float* out_host) {
+    if (!out_host) return fail(TLB_ERR_INVALID_ARG, "out is NULL");
+    if (n <= 0 || dst_h <= 0 || dst_w <= 0) return fail(TLB_ERR_INVALID_ARG, "empty batch or non-positive size");
+    int dev;
+    if (int rc = current_device(&dev)) return rc;
+    DeviceState& st = g_dev[dev];
+    const size_t bytes = static_cast<size_t>(n) * 3 * dst_h * dst_w * sizeof(float);
+    {
+        std::lock_guard<std::mutex> lk(st.mu);
+        if (!st.stream) TLB_CUDA(cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking));
+        if (bytes > st.sync_out_cap) {
+            if (st.sync_out) cudaFree(st.sync_out);
+            st.sync_out = nullptr;
+            st.sync_out_cap = 0;
+            TLB_CUDA(cudaMalloc(&st.sync_out, bytes));
+            st.sync_out_cap = bytes;
+        }
+    }
+    if (int rc = host_images_to_device(imgs, crops, n, dst_h, dst_w, mean, std_, 1, st.sync_out, TLB_F32, TLB_NCHW,
+                                       nullptr, st.stream))
+        return rc;
+    TLB_CUDA(cudaMemcpyAsync(out_host, st.sync_out, bytes, cudaMemcpyDeviceToHost, st.stream));
+    TLB_CUDA(cudaStreamSynchronize(st.stream));
+    return TLB_OK;
+}
+
+uintptr_t resident_form(uintptr_t src_dev, uintptr_t sel_dev, bool gather, int n, int h, int w, const float mean[3],
+                        const float std_[3]) {
+    if (!src_dev || (gather && !sel_dev) || n <= 0 || h <= 0 || w <= 0 || !mean || !std_) {
+        fail(TLB_ERR_INVALID_ARG, "resident normalize: NULL pointer or non-positive size");
+        return 0;
+    }
+    int dev;
+    if (current_device(&dev)) return 0;
+    DeviceState& st = g_dev[dev];
+    std::lock_guard<std::mutex> lk(st.mu);
+    if (!st.stream && cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking) != cudaSuccess) {
+        fail(TLB_ERR_CUDA, "cudaStreamCreate failed");
+        return 0;
+    }
+    const size_t bytes = static_cast<size_t>(n) * 3 * h * w * sizeof(float);
+    const int slot = st.out_next;
+    if (bytes > st.out_cap[slot]) {
+        if (st.out_ring[slot]) cudaFree(st.out_ring[slot]);
+        st.out_ring[slot] = nullptr;
+        st.out_cap[slot] = 0;
+        cudaError_t e = cudaMalloc(&st.out_ring[slot], bytes);
+        if (e != cudaSuccess) {
+            cuda_fail(e, "cudaMalloc(resident output ring)");
+            return 0;
+        }
+        st.out_cap[slot] = bytes;
+    }
+    tlb_transform_desc d{};
+    d.src = reinterpret_cast<const uint8_t*>(src_dev);
+    // Without a gather the batch is the first n images at src_dev.  With one, the caller's
+    // dataset extent is unknown to this legacy signature: indices are trusted, as in the
+    // function it replaces, and the readable region is left unbounded.
+    d.n_src = gather ? (1ll << 40) : n;
+    d.src_bytes = gather ? ~0ull >> 1 : static_cast<uint64_t>(n) * h * w * 3;
+    d.src_w = w;
+    d.src_h = h;
+    d.n = n;
+    d.sel = gather ? reinterpret_cast<const int64_t*>(sel_dev) : nullptr;
+    d.dst_h = h;
+    d.dst_w = w;
+    d.out = st.out_ring[slot];
+    d.out_dtype = TLB_F32;
+    d.out_layout = TLB_NCHW;
+    for (int c = 0; c < 3; ++c) {
+        d.mean[c] = mean[c];
+        d.std[c] = std_[c];
+    }
+    d.normalize_01 = 1;
+    if (check_common(&d)) return 0;
+    if (launch_desc(d, w, st.stream)) return 0;
+    cudaError_t e = cudaStreamSynchronize(st.stream);
+    if (e != cudaSuccess) {
+        cuda_fail(e, "resident normalize");
+        return 0;
+    }
+    st.out_next = (slot + 1) % 4;
+    return reinterpret_cast<uintptr_t>(st.out_ring[slot]);
+}
+
+}  // namespace
+
+extern "C" {
+
+int tlb_available(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        return 0;
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
+    return major == 10 ? 1 : 0;  // the kernels are built for sm_100a only
+}
+
+int tlb_device_name(int device, char* buf, size_t cap) {
+    if (!buf || cap == 0) return fail(TLB_ERR_INVALID_ARG, "buf is NULL or empty");
+    buf[0] = 0;
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TLB_ERR_NO_DEVICE, "cudaGetDeviceProperties(%d): %s", device, cudaGetErrorString(e));
+    }
+    std::snprintf(buf, cap, "%s", prop.name);
+    return TLB_OK;
+}
+
+const char* tlb_version(void) { return "turboloader_b200 0.1 (sm_100a)"; }
+
+const char* tlb_last_error(void) { return t_err.c_str(); }
+
+int tlb_fused_transform(const tlb_transform_desc* desc, void* stream) {
+    if (int rc = check_common(desc)) return rc;
+    if (desc->n == 0) return TLB_OK;
+    const int mcw = derive_max_crop_w(*desc);
+    if (mcw <= 0)
+        return fail(TLB_ERR_INVALID_ARG, "max_crop_w is required when sizes and boxes are per-sample device tables");
+    return launch_desc(*desc, mcw, stream);
+}
+
+int tlb_fused_transform_host_params(const tlb_transform_desc* desc, void* stream) {
+    if (int rc = check_common(desc)) return rc;
+    const tlb_transform_desc& d = *desc;
+    if (d.n == 0) return TLB_OK;
+    const int n = d.n;
+    // ---- validate on the host -----------------------------------------------------------
+    int max_cw = 0;
+    for (int k = 0; k < n; ++k) {
+        const long long s = d.sel ? d.sel[k] : k;
+        if (s < 0 || s >= d.n_src) return fail(TLB_ERR_BAD_INDEX, "sample %d: gather index %lld outside [0, %lld)", k, s, static_cast<long long>(d.n_src));
+        const int iw = d.src_sizes ? d.src_sizes[2 * s] : d.src_w;
+        const int ih = d.src_sizes ? d.src_sizes[2 * s + 1] : d.src_h;
+        int x = 0, y = 0, w = iw, h = ih;
+        if (d.boxes) {
+            x = d.boxes[4 * k]; y = d.boxes[4 * k + 1]; w = d.boxes[4 * k + 2]; h = d.boxes[4 * k + 3];
+        } else if (d.uniform_box[2] > 0) {
+            x = d.uniform_box[0]; y = d.uniform_box[1]; w = d.uniform_box[2]; h = d.uniform_box[3];
+        }
+        if (iw <= 0 || ih <= 0 || w <= 0 || h <= 0 || x < 0 || y < 0 || x > iw - w || y > ih - h)
+            return fail(TLB_ERR_BAD_BOX, "sample %d: box (%d,%d,%d,%d) leaves the %dx%d image", k, x, y, w, h, iw, ih);
+        const long long off = d.src_offsets ? d.src_offsets[s] : s * (static_cast<long long>(iw) * ih * 3);
+        if (off < 0 || static_cast<unsigned long long>(off) + static_cast<unsigned long long>(iw) * ih * 3 > d.src_bytes)
+            return fail(TLB_ERR_BAD_INDEX, "sample %d: image %lld lies outside the %llu readable bytes", k, s, static_cast<unsigned long long>(d.src_bytes));
+        max_cw = std::max(max_cw, w);
+    }
+    // ---- upload the tables ---------------------------------------------------------------
+    int dev;
+    if (int rc = current_device(&dev)) return rc;
+    DeviceState& st = g_dev[dev];
+    const size_t ns = static_cast<size_t>(d.n_src);
+    size_t off_sel = 0, off_box = 0, off_flip = 0, off_offs = 0, off_sizes = 0, total = 0;
+    auto reserve = [&](size_t bytes) { size_t o = total; total = (total + bytes + 15) & ~static_cast<size_t>(15); return o; };
+    if (d.sel) off_sel = reserve(8 * size_t(n));
+    if (d.boxes) off_box = reserve(16 * size_t(n));
+    if (d.flips) off_flip = reserve(size_t(n));
+    if (d.src_offsets) off_offs = reserve(8 * ns);
+    if (d.src_sizes) off_sizes = reserve(8 * ns);
+    tlb_transform_desc dd = d;
+    if (total) {
+        std::unique_lock<std::mutex> lk(st.mu);
+        Buffer& buf = st.params[st.params_next];
+        st.params_next = (st.params_next + 1) % 4;
+        if (int rc = grow(buf, total)) return rc;
+        lk.unlock();
+        auto* hb = static_cast<unsigned char*>(buf.host);
+        auto* db = static_cast<unsigned char*>(buf.dev);
+        if (d.sel) { std::memcpy(hb + off_sel, d.sel, 8 * size_t(n)); dd.sel = reinterpret_cast<const int64_t*>(db + off_sel); }
+        if (d.boxes) { std::memcpy(hb + off_box, d.boxes, 16 * size_t(n)); dd.boxes = reinterpret_cast<const int32_t*>(db + off_box); }
+        if (d.flips) { std::memcpy(hb + off_flip, d.flips, size_t(n)); dd.flips = db + off_flip; }
+        if (d.src_offsets) { std::memcpy(hb + off_offs, d.src_offsets, 8 * ns); dd.src_offsets = reinterpret_cast<const int64_t*>(db + off_offs); }
+        if (d.src_sizes) { std::memcpy(hb + off_sizes, d.src_sizes, 8 * ns); dd.src_sizes = reinterpret_cast<const int32_t*>(db + off_sizes); }
+        cudaStream_t cs = static_cast<cudaStream_t>(stream);
+        TLB_CUDA(cudaMemcpyAsync(buf.dev, buf.host, total, cudaMemcpyHostToDevice, cs));
+        const int rc = launch_desc(dd, max_cw, stream);
+        // Reusable once the kernel that reads the device half has finished.
+        TLB_CUDA(cudaEventRecord(buf.done, cs));
+        buf.pending = true;
+        return rc;
+    }
+    return launch_desc(dd, max_cw, stream);
+}
+
+int tlb_resize_normalize_batch(const tlb_image_ref* imgs, int32_t n, int32_t dst_h, int32_t dst_w, const float mean[3],
+                               const float std_[3], float* out_host) {
+    return sync_host_form(imgs, nullptr, n, dst_h, dst_w, mean, std_, out_host);
+}
+
+int tlb_crop_resize_normalize_batch(const tlb_image_ref* imgs, const tlb_crop_params* crops, int32_t n, int32_t dst_h,
+                                    int32_t dst_w, const float mean[3], const float std_[3], float* out_host) {
+    if (!crops) return fail(TLB_ERR_INVALID_ARG, "crops is NULL");
+    return sync_host_form(imgs, crops, n, dst_h, dst_w, mean, std_, out_host);
+}
+
+int tlb_crop_resize_normalize_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crops, int32_t n,
+                                        int32_t dst_h, int32_t dst_w, const float mean[3], const float std_[3],
+                                        int32_t normalize_01, void* out_dev, int32_t out_dtype, int32_t out_layout,
+                                        uint32_t* status_dev, void* stream) {
+    if (dst_h <= 0 || dst_w <= 0) return fail(TLB_ERR_INVALID_ARG, "dst size must be positive");
+    return host_images_to_device(imgs, crops, n, dst_h, dst_w, mean, std_, normalize_01, out_dev, out_dtype, out_layout,
+                                 status_dev, static_cast<cudaStream_t>(stream));
+}
+
+uintptr_t tlb_normalize_resident_batch(uintptr_t src_dev, int32_t n, int32_t h, int32_t w, const float mean[3],
+                                       const float std_[3]) {
+    return resident_form(src_dev, 0, false, n, h, w, mean, std_);
+}
+
+uintptr_t tlb_normalize_resident_gather_batch(uintptr_t src_dev, uintptr_t sel_dev, int32_t n, int32_t h, int32_t w,
+                                              const float mean[3], const float std_[3]) {
+    return resident_form(src_dev, sel_dev, true, n, h, w, mean, std_);
+}
+
+int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block, int32_t* smem_bytes,
+                   int32_t* tile_rows, int32_t* tile_cols) {
+    if (int rc = check_common(desc)) return rc;
+    const int mcw = derive_max_crop_w(*desc);
+    if (mcw <= 0) return fail(TLB_ERR_INVALID_ARG, "max_crop_w is required");
+    tlb::Plan pl{};
+    if (int rc = make_plan(*desc, mcw, pl)) return rc;
+    if (grid) *grid = static_cast<int32_t>(pl.grid);
+    if (block) *block = tlb::kThreads;
+    if (smem_bytes) *smem_bytes = pl.smem_bytes;
+    if (tile_rows) *tile_rows = pl.tile_rows;
+    if (tile_cols) *tile_cols = pl.tile_cols;
+    return TLB_OK;
+}
+
+uint64_t tlb_launch_count(void) { return tlb::launch_count(); }
+
+}  // extern "C"

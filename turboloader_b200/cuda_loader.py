@@ -1,0 +1,278 @@
+"""GPU-resident image loader over the fused sm_100a transform.
+
+Keeps the constructor, iteration and ``return_indices`` contract of TurboLoader's
+``CudaResidentLoader`` (turboloader/cuda_loader.py:385-535): the uint8 dataset is uploaded
+once, every epoch is served from HBM with one kernel launch per batch, the shuffle is the
+device-side index gather fused into that kernel, and the permutation is
+``np.random.default_rng(seed + epoch).permutation(n)`` (cuda_loader.py:506-510).
+
+Additions that default to the reference behaviour: ``crop_size`` / ``output_size`` /
+``hflip_prob`` / explicit ``boxes`` (crop + flip + resize fused into the same launch),
+``dtype`` (float32 | bfloat16), ``channels_last``, and ``state_dict`` /
+``load_state_dict`` with the same dict the CPU loaders use
+(turboloader/__init__.py:689-700).  Unlike the reference there is no per-batch
+synchronisation: batches are enqueued on the current stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _capi, ops
+
+__all__ = ["CudaResidentLoader", "_CudaArray"]
+
+
+class _CudaArray:
+    """A CUDA device pointer as a ``__cuda_array_interface__`` v3 float32 array
+    (turboloader/cuda_loader.py:37-55) so torch/cupy adopt it without a copy:
+    ``torch.as_tensor(x, device='cuda')``.  ``owner`` keeps the backing allocation alive."""
+
+    def __init__(self, ptr, shape, owner=None, stream=None):
+        self.__cuda_array_interface__ = {
+            "data": (int(ptr), False),
+            "shape": tuple(int(s) for s in shape),
+            "typestr": "<f4",
+            "version": 3,
+        }
+        if stream is not None:
+            self.__cuda_array_interface__["stream"] = int(stream)
+        self._owner = owner
+
+    @property
+    def shape(self):
+        return self.__cuda_array_interface__["shape"]
+
+    def __len__(self):
+        return self.shape[0]
+
+
+class CudaResidentLoader:
+    def __init__(self, paths, image_size=160, batch_size=64, *, mean=ops.IMAGENET_MEAN, std=ops.IMAGENET_STD,
+                 drop_last=True, num_workers=8, shuffle=False, seed=42, return_indices=False, **extra):
+        from concurrent.futures import ThreadPoolExecutor
+
+        from PIL import Image
+
+        paths = list(paths)
+        H = W = int(image_size)
+        arr = np.empty((len(paths), H, W, 3), dtype=np.uint8)
+
+        def _load(i):
+            with Image.open(paths[i]) as im:
+                arr[i] = np.asarray(im.convert("RGB").resize((W, H)))
+
+        with ThreadPoolExecutor(max_workers=max(1, int(num_workers))) as ex:
+            list(ex.map(_load, range(len(paths))))
+        self._init_common(arr, batch_size, mean=mean, std=std, drop_last=drop_last, shuffle=shuffle, seed=seed,
+                          return_indices=return_indices, **extra)
+
+    @classmethod
+    def from_array(cls, array, batch_size=64, **kw):
+        """Build from an in-memory or memory-mapped ``(N, H, W, 3)`` uint8 array (or an
+        already-resident CUDA uint8 tensor of that shape)."""
+        self = cls.__new__(cls)
+        self._init_common(array, batch_size, **kw)
+        return self
+
+    @classmethod
+    def from_tbl(cls, path, batch_size=64, **kw):
+        """Build from a pre-processed RAW_U8 ``.tbl`` file (turboloader/cuda_loader.py:453-492):
+        the upload reads straight through a memory map."""
+        from .tbl import open_raw_view
+
+        view, H, W = open_raw_view(path)
+        if H != W:
+            raise ValueError(f"resident loader needs square samples, file is {W}x{H}")
+        return cls.from_array(view, batch_size, **kw)
+
+    # ------------------------------------------------------------------------------------
+    def _init_common(self, array, batch_size, *, mean=ops.IMAGENET_MEAN, std=ops.IMAGENET_STD, drop_last=True,
+                     shuffle=False, seed=42, return_indices=False, crop_size=None, output_size=None,
+                     hflip_prob=0.0, boxes=None, dtype=None, channels_last=False, as_tensor=None, labels=None,
+                     ring=4, device=None):
+        import torch
+
+        if not ops.cuda_available():
+            raise RuntimeError("CudaResidentLoader needs an sm_100 CUDA device and the built C-ABI library.")
+        self._torch = torch
+        self._device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        if isinstance(array, torch.Tensor):
+            if array.dtype != torch.uint8 or array.dim() != 4 or array.shape[3] != 3:
+                raise ValueError("dataset tensor must be (N, H, W, 3) uint8")
+            self._gpu = array.to(self._device).contiguous()
+        else:
+            if array.ndim != 4 or array.shape[3] != 3 or array.dtype != np.uint8:
+                raise ValueError("dataset must be (N, H, W, 3) uint8")
+            n, H, W, _ = array.shape
+            # Chunked upload (~64 MB): peak host memory is one chunk even for a memory map.
+            self._gpu = torch.empty((n, H, W, 3), dtype=torch.uint8, device=self._device)
+            step = max(1, (64 << 20) // max(1, H * W * 3))
+            for s in range(0, n, step):
+                chunk = np.ascontiguousarray(array[s:s + step])
+                self._gpu[s:s + chunk.shape[0]] = torch.from_numpy(chunk)
+        self._n, self._H, self._W = int(self._gpu.shape[0]), int(self._gpu.shape[1]), int(self._gpu.shape[2])
+        self.batch_size = int(batch_size)
+        self.mean, self.std = list(mean), list(std)
+        self.drop_last, self.shuffle, self.seed = bool(drop_last), bool(shuffle), int(seed)
+        self.return_indices = bool(return_indices)
+        self.hflip_prob = float(hflip_prob)
+        self.channels_last = bool(channels_last)
+        self.dtype = torch.float32 if dtype is None else dtype
+        if self.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("dtype must be torch.float32 or torch.bfloat16")
+        if crop_size is None:
+            self._box = (0, 0, self._W, self._H)
+        else:
+            cw, ch = (crop_size, crop_size) if np.isscalar(crop_size) else (crop_size[1], crop_size[0])
+            if cw > self._W or ch > self._H or cw <= 0 or ch <= 0:
+                raise ValueError("crop_size must fit inside the stored images")
+            # Centre crop: offset (W - cw) / 2 (src/transforms/crop_transform.hpp:37-38).
+            self._box = ((self._W - int(cw)) // 2, (self._H - int(ch)) // 2, int(cw), int(ch))
+        if output_size is None:
+            self._oh, self._ow = self._box[3], self._box[2]
+        else:
+            self._oh, self._ow = (output_size, output_size) if np.isscalar(output_size) else tuple(output_size)
+        self._boxes_fn = boxes  # callable(epoch, order) -> int32[len(order), 4], or None
+        # Plain float32 NCHW batches are handed out as __cuda_array_interface__ objects like the
+        # reference's; bf16 has no CAI typestr and channels-last needs strides, so those are tensors.
+        plain = self.dtype == torch.float32 and not self.channels_last
+        self._as_tensor = (not plain) if as_tensor is None else bool(as_tensor) or not plain
+        self._labels = None if labels is None else torch.as_tensor(np.asarray(labels), dtype=torch.int64).to(self._device)
+        self._ring = [None] * max(2, int(ring))
+        self._ring_pos = 0
+        self._epoch = 0
+        self._resume_batches = 0
+        self._batches_served = 0
+        self._status = torch.zeros(1, dtype=torch.int32, device=self._device)
+
+    # ---- reference surface ------------------------------------------------------------------
+    def set_epoch(self, epoch):
+        self._epoch = int(epoch)
+
+    def __len__(self):
+        return self._n // self.batch_size if self.drop_last else -(-self._n // self.batch_size)
+
+    def state_dict(self):
+        return {"version": 1, "epoch": int(self._epoch), "batches_served": int(self._batches_served)}
+
+    def load_state_dict(self, state):
+        if int(state.get("version", 0)) != 1:
+            raise ValueError("unsupported state_dict version")
+        self._epoch = int(state["epoch"])
+        self._resume_batches = int(state["batches_served"])
+
+    def device_status(self) -> int:
+        """Status bits the kernels OR-ed so far (synchronises); 0 when every sample was valid."""
+        return int(self._status.item())
+
+    # ---- epoch plan ---------------------------------------------------------------------------
+    def epoch_order(self, epoch=None) -> np.ndarray:
+        e = self._epoch if epoch is None else int(epoch)
+        if self.shuffle:
+            return np.random.default_rng(self.seed + e).permutation(self._n).astype(np.int64)
+        return np.arange(self._n, dtype=np.int64)
+
+    def epoch_flips(self, epoch=None) -> np.ndarray:
+        """Flip flag per epoch position: Bernoulli(hflip_prob) from ``default_rng([seed, epoch, 7])``."""
+        e = self._epoch if epoch is None else int(epoch)
+        if self.hflip_prob <= 0.0:
+            return np.zeros(self._n, dtype=np.uint8)
+        return (np.random.default_rng([self.seed, e, 7]).random(self._n) < self.hflip_prob).astype(np.uint8)
+
+    def _out_buffer(self, n):
+        torch = self._torch
+        shape = (n, self._oh, self._ow, 3) if self.channels_last else (n, 3, self._oh, self._ow)
+        slot = self._ring_pos
+        self._ring_pos = (slot + 1) % len(self._ring)
+        buf = self._ring[slot]
+        if buf is None or buf.shape[0] < self.batch_size:
+            full = (self.batch_size,) + shape[1:]
+            buf = torch.empty(full, dtype=self.dtype, device=self._device)
+            self._ring[slot] = buf
+        return buf[:n]
+
+    def __iter__(self):
+        torch = self._torch
+        bs = self.batch_size
+        end = (self._n // bs) * bs if self.drop_last else self._n
+        order = self.epoch_order()
+        flips = self.epoch_flips()
+        with torch.cuda.device(self._device):
+            d_order = torch.from_numpy(order).to(self._device) if self.shuffle else None
+            d_flips = torch.from_numpy(flips).to(self._device) if self.hflip_prob > 0.0 else None
+            d_boxes = None
+            if self._boxes_fn is not None:
+                b = np.ascontiguousarray(self._boxes_fn(self._epoch, order), dtype=np.int32).reshape(-1, 4)
+                if b.shape[0] != self._n:
+                    raise ValueError("boxes callable must return one box per epoch position")
+                if (b[:, 2] <= 0).any() or (b[:, 3] <= 0).any() or (b[:, 0] < 0).any() or (b[:, 1] < 0).any() or \
+                        (b[:, 0] + b[:, 2] > self._W).any() or (b[:, 1] + b[:, 3] > self._H).any():
+                    raise ValueError("a crop box leaves the stored image")
+                d_boxes = torch.from_numpy(b).to(self._device)
+                max_cw = int(b[:, 2].max())
+            else:
+                max_cw = self._box[2]
+            d_idx_ring = [torch.empty(bs, dtype=torch.int64, device=self._device) for _ in self._ring] \
+                if (self.return_indices and self.shuffle) else None
+            d_lab_ring = [torch.empty(bs, dtype=torch.int64, device=self._device) for _ in self._ring] \
+                if self._labels is not None else None
+            lib = _capi.load()
+            start = self._resume_batches * bs
+            self._batches_served = self._resume_batches
+            self._resume_batches = 0
+            stride = self._H * self._W * 3
+            for b0 in range(start, end, bs):
+                n = min(bs, self._n - b0)
+                out = self._out_buffer(n)
+                slot = (self._ring_pos - 1) % len(self._ring)
+                d = _capi.TransformDesc()
+                if d_order is not None:
+                    d.src = self._gpu.data_ptr()
+                    d.src_bytes = self._gpu.numel()
+                    d.n_src = self._n
+                    d.sel = d_order.data_ptr() + 8 * b0
+                else:  # sequential: the batch is a contiguous slice of the dataset
+                    d.src = self._gpu.data_ptr() + b0 * stride
+                    d.src_bytes = n * stride
+                    d.n_src = n
+                d.src_w, d.src_h = self._W, self._H
+                d.n = n
+                if d_boxes is not None:
+                    d.boxes = d_boxes.data_ptr() + 16 * b0
+                else:
+                    d.uniform_box = (C.c_int32 * 4)(*self._box)
+                if d_flips is not None:
+                    d.flips = d_flips.data_ptr() + b0
+                d.dst_h, d.dst_w = self._oh, self._ow
+                d.out = out.data_ptr()
+                d.out_dtype = _capi.TLB_F32 if self.dtype == torch.float32 else _capi.TLB_BF16
+                d.out_layout = _capi.TLB_NHWC if self.channels_last else _capi.TLB_NCHW
+                if d_idx_ring is not None:
+                    d.out_indices = d_idx_ring[slot].data_ptr()
+                if d_lab_ring is not None:
+                    d.labels_in = self._labels.data_ptr()
+                    d.labels_out = d_lab_ring[slot].data_ptr()
+                    if d_order is None:  # labels of a sequential slice start at b0
+                        d.labels_in = self._labels.data_ptr() + 8 * b0
+                d.mean = _capi.f3(self.mean)
+                d.std = _capi.f3(self.std)
+                d.normalize_01 = 1
+                d.max_crop_w = max_cw
+                d.status = self._status.data_ptr()
+                stream = torch.cuda.current_stream(self._device)
+                _capi.check(lib.tlb_fused_transform(C.byref(d), C.c_void_p(stream.cuda_stream)))
+                self._batches_served += 1
+                if self._as_tensor:
+                    batch = out.permute(0, 3, 1, 2) if self.channels_last else out
+                else:
+                    batch = _CudaArray(out.data_ptr(), (n, 3, self._oh, self._ow), owner=out)
+                items = [batch]
+                if d_lab_ring is not None:
+                    items.append(d_lab_ring[slot][:n])
+                if self.return_indices:
+                    items.append(d_idx_ring[slot][:n] if d_idx_ring is not None else np.arange(b0, b0 + n))
+                yield items[0] if len(items) == 1 else tuple(items)
+            self._batches_served = 0
+            self._epoch_done = True

@@ -1,0 +1,212 @@
+"""Python-facing operators: the names and argument meaning of TurboLoader's ``cuda_*``
+bindings (src/python/turboloader_bindings.cpp:1623-1753) over the B200 C ABI, plus the
+general ``fused_transform`` the loaders use.  torch appears only to allocate device
+memory and to name the current stream; every computation happens inside the C-ABI
+library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _capi
+
+IMAGENET_MEAN = (0.485, 0.456, 0.406)
+IMAGENET_STD = (0.229, 0.224, 0.225)
+
+
+def cuda_available() -> bool:
+    """True if the library loads and the current device is an sm_100 GPU
+    (``turboloader.cuda_available``, turboloader_bindings.cpp:1627)."""
+    return bool(_capi.load().tlb_available())
+
+
+def cuda_device_name(device: int = 0) -> str:
+    """Device name or '' (``turboloader.cuda_device_name``, turboloader_bindings.cpp:1629)."""
+    buf = C.create_string_buffer(256)
+    if _capi.load().tlb_device_name(int(device), buf, 256) != 0:
+        return ""
+    return buf.value.decode()
+
+
+def launch_count() -> int:
+    return int(_capi.load().tlb_launch_count())
+
+
+def _image_refs(images):
+    holds, refs = [], (_capi.ImageRef * len(images))()
+    for i, im in enumerate(images):
+        a = np.ascontiguousarray(im, dtype=np.uint8)
+        if a.ndim != 3 or a.shape[2] != 3:
+            raise RuntimeError("each image must be HxWx3 uint8 (RGB)")
+        holds.append(a)
+        refs[i].data = a.ctypes.data
+        refs[i].w = a.shape[1]
+        refs[i].h = a.shape[0]
+    return holds, refs
+
+
+def _crop_params(crops, flips, n):
+    crops = np.ascontiguousarray(crops, dtype=np.float32)
+    flips = np.ascontiguousarray(flips, dtype=np.int32)
+    if crops.ndim != 2 or crops.shape != (n, 4):
+        raise RuntimeError("crops must have shape (N, 4): x, y, w, h in src pixels")
+    if flips.ndim != 1 or flips.shape[0] != n:
+        raise RuntimeError("flips must have shape (N,)")
+    arr = (_capi.CropParams * n)()
+    for i in range(n):
+        arr[i].x, arr[i].y, arr[i].w, arr[i].h = (float(v) for v in crops[i])
+        arr[i].flip = int(flips[i])
+    return arr
+
+
+def cuda_resize_normalize(images, dst_h, dst_w, mean=IMAGENET_MEAN, std=IMAGENET_STD):
+    """List of HWC uint8 RGB arrays -> host float32 ``(N, 3, dst_h, dst_w)``
+    (``turboloader.cuda_resize_normalize``, turboloader_bindings.cpp:1631-1664)."""
+    images = list(images)
+    if not images:
+        raise RuntimeError("cuda_resize_normalize: empty image list")
+    holds, refs = _image_refs(images)
+    out = np.empty((len(images), 3, int(dst_h), int(dst_w)), dtype=np.float32)
+    _capi.check(_capi.load().tlb_resize_normalize_batch(refs, len(images), int(dst_h), int(dst_w), _capi.f3(mean),
+                                                        _capi.f3(std), out.ctypes.data))
+    del holds
+    return out
+
+
+def cuda_crop_resize_normalize(images, crops, flips, dst_h, dst_w, mean=IMAGENET_MEAN, std=IMAGENET_STD):
+    """Fused crop + flip + resize + normalize of host images -> host float32 NCHW.  Same
+    arguments as the reference's ``metal_crop_resize_normalize`` binding
+    (turboloader_bindings.cpp:1326-1363); the CUDA twin exists in the reference
+    (src/cuda/cuda_transforms.hpp:117-119) but is not bound there.  Crop values must be
+    whole pixels: results follow the CPU fused path, whose crop rects are integers."""
+    images = list(images)
+    if not images:
+        raise RuntimeError("cuda_crop_resize_normalize: empty image list")
+    holds, refs = _image_refs(images)
+    cps = _crop_params(crops, flips, len(images))
+    out = np.empty((len(images), 3, int(dst_h), int(dst_w)), dtype=np.float32)
+    _capi.check(_capi.load().tlb_crop_resize_normalize_batch(refs, cps, len(images), int(dst_h), int(dst_w),
+                                                             _capi.f3(mean), _capi.f3(std), out.ctypes.data))
+    del holds
+    return out
+
+
+def cuda_normalize_resident(src_dev, N, H, W, mean=IMAGENET_MEAN, std=IMAGENET_STD) -> int:
+    """Device ``[N,H,W,3]`` uint8 at address ``src_dev`` -> device address (int) of the
+    ``[N,3,H,W]`` float32 batch, valid until the 4th-next call
+    (``turboloader.cuda_normalize_resident``, turboloader_bindings.cpp:1665-1684)."""
+    ptr = _capi.load().tlb_normalize_resident_batch(int(src_dev), int(N), int(H), int(W), _capi.f3(mean),
+                                                    _capi.f3(std))
+    if not ptr:
+        raise RuntimeError("cuda_normalize_resident failed: " + _capi.load().tlb_last_error().decode())
+    return int(ptr)
+
+
+def cuda_normalize_resident_gather(src_dev, sel_dev, N, H, W, mean=IMAGENET_MEAN, std=IMAGENET_STD) -> int:
+    """Like ``cuda_normalize_resident`` but sample n reads dataset image ``sel_dev[n]``
+    (device int64) (``turboloader.cuda_normalize_resident_gather``,
+    turboloader_bindings.cpp:1736-1753)."""
+    ptr = _capi.load().tlb_normalize_resident_gather_batch(int(src_dev), int(sel_dev), int(N), int(H), int(W),
+                                                           _capi.f3(mean), _capi.f3(std))
+    if not ptr:
+        raise RuntimeError("cuda_normalize_resident_gather failed: " + _capi.load().tlb_last_error().decode())
+    return int(ptr)
+
+
+# ---- the general device-resident call ---------------------------------------------------------
+
+def _dev_ptr(t, dtype, what):
+    import torch
+
+    if t is None:
+        return None
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError(f"{what} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise TypeError(f"{what} must have dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{what} must be contiguous")
+    return t.data_ptr()
+
+
+def make_desc(src, *, n, dst_h, dst_w, out, src_w=0, src_h=0, n_src=None, src_offsets=None, src_sizes=None,
+              sel=None, boxes=None, uniform_box=None, flips=None, mean=IMAGENET_MEAN, std=IMAGENET_STD,
+              normalize_01=True, channels_last=False, out_indices=None, labels_in=None, labels_out=None,
+              max_crop_w=0, status=None):
+    """Fill a ``tlb_transform_desc`` from CUDA tensors (all tables on the device)."""
+    import torch
+
+    d = _capi.TransformDesc()
+    d.src = _dev_ptr(src, torch.uint8, "src")
+    d.src_bytes = src.numel()
+    if n_src is None:
+        n_src = src_sizes.shape[0] if src_sizes is not None else (src.shape[0] if src.dim() == 4 else n)
+    d.n_src = int(n_src)
+    d.src_offsets = _dev_ptr(src_offsets, torch.int64, "src_offsets")
+    d.src_sizes = _dev_ptr(src_sizes, torch.int32, "src_sizes")
+    if src.dim() == 4 and not (src_w and src_h):
+        src_h, src_w = src.shape[1], src.shape[2]
+    d.src_w, d.src_h = int(src_w), int(src_h)
+    d.n = int(n)
+    d.sel = _dev_ptr(sel, torch.int64, "sel")
+    d.boxes = _dev_ptr(boxes, torch.int32, "boxes")
+    if uniform_box is not None:
+        d.uniform_box = (C.c_int32 * 4)(*[int(v) for v in uniform_box])
+    d.flips = _dev_ptr(flips, torch.uint8, "flips")
+    d.dst_h, d.dst_w = int(dst_h), int(dst_w)
+    if out.dtype == torch.float32:
+        d.out_dtype = _capi.TLB_F32
+    elif out.dtype == torch.bfloat16:
+        d.out_dtype = _capi.TLB_BF16
+    else:
+        raise TypeError("out must be float32 or bfloat16")
+    if not out.is_cuda or not out.is_contiguous() or out.numel() != n * 3 * dst_h * dst_w:
+        raise ValueError("out must be a contiguous CUDA tensor of n*3*dst_h*dst_w elements")
+    d.out = out.data_ptr()
+    d.out_layout = _capi.TLB_NHWC if channels_last else _capi.TLB_NCHW
+    d.out_indices = _dev_ptr(out_indices, torch.int64, "out_indices")
+    d.labels_in = _dev_ptr(labels_in, torch.int64, "labels_in")
+    d.labels_out = _dev_ptr(labels_out, torch.int64, "labels_out")
+    d.mean = _capi.f3(mean)
+    d.std = _capi.f3(std)
+    d.normalize_01 = int(bool(normalize_01))
+    d.max_crop_w = int(max_crop_w)
+    d.status = _dev_ptr(status, torch.int32, "status")
+    return d
+
+
+def fused_transform(src, *, stream=None, **kw):
+    """Enqueue one fused batch on ``stream`` (default: torch's current stream); returns
+    immediately.  See ``make_desc`` for the keyword arguments."""
+    import torch
+
+    d = make_desc(src, **kw)
+    st = stream if stream is not None else torch.cuda.current_stream(src.device)
+    with torch.cuda.device(src.device):
+        _capi.check(_capi.load().tlb_fused_transform(C.byref(d), C.c_void_p(st.cuda_stream)))
+    return kw["out"]
+
+
+def fused_plan(desc):
+    vals = [C.c_int32() for _ in range(5)]
+    _capi.check(_capi.load().tlb_fused_plan(C.byref(desc), *[C.byref(v) for v in vals]))
+    keys = ("grid", "block", "smem_bytes", "tile_rows", "tile_cols")
+    return {k: v.value for k, v in zip(keys, vals)}
+
+
+def features() -> dict:
+    """Capability dict in the spirit of ``turboloader.features()``
+    (turboloader_bindings.cpp:1977-2055), honest about what this build contains."""
+    ok = cuda_available()
+    return {
+        "version": _capi.load().tlb_version().decode(),
+        "gpu_transforms": ok,
+        "sm100_fused_transform": ok,
+        "bf16_output": True,
+        "channels_last_output": True,
+        "cpu_fallback": False,
+        "nvjpeg": False,
+        "nvimgcodec": False,
+    }
