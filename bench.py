@@ -1,0 +1,498 @@
+#!/usr/bin/env python
+"""Benchmark of the fused image-transform path (crop + flip + bilinear resize + normalize
+-> 224x224) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A "step" is one pass of the fused transform over one batch of synthetic pre-decoded uint8
+images.  The default workload is the variable-size RandomResizedCrop configuration
+(512 images, H and W uniform in [200, 500], explicit torchvision-style RRC boxes, flips,
+fp32 NCHW 224x224).  Under torchrun every rank transforms batches of its own disjoint
+shard with no collective ("weak" scaling: per-rank work is fixed).
+
+Prints ONE JSON line (rank 0).  ``value`` is images/s over all ranks with inputs resident
+in HBM; ``e2e`` is the same metric through the host-image C-ABI entry point (pinned host
+pixels -> H2D -> kernel -> device batch, status word read back every step); ``roofline``
+compares the kernel's algorithmic bytes per second with the measured HBM copy bandwidth;
+``cpu_baseline`` times the reference's own CPU fused path on this box's host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "img/s (crop+flip+resize+normalize->224)"
+UNIT = "img/s"
+WORKLOADS = ("variable_rrc", "fixed_resize", "resident_epoch", "highres_nhwc", "sharded_scaling")
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s)"
+
+
+def ncu_traffic(workload):
+    """DRAM bytes per launch from the committed ncu capture summary, or None."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            return json.load(f).get(workload)
+    except Exception:
+        return None
+
+
+# ---- workloads -----------------------------------------------------------------------------
+
+def make_host_workload(name, seed, sets):
+    """``sets`` distinct host workloads of the named configuration (full size)."""
+    from turboloader_b200 import synthetic as S
+
+    if name == "variable_rrc":
+        return [S.config2(seed=seed + 17 * i, n=512) for i in range(sets)]
+    if name == "fixed_resize":
+        return [S.config1(seed=seed + 17 * i, n=256) for i in range(sets)]
+    if name == "highres_nhwc":
+        return [S.config4(seed=seed + 17 * i, n=256) for i in range(sets)]
+    raise ValueError(name)
+
+
+class DeviceBatch:
+    """One batch with every table resident on the device, ready to launch repeatedly."""
+
+    def __init__(self, wl, device, src=None, keep=None):
+        import torch
+
+        from turboloader_b200 import _capi
+
+        self.wl = wl
+        self.keep = [] if keep is None else list(keep)
+        dev = device
+        if src is None:
+            src = torch.from_numpy(np.ascontiguousarray(wl.src)).to(dev)
+        self.src = src
+        d = _capi.TransformDesc()
+        d.src = src.data_ptr()
+        d.src_bytes = src.numel()
+        d.n_src = wl.n_src
+        d.n = wl.n
+
+        def up(a, dt):
+            if a is None:
+                return None
+            t = torch.from_numpy(np.ascontiguousarray(a, dtype=dt)).to(dev)
+            self.keep.append(t)
+            return t.data_ptr()
+
+        if wl.uniform_hw is not None:
+            d.src_h, d.src_w = wl.uniform_hw
+        else:
+            d.src_offsets = up(wl.offsets, np.int64)
+            d.src_sizes = up(wl.sizes, np.int32)
+            d.src_w = int(wl.sizes[:, 0].max())
+            d.src_h = int(wl.sizes[:, 1].max())
+        d.sel = up(wl.sel, np.int64)
+        d.boxes = up(wl.boxes, np.int32)
+        d.flips = up(wl.flips, np.uint8)
+        d.dst_h, d.dst_w = wl.dst_h, wl.dst_w
+        tdt = torch.float32 if wl.dtype == "f32" else torch.bfloat16
+        shape = (wl.n, wl.dst_h, wl.dst_w, 3) if wl.channels_last else (wl.n, 3, wl.dst_h, wl.dst_w)
+        self.out = torch.empty(shape, dtype=tdt, device=dev)
+        d.out = self.out.data_ptr()
+        d.out_dtype = _capi.TLB_F32 if wl.dtype == "f32" else _capi.TLB_BF16
+        d.out_layout = _capi.TLB_NHWC if wl.channels_last else _capi.TLB_NCHW
+        if wl.sel is not None:
+            self.idx = torch.empty(wl.n, dtype=torch.int64, device=dev)
+            d.out_indices = self.idx.data_ptr()
+        d.mean = _capi.f3(wl.mean)
+        d.std = _capi.f3(wl.std)
+        d.normalize_01 = int(wl.normalize_01)
+        d.max_crop_w = int(wl.crop_wh()[:, 0].max())
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        d.status = self.status.data_ptr()
+        self.desc = d
+
+    def launch(self, lib, stream_ptr):
+        rc = lib.tlb_fused_transform(C.byref(self.desc), stream_ptr)
+        if rc != 0:
+            raise RuntimeError(lib.tlb_last_error().decode())
+
+
+def make_device_batches(name, seed, device, sets):
+    """Device-resident batches of the named workload (distinct data per set)."""
+    import torch
+
+    from turboloader_b200 import synthetic as S
+
+    if name in ("variable_rrc", "fixed_resize", "highres_nhwc"):
+        return [DeviceBatch(w, device) for w in make_host_workload(name, seed, sets)]
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    if name == "resident_epoch":
+        # 100,000 x 160x160x3 uniform-noise images resident in HBM (7.68 GB); batches of 1024
+        # gathered through default_rng(seed).permutation; centre crop 144 -> 128, bf16 NCHW + indices.
+        n_ds, src, batch = 100_000, 160, 1024
+        data = torch.randint(0, 256, (n_ds, src, src, 3), dtype=torch.uint8, device=device, generator=g)
+        perm = np.random.default_rng(seed).permutation(n_ds).astype(np.int64)
+        flips = (np.random.default_rng([seed, 0, 7]).random(n_ds) < 0.5).astype(np.uint8)
+        out = []
+        for b in range(sets):
+            sel = perm[b * batch:(b + 1) * batch]
+            off = (src - 144) // 2
+            wl = S.Workload("resident_epoch", np.empty(0, np.uint8), np.empty(0, np.int64),
+                            np.tile(np.array([[src, src]], np.int32), (n_ds, 1)), batch, 128, 128, sel=sel,
+                            boxes=np.tile(np.array([[off, off, 144, 144]], np.int32), (batch, 1)),
+                            flips=flips[b * batch:(b + 1) * batch], dtype="bf16", uniform_hw=(src, src))
+            out.append(DeviceBatch(wl, device, src=data.view(-1)))
+        return out
+    if name == "sharded_scaling":
+        # Per-rank batches of 1024 uniform-noise 256x256x3 images, RRC(0.08, 1) boxes, bf16 NCHW.
+        src, batch = 256, 1024
+        out = []
+        for b in range(sets):
+            data = torch.randint(0, 256, (batch, src, src, 3), dtype=torch.uint8, device=device, generator=g)
+            sizes = np.tile(np.array([[src, src]], np.int32), (batch, 1))
+            wl = S.Workload("sharded_scaling", np.empty(0, np.uint8), np.empty(0, np.int64), sizes, batch, 224, 224,
+                            boxes=S.rrc_boxes(sizes, (0.08, 1.0), seed=seed + b),
+                            flips=(np.random.default_rng([seed, b]).random(batch) < 0.5).astype(np.uint8), dtype="bf16",
+                            uniform_hw=(src, src))
+            out.append(DeviceBatch(wl, device, src=data.view(-1)))
+        return out
+    raise ValueError(name)
+
+
+# ---- clocks --------------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the bench runs."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz, self._stop, self._h = [], set(), None, threading.Event(), None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if vis:
+                ids = [v for v in vis.split(",") if v.strip()]
+                if index < len(ids) and ids[index].strip().isdigit():
+                    phys = int(ids[index])
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def sample(self):
+        if self._h is None:
+            return
+        try:
+            self.samples.append(int(self._nv.nvmlDeviceGetClockInfo(self._h, self._nv.NVML_CLOCK_SM)))
+            mask = int(self._nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self.sample()
+            self._stop.wait(0.02)
+
+    def start(self):
+        self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        self._t.join(timeout=1)
+
+    def summary(self):
+        return {"sm_mhz": int(statistics.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---- CPU legs ------------------------------------------------------------------------------
+
+def cpu_reference_pass(wl, flavour, threads):
+    """One pass of the reference's CPU fused path over the batch; returns seconds."""
+    from oracle import oracle as O
+
+    out = np.empty((wl.n, 3, wl.dst_h, wl.dst_w), dtype=np.float32)
+    impl = f"ref-{flavour}" if flavour != "port" else "port"
+    t0 = time.perf_counter()
+    O.fused_batch(wl.src, wl.offsets, wl.sizes, wl.sel, wl.boxes, wl.flips, wl.dst_h, wl.dst_w, wl.mean, wl.std,
+                  wl.normalize_01, impl=impl, threads=threads, out=out)
+    return time.perf_counter() - t0
+
+
+def pick_cpu_flavour():
+    from oracle import oracle as O
+
+    for fl in ("avx2fma", "parity"):
+        if O.ref_available(fl):
+            return fl, "reference"
+    O.build_port()
+    return "port", "port"
+
+
+def cpu_baseline(wl, budget_s=4.0, min_passes=3):
+    from oracle import oracle as O
+
+    flavour, kind = pick_cpu_flavour()
+    threads = O.ref_threads(flavour) if kind == "reference" else 1
+    cpu_reference_pass(wl, flavour, threads)  # warm-up (thread pool start, page faults)
+    times, t_end = [], time.perf_counter() + budget_s
+    while len(times) < min_passes or (time.perf_counter() < t_end and len(times) < 50):
+        times.append(cpu_reference_pass(wl, flavour, threads))
+    med = statistics.median(times)
+    build = {"avx2fma": "-O3 -mavx2 -mfma -funroll-loops (hand-written AVX2 branch)",
+             "parity": "-O2 -mavx2 -ffp-contract=off", "port": "C restatement, -O2, scalar"}[flavour]
+    return {"value": wl.n / med, "unit": UNIT, "cores": threads, "kind": kind,
+            "sample": f"{len(times)} passes over the {wl.n}-image batch of '{wl.name}' (median), build {build}, "
+                      f"host has {os.cpu_count()} logical cores"}
+
+
+# ---- main ----------------------------------------------------------------------------------
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = make_host_workload(args.workload if args.workload in ("variable_rrc", "fixed_resize", "highres_nhwc")
+                            else "variable_rrc", args.seed, 1)[0]
+    from oracle import oracle as O
+
+    flavour, kind = pick_cpu_flavour()
+    threads = O.ref_threads(flavour) if kind == "reference" else 1
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu_reference_pass(wl, flavour, threads)
+    steps = max(1, min(args.steps, 200))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_reference_pass(wl, flavour, threads)
+    dt = time.perf_counter() - t0
+    val = steps * wl.n / dt
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * dt / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl.name, "batch": wl.n, "dst": [wl.dst_h, wl.dst_w],
+                       "note": "reference CPU fused path (resize_bilinear_simd + deinterleave_hwc_to_chw_f32 on its "
+                               "own parallel_for), one host, rank 0 only"},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": kind,
+                             "sample": f"each step = one pass over the {wl.n}-image batch, flavour {flavour}"},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def time_steps(batches, lib, stream, steps, warmup, torch, barrier):
+    sp = C.c_void_p(stream.cuda_stream)
+    for i in range(warmup):
+        batches[i % len(batches)].launch(lib, sp)
+    torch.cuda.synchronize()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for i in range(steps):
+        batches[i % len(batches)].launch(lib, sp)
+    stop.record(stream)
+    torch.cuda.synchronize()
+    barrier()
+    return start.elapsed_time(stop) / 1e3
+
+
+def e2e_steps(wl_sets, lib, stream, steps, warmup, torch, device):
+    """Host images (pinned) -> device batch through tlb_crop_resize_normalize_to_device."""
+    from turboloader_b200 import _capi
+
+    prepared = []
+    for wl in wl_sets:
+        pinned = torch.from_numpy(np.ascontiguousarray(wl.src)).pin_memory()
+        base = pinned.data_ptr()
+        n = wl.n
+        refs = (_capi.ImageRef * n)()
+        crops = (_capi.CropParams * n)()
+        for i in range(n):
+            s = int(wl.sel[i]) if wl.sel is not None else i
+            refs[i].data = base + int(wl.offsets[s])
+            refs[i].w, refs[i].h = int(wl.sizes[s, 0]), int(wl.sizes[s, 1])
+            x, y, w, h = (wl.boxes[i] if wl.boxes is not None else (0, 0, refs[i].w, refs[i].h))
+            crops[i].x, crops[i].y, crops[i].w, crops[i].h = float(x), float(y), float(w), float(h)
+            crops[i].flip = int(wl.flips[i]) if wl.flips is not None else 0
+        tdt = torch.float32 if wl.dtype == "f32" else torch.bfloat16
+        out = torch.empty((n, 3, wl.dst_h, wl.dst_w), dtype=tdt, device=device)
+        prepared.append((wl, pinned, refs, crops, out))
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+    sp = C.c_void_p(stream.cuda_stream)
+
+    def step(i):
+        wl, _, refs, crops, out = prepared[i % len(prepared)]
+        rc = lib.tlb_crop_resize_normalize_to_device(
+            refs, crops, wl.n, wl.dst_h, wl.dst_w, _capi.f3(wl.mean), _capi.f3(wl.std), int(wl.normalize_01),
+            out.data_ptr(), _capi.TLB_F32 if wl.dtype == "f32" else _capi.TLB_BF16,
+            _capi.TLB_NHWC if wl.channels_last else _capi.TLB_NCHW, status.data_ptr(), sp)
+        if rc != 0:
+            raise RuntimeError(lib.tlb_last_error().decode())
+        status_host.copy_(status, non_blocking=True)  # the step's result word comes back to the host
+        stream.synchronize()
+        if int(status_host.item()) != 0:
+            raise RuntimeError("device status word is non-zero")
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record(stream)
+    for i in range(steps):
+        step(i)
+    stop.record(stream)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    dev_s = start.elapsed_time(stop) / 1e3
+    wl = prepared[0][0]
+    wh = wl.crop_wh()
+    h2d = int((((wh[:, 0] * wh[:, 1] * 3) + 15) // 16 * 16).sum()) + wl.n * 33
+    return max(wall, dev_s), h2d, 4
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="variable_rrc", choices=WORKLOADS)
+    ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--sets", type=int, default=2, help="distinct input/output sets cycled through")
+    ap.add_argument("--no-extras", action="store_true", help="skip e2e, CPU baseline and the other workloads")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+
+    from turboloader_b200 import _capi, ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    if not ops.cuda_available():
+        raise SystemExit("bench.py: the C-ABI library did not find an sm_100 device (no fallback exists)")
+    lib = _capi.load()
+    stream = torch.cuda.current_stream()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    # Every rank owns a disjoint shard: its data are generated from a rank-specific seed.
+    seed = args.seed + 100_003 * rank
+    batches = make_device_batches(args.workload, seed, device, args.sets)
+    wl = batches[0].wl
+    launches0 = ops.launch_count()
+    sampler.sample()
+    secs = time_steps(batches, lib, stream, args.steps, args.warmup, torch, barrier)
+    sampler.sample()
+    launches = ops.launch_count() - launches0 - args.warmup
+    for b in batches:
+        if int(b.status.item()) != 0:
+            raise SystemExit("bench.py: device status word is non-zero")
+    t = torch.tensor([secs], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    secs_max = float(t.item())
+    value = world * args.steps * wl.n / secs_max
+
+    rd, wr = wl.algorithmic_bytes()
+    peak, peak_src = measured_peak_gbs()
+    achieved = (rd + wr) / (secs / args.steps) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * secs_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 arithmetic, %s output" % wl.dtype, "data": "synthetic",
+        "config": {"workload": wl.name, "batch_per_gpu": wl.n, "dst": [wl.dst_h, wl.dst_w],
+                   "out": f"{wl.dtype} {'NHWC' if wl.channels_last else 'NCHW'}", "sharding": "disjoint shard per rank, no collective",
+                   "l2": f"per-step traffic {(rd + wr) / 1e6:.0f} MB exceeds the 126 MB L2; {args.sets} distinct "
+                         "input/output sets are cycled"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": ncu_traffic(wl.name), "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": rd + wr, "kernel": "fused_transform_kernel"},
+        "gpu_launches": int(launches),
+    }
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        host_sets = [b.wl for b in batches]
+        if args.workload in ("variable_rrc", "fixed_resize", "highres_nhwc"):
+            e_steps = max(3, min(args.steps, 20))
+            es, h2d, d2h = e2e_steps(host_sets, lib, stream, e_steps, 3, torch, device)
+            line["e2e"] = {"value": e_steps * wl.n / es, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                           "d2h_bytes_per_step": d2h, "steps": e_steps,
+                           "path": "tlb_crop_resize_normalize_to_device: pinned host pixels -> crop pack -> one H2D -> kernel"}
+            line["cpu_baseline"] = cpu_baseline(host_sets[0])
+        others = {}
+        for name in WORKLOADS:
+            if name == args.workload:
+                continue
+            try:
+                del batches
+            except NameError:
+                pass
+            torch.cuda.empty_cache()
+            batches = make_device_batches(name, seed, device, 2)
+            s = time_steps(batches, lib, stream, 50, 5, torch, barrier)
+            r, w = batches[0].wl.algorithmic_bytes()
+            others[name] = {"img_per_s": 50 * batches[0].wl.n / s, "GB_per_s": (r + w) / (s / 50) / 1e9,
+                            "frac_of_peak": (r + w) / (s / 50) / 1e9 / peak, "batch": batches[0].wl.n}
+        line["other_workloads"] = others
+    elif world > 1:
+        # Multi-GPU: e2e at N GPUs = every rank feeding its own GPU from its own pinned host shard.
+        if args.workload in ("variable_rrc", "fixed_resize", "highres_nhwc") and not args.no_extras:
+            host_sets = make_host_workload(args.workload, seed, 1)
+            e_steps = max(3, min(args.steps, 10))
+            barrier()
+            es, h2d, d2h = e2e_steps(host_sets, lib, stream, e_steps, 3, torch, device)
+            te = torch.tensor([es], dtype=torch.float64, device=device)
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            line["e2e"] = {"value": world * e_steps * wl.n / float(te.item()), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                           "d2h_bytes_per_step": d2h, "steps": e_steps}
+    sampler.stop()
+    line["clocks"] = sampler.summary()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -41,7 +41,7 @@ def run_gpu(wl: Workload, *, host_params=False, device_tables=True, status=True,
     tdtype = torch.float32 if wl.dtype == "f32" else torch.bfloat16
     shape = (n, wl.dst_h, wl.dst_w, 3) if wl.channels_last else (n, 3, wl.dst_h, wl.dst_w)
     guard = 64
-    flat = torch.full((int(np.prod(shape)) + 2 * guard,), -777.0, dtype=tdtype, device=dev)
+    flat = torch.full((int(np.prod(shape)) + 2 * guard,), -512.0, dtype=tdtype, device=dev)
     out = flat[guard:guard + int(np.prod(shape))].view(shape)
     keep = [raw, flat]
     d = _capi.TransformDesc()
@@ -103,7 +103,7 @@ def run_gpu(wl: Workload, *, host_params=False, device_tables=True, status=True,
     res = {"status": int(st.item()) if st is not None else None}
     g0 = flat[:guard].float().cpu().numpy()
     g1 = flat[guard + int(np.prod(shape)):].float().cpu().numpy()
-    assert (g0 == -777.0).all() and (g1 == -777.0).all(), "guard band around the output was overwritten"
+    assert (g0 == -512.0).all() and (g1 == -512.0).all(), "guard band around the output was overwritten"
     if wl.dtype == "f32":
         res["out"] = out.cpu().numpy()
     else:

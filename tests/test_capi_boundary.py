@@ -1,0 +1,119 @@
+"""The C-ABI library loads without a GPU, exports every symbol the header declares, and
+rejects bad arguments on the host before any CUDA call."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from turboloader_b200 import _capi, ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "turboloader_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"TLB_API\s+[\w\s\*]+?\b(tlb_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported():
+    lib = _capi.load()
+    names = _declared_symbols()
+    assert len(names) >= 16
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+
+
+def test_struct_layout_matches_header_order():
+    text = open(os.path.join(ROOT, "include", "turboloader_b200.h")).read()
+    start = text.index("typedef struct tlb_transform_desc {") + len("typedef struct tlb_transform_desc {")
+    body = text[start:text.index("} tlb_transform_desc;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        for part in decl.split(","):
+            m = re.search(r"(\w+)\s*(\[\d+\])?\s*$", part.strip())
+            fields.append(m.group(1))
+    assert fields == [f[0] for f in _capi.TransformDesc._fields_]
+
+
+def _desc(**kw):
+    d = _capi.TransformDesc()
+    d.src = 0x1000
+    d.src_bytes = 1 << 20
+    d.n_src = 4
+    d.src_w, d.src_h = 32, 32
+    d.n = 4
+    d.dst_h, d.dst_w = 16, 16
+    d.out = 0x2000
+    d.mean = _capi.f3((0, 0, 0))
+    d.std = _capi.f3((1, 1, 1))
+    for k, v in kw.items():
+        setattr(d, k, v)
+    return d
+
+
+def test_plan_is_computed_without_a_gpu():
+    plan = ops.fused_plan(_desc(dst_h=224, dst_w=224, src_w=256, src_h=256, n=256, n_src=256))
+    assert plan["block"] == 256 and plan["tile_cols"] == 224 and plan["smem_bytes"] <= 227 * 1024
+    assert plan["grid"] == 256 * -(-224 // plan["tile_rows"])
+    wide = ops.fused_plan(_desc(dst_h=8, dst_w=600, src_w=700, src_h=60))
+    assert wide["tile_cols"] <= 256 and wide["tile_cols"] % 16 == 0
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(dst_h=0), 1), (dict(out_dtype=7), 1), (dict(out_layout=3), 1), (dict(src=None), 1), (dict(n_src=0), 1),
+    (dict(std=_capi.f3((1, 0, 1))), 1), (dict(n=9), 3), (dict(uniform_box=(C.c_int32 * 4)(30, 0, 8, 8)), 2),
+    (dict(src_w=0, src_h=0), 1),
+])
+def test_invalid_descriptors_are_rejected_on_the_host(kw, code):
+    lib = _capi.load()
+    rc = lib.tlb_fused_transform(C.byref(_desc(**kw)), None)
+    assert rc == code
+    assert lib.tlb_last_error()
+
+
+def test_host_params_validation_names_the_sample():
+    lib = _capi.load()
+    sel = np.array([0, 1, 4, 2], dtype=np.int64)
+    d = _desc(sel=sel.ctypes.data)
+    assert lib.tlb_fused_transform_host_params(C.byref(d), None) == 3
+    assert b"sample 2" in lib.tlb_last_error()
+    boxes = np.array([[0, 0, 32, 32], [1, 0, 32, 32], [0, 0, 1, 1], [0, 0, 1, 1]], dtype=np.int32)
+    d = _desc(boxes=boxes.ctypes.data)
+    assert lib.tlb_fused_transform_host_params(C.byref(d), None) == 2
+    assert b"sample 1" in lib.tlb_last_error()
+
+
+def test_empty_batch_is_a_no_op():
+    assert _capi.load().tlb_fused_transform(C.byref(_desc(n=0)), None) == 0
+
+
+def test_host_image_forms_validate_before_touching_cuda():
+    lib = _capi.load()
+    img = np.zeros((8, 8, 3), dtype=np.uint8)
+    refs = (_capi.ImageRef * 1)()
+    refs[0].data, refs[0].w, refs[0].h = img.ctypes.data, 8, 8
+    out = np.zeros((1, 3, 4, 4), dtype=np.float32)
+    crops = (_capi.CropParams * 1)()
+    crops[0].x, crops[0].y, crops[0].w, crops[0].h = 0.5, 0, 4, 4
+    m, s = _capi.f3((0, 0, 0)), _capi.f3((1, 1, 1))
+    if not ops.cuda_available():
+        pytest.skip("host-image forms look up the current device first")
+    assert lib.tlb_crop_resize_normalize_batch(refs, crops, 1, 4, 4, m, s, out.ctypes.data) == 1
+
+
+def test_no_gpu_means_unavailable_not_fallback():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    assert ops.cuda_available() is False
+    assert ops.cuda_device_name() == ""
+    assert ops.features()["cpu_fallback"] is False
+    with pytest.raises(RuntimeError):
+        ops.cuda_resize_normalize([np.zeros((4, 4, 3), np.uint8)], 2, 2)

@@ -1,0 +1,183 @@
+"""GPU tests of the reference-facing surface: the pointer-returning resident operators, the
+host-image operators, the host-to-device streaming entry point and CudaResidentLoader."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import turboloader_b200 as t
+from oracle import oracle as O
+from turboloader_b200 import _capi
+from turboloader_b200 import synthetic as S
+
+from helpers import check_bf16, expected
+
+pytestmark = pytest.mark.gpu
+MEAN, STD = t.IMAGENET_MEAN, t.IMAGENET_STD
+
+
+def _dataset(n=40, hw=24, seed=0):
+    return np.random.RandomState(seed).randint(0, 256, size=(n, hw, hw, 3), dtype=np.uint8)
+
+
+def _oracle_uniform(data, sel=None, box=None, flips=None, dst=None, mean=MEAN, std=STD):
+    n, h, w, _ = data.shape
+    flat, offsets, sizes = S.uniform_dataset(data)
+    m = len(sel) if sel is not None else n
+    boxes = None if box is None else np.tile(np.array([box], np.int32), (m, 1))
+    dh, dw = dst if dst else ((box[3], box[2]) if box else (h, w))
+    return O.fused_batch(flat, offsets, sizes, sel, boxes, flips, dh, dw, mean, std, True)
+
+
+def test_normalize_resident_and_gather_pointer_forms():
+    import torch
+    data = _dataset()
+    gpu = torch.from_numpy(data).cuda()
+    ptr = t.cuda_normalize_resident(gpu.data_ptr(), 40, 24, 24, mean=MEAN, std=STD)
+    got = torch.as_tensor(t._CudaArray(ptr, (40, 3, 24, 24)), device="cuda").cpu().numpy()
+    assert np.array_equal(got, _oracle_uniform(data))
+    # numpy formula within 1e-5 (reference tests/test_tbl_raw.py:228-240 compares GPU and CPU serve)
+    want = ((data.astype(np.float32) / 255 - np.array(MEAN, np.float32)) / np.array(STD, np.float32)).transpose(0, 3, 1, 2)
+    assert np.abs(got - want).max() < 1e-5
+    sel = torch.from_numpy(np.array([5, 0, 39, 5, 17], dtype=np.int64)).cuda()
+    ptr2 = t.cuda_normalize_resident_gather(gpu.data_ptr(), sel.data_ptr(), 5, 24, 24)
+    got2 = torch.as_tensor(t._CudaArray(ptr2, (5, 3, 24, 24)), device="cuda").cpu().numpy()
+    assert np.array_equal(got2, _oracle_uniform(data, sel=sel.cpu().numpy()))
+
+
+def test_pointer_ring_is_four_deep():
+    import torch
+    gpu = torch.from_numpy(_dataset(8, 16)).cuda()
+    ptrs = [t.cuda_normalize_resident(gpu.data_ptr(), 8, 16, 16) for _ in range(5)]
+    assert len(set(ptrs[:4])) == 4 and ptrs[4] == ptrs[0]
+    with pytest.raises(RuntimeError):
+        t.cuda_normalize_resident(0, 8, 16, 16)
+
+
+def test_host_image_operators():
+    rs = np.random.RandomState(3)
+    images = [rs.randint(0, 256, size=(h, w, 3), dtype=np.uint8) for h, w in [(50, 70), (33, 20), (64, 64), (9, 200)]]
+    flat, offsets, sizes = S.pack_images(images)
+    got = t.cuda_resize_normalize(images, 32, 48)
+    want = O.fused_batch(flat, offsets, sizes, None, None, None, 32, 48, MEAN, STD, True)
+    assert got.shape == (4, 3, 32, 48) and np.array_equal(got, want)
+    crops = np.array([[3, 4, 40, 30], [0, 0, 20, 33], [10, 10, 54, 54], [100, 2, 90, 7]], dtype=np.float32)
+    flips = np.array([1, 0, 1, 0], dtype=np.int32)
+    got = t.cuda_crop_resize_normalize(images, crops, flips, 32, 48)
+    want = O.fused_batch(flat, offsets, sizes, None, crops.astype(np.int32), flips.astype(np.uint8), 32, 48, MEAN, STD, True)
+    assert np.array_equal(got, want)
+    with pytest.raises(RuntimeError):
+        t.cuda_resize_normalize([], 8, 8)
+    with pytest.raises(RuntimeError):
+        t.cuda_crop_resize_normalize(images, crops[:3], flips, 8, 8)
+    bad = crops.copy()
+    bad[1] = (5, 0, 20, 33)
+    with pytest.raises(_capi.TurboLoaderB200Error) as e:
+        t.cuda_crop_resize_normalize(images, bad, flips, 8, 8)
+    assert e.value.code == 2
+    frac = crops.copy()
+    frac[0, 0] = 3.5
+    with pytest.raises(_capi.TurboLoaderB200Error):
+        t.cuda_crop_resize_normalize(images, frac, flips, 8, 8)
+
+
+def test_host_to_device_streaming_entry():
+    import torch
+    wl = S.config2(seed=21, n=10, lo=50, hi=120, dst=64)
+    wl.dtype = "bf16"
+    lib = _capi.load()
+    refs = (_capi.ImageRef * wl.n)()
+    crops = (_capi.CropParams * wl.n)()
+    for i in range(wl.n):
+        refs[i].data = wl.src.ctypes.data + int(wl.offsets[i])
+        refs[i].w, refs[i].h = int(wl.sizes[i, 0]), int(wl.sizes[i, 1])
+        crops[i].x, crops[i].y, crops[i].w, crops[i].h = (float(v) for v in wl.boxes[i])
+        crops[i].flip = int(wl.flips[i])
+    out = torch.empty((wl.n, 3, 64, 64), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(3):  # exercises the two-deep staging ring
+        rc = lib.tlb_crop_resize_normalize_to_device(refs, crops, wl.n, 64, 64, _capi.f3(wl.mean), _capi.f3(wl.std), 1,
+                                                     out.data_ptr(), _capi.TLB_BF16, _capi.TLB_NCHW, status.data_ptr(),
+                                                     C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0, lib.tlb_last_error()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert check_bf16(out.view(torch.int16).cpu().numpy().view(np.uint16), expected(wl)) == 0
+
+
+def test_resident_loader_reference_contract():
+    import torch
+    data = _dataset(50, 20, seed=4)
+    ld = t.CudaResidentLoader.from_array(data, batch_size=16, shuffle=True, seed=42, return_indices=True)
+    assert len(ld) == 3
+    perm = np.random.default_rng(42).permutation(50)
+    seen = []
+    for b, (batch, idx) in enumerate(ld):
+        x = torch.as_tensor(batch, device="cuda")
+        assert x.shape == (16, 3, 20, 20) and x.dtype == torch.float32
+        idx = idx.cpu().numpy()
+        assert np.array_equal(idx, perm[b * 16:(b + 1) * 16])
+        assert np.array_equal(x.cpu().numpy(), _oracle_uniform(data, sel=idx))
+        seen.append(idx)
+    assert len(seen) == 3
+    ld.set_epoch(1)
+    first = next(iter(ld))[1].cpu().numpy()
+    assert np.array_equal(first, np.random.default_rng(43).permutation(50)[:16])
+    # sequential, ragged tail kept, numpy arange indices (turboloader/cuda_loader.py:528-533)
+    ld2 = t.CudaResidentLoader.from_array(data, batch_size=16, drop_last=False, return_indices=True)
+    got = list(ld2)
+    assert len(got) == 4 and len(got[-1][0]) == 2
+    assert np.array_equal(got[-1][1], np.arange(48, 50))
+    assert np.array_equal(torch.as_tensor(got[1][0], device="cuda").cpu().numpy(), _oracle_uniform(data[16:32]))
+    assert ld.device_status() == 0 and ld2.device_status() == 0
+
+
+def test_resident_loader_crop_flip_bf16_channels_last_labels_and_resume():
+    import torch
+    data = _dataset(64, 40, seed=5)
+    labels = np.arange(64) * 3 + 1
+    kw = dict(batch_size=8, shuffle=True, seed=7, return_indices=True, crop_size=36, output_size=32, hflip_prob=0.5,
+              dtype=torch.bfloat16, channels_last=True, labels=labels)
+    ld = t.CudaResidentLoader.from_array(data, **kw)
+    order, flips = ld.epoch_order(), ld.epoch_flips()
+    assert flips.sum() not in (0, 64)
+    batches = []
+    for b, (x, y, idx) in enumerate(ld):
+        assert x.shape == (8, 3, 32, 32) and x.is_contiguous(memory_format=torch.channels_last)
+        idx = idx.cpu().numpy()
+        assert np.array_equal(idx, order[b * 8:(b + 1) * 8])
+        assert np.array_equal(y.cpu().numpy(), labels[idx])
+        ref = _oracle_uniform(data, sel=idx, box=(2, 2, 36, 36), flips=flips[b * 8:(b + 1) * 8], dst=(32, 32))
+        got = x.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)  # logical NCHW order
+        assert check_bf16(got, O.bf16_bits(ref)) == 0
+        batches.append(got.copy())
+        if b == 2:
+            state = ld.state_dict()
+    assert state == {"version": 1, "epoch": 0, "batches_served": 3}
+    ld2 = t.CudaResidentLoader.from_array(data, **kw)
+    ld2.load_state_dict(state)
+    rest = [x.contiguous().view(torch.int16).cpu().numpy().view(np.uint16) for x, _, _ in ld2]
+    assert len(rest) == 5
+    for a, b in zip(rest, batches[3:]):
+        assert np.array_equal(a, b)
+
+
+def test_resident_loader_explicit_boxes():
+    import torch
+    data = _dataset(20, 48, seed=6)
+
+    def boxes(epoch, order):
+        rs = np.random.RandomState(epoch)
+        w = rs.randint(8, 49, size=len(order))
+        h = rs.randint(8, 49, size=len(order))
+        return np.stack([rs.randint(0, 48 - w + 1), rs.randint(0, 48 - h + 1), w, h], axis=1)
+
+    ld = t.CudaResidentLoader.from_array(data, batch_size=10, shuffle=True, boxes=boxes, output_size=24, hflip_prob=0.3,
+                                         return_indices=True, as_tensor=True)
+    bx = boxes(0, ld.epoch_order()).astype(np.int32)
+    fl = ld.epoch_flips()
+    flat, offsets, sizes = S.uniform_dataset(data)
+    for b, (x, idx) in enumerate(ld):
+        want = O.fused_batch(flat, offsets, sizes, idx.cpu().numpy(), bx[b * 10:(b + 1) * 10], fl[b * 10:(b + 1) * 10], 24, 24,
+                             MEAN, STD, True)
+        assert np.array_equal(x.cpu().numpy(), want)

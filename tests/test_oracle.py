@@ -1,0 +1,107 @@
+"""The CPU oracle (C restatement in oracle/fused_ref.c) against the golden vectors generated
+from the reference's own headers, and against the compiled reference when it is present."""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+from golden.make_golden import FUSED_HASHED, FUSED_SMALL, MEAN, RESIZE_CASES, STD, fused_case, rs_image
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _run(c, impl, mean=MEAN, std=STD, n01=True):
+    return O.fused_batch(c["src"], c["offsets"], c["sizes"], c["sel"], c["boxes"], c["flips"], c["dst_h"], c["dst_w"],
+                         mean, std, n01, impl=impl)
+
+
+def test_resize_matches_reference_hashes():
+    gold = json.load(open(os.path.join(GOLD, "resize_cases.json")))
+    for i, (sw, sh, dw, dh) in enumerate(RESIZE_CASES):
+        rec = gold[f"{sw}x{sh}->{dw}x{dh}"]
+        res = O.resize_bilinear_u8(rs_image(rec["seed"], sh, sw), dh, dw, impl="port")
+        assert hashlib.sha256(res.tobytes()).hexdigest() == rec["sha256"], (sw, sh, dw, dh)
+
+
+def test_fused_small_bit_exact():
+    gold = np.load(os.path.join(GOLD, "fused_small.npz"))
+    for j, spec in enumerate(FUSED_SMALL):
+        c = fused_case(**spec)
+        assert np.array_equal(_run(c, "port").view(np.uint32), gold[f"case{j}_out01"].view(np.uint32))
+        got255 = _run(c, "port", tuple(m * 255 for m in MEAN), tuple(s * 255 for s in STD), False)
+        assert np.array_equal(got255.view(np.uint32), gold[f"case{j}_out255"].view(np.uint32))
+
+
+def test_fused_config_shapes_match_reference_hashes():
+    gold = json.load(open(os.path.join(GOLD, "fused_hashes.json")))
+    for spec in FUSED_HASHED:
+        got = _run(fused_case(**spec), "port")
+        assert hashlib.sha256(got.tobytes()).hexdigest() == gold[json.dumps(spec, sort_keys=True)]
+
+
+def test_normalize_formula():
+    # (x/255 - mean)/std within 1e-5 (reference tests/test_tbl_raw.py:186-193).
+    rs = np.random.RandomState(5)
+    img = rs.randint(0, 256, size=(4, 16, 16, 3), dtype=np.uint8)
+    off = np.arange(4, dtype=np.int64) * 16 * 16 * 3
+    sizes = np.full((4, 2), 16, dtype=np.int32)
+    got = O.fused_batch(img.reshape(-1), off, sizes, None, None, None, 16, 16, MEAN, STD, True)
+    want = (img.astype(np.float32) / 255.0 - np.array(MEAN, np.float32)) / np.array(STD, np.float32)
+    assert np.abs(got - want.transpose(0, 3, 1, 2)).max() < 1e-5
+
+
+def test_gather_equals_take_then_batch():
+    # reference tests/test_tbl_raw.py:266-275
+    rs = np.random.RandomState(6)
+    img = rs.randint(0, 256, size=(10, 8, 8, 3), dtype=np.uint8)
+    off = np.arange(10, dtype=np.int64) * 8 * 8 * 3
+    sizes = np.full((10, 2), 8, dtype=np.int32)
+    sel = np.array([9, 0, 3, 3, 7], dtype=np.int64)
+    a = O.fused_batch(img.reshape(-1), off, sizes, sel, None, None, 8, 8, MEAN, STD, True)
+    taken = np.ascontiguousarray(img[sel])
+    b = O.fused_batch(taken.reshape(-1), off[:5], sizes[:5], None, None, None, 8, 8, MEAN, STD, True)
+    assert np.array_equal(a, b)
+
+
+def test_out_of_range_index_and_box_raise():
+    # reference tests/test_tbl_raw.py:277-283
+    img = np.zeros((2, 4, 4, 3), dtype=np.uint8)
+    off = np.arange(2, dtype=np.int64) * 48
+    sizes = np.full((2, 2), 4, dtype=np.int32)
+    with pytest.raises(IndexError):
+        O.fused_batch(img.reshape(-1), off, sizes, np.array([2], dtype=np.int64), None, None, 4, 4, MEAN, STD)
+    with pytest.raises(IndexError):
+        O.fused_batch(img.reshape(-1), off, sizes, None, np.array([[0, 0, 4, 4], [1, 0, 4, 4]], dtype=np.int32), None, 4, 4,
+                      MEAN, STD)
+
+
+def test_flip_direction_and_identity():
+    # Same-size crop is the identity; the flip mirrors the resized image (tests/test_train_aug.py:106-110).
+    img = np.arange(2 * 3 * 3, dtype=np.uint8).reshape(1, 2, 3, 3)
+    off = np.zeros(1, dtype=np.int64)
+    sizes = np.array([[3, 2]], dtype=np.int32)
+    plain = O.fused_batch(img.reshape(-1), off, sizes, None, None, np.array([0], np.uint8), 2, 3, (0, 0, 0), (1, 1, 1), False)
+    flip = O.fused_batch(img.reshape(-1), off, sizes, None, None, np.array([1], np.uint8), 2, 3, (0, 0, 0), (1, 1, 1), False)
+    assert np.array_equal(plain[0].transpose(1, 2, 0), img[0].astype(np.float32))
+    assert np.array_equal(flip[0], plain[0][:, :, ::-1])
+
+
+def test_bf16_rounding_is_nearest_even():
+    x = np.array([1.0, 1.00390625, 1.005859375, -2.0078125, 3.4e38, 1e-40, 0.0], dtype=np.float32)
+    import torch
+    want = torch.from_numpy(x).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(O.bf16_bits(x), want)
+
+
+@pytest.mark.skipif(not O.ref_available("parity"), reason="compiled reference harness not present")
+def test_port_equals_compiled_reference():
+    for spec in FUSED_SMALL + FUSED_HASHED:
+        c = fused_case(**spec)
+        assert np.array_equal(_run(c, "port").view(np.uint32), _run(c, "ref-parity").view(np.uint32))
+    for i, (sw, sh, dw, dh) in enumerate(RESIZE_CASES):
+        img = rs_image(77 + i, sh, sw)
+        assert np.array_equal(O.resize_bilinear_u8(img, dh, dw, "port"), O.resize_bilinear_u8(img, dh, dw, "ref-parity"))
