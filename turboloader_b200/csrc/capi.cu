@@ -64,7 +64,8 @@ struct Buffer {
 
 struct DeviceState {
     std::mutex mu;
-    bool prepared = false;
+    std::mutex prep_mu;  // separate from mu: the resident forms hold mu while they launch
+    std::atomic<bool> prepared{false};
     Buffer params[4];  // ring for host-supplied per-sample tables
     int params_next = 0;
     Buffer images[2];  // ring for host-image batches (pixels + tables)
@@ -88,12 +89,12 @@ int current_device(int* dev) {
 }
 
 int ensure_prepared(DeviceState& st) {
-    if (st.prepared) return TLB_OK;
-    std::lock_guard<std::mutex> lk(st.mu);
-    if (st.prepared) return TLB_OK;
+    if (st.prepared.load(std::memory_order_acquire)) return TLB_OK;
+    std::lock_guard<std::mutex> lk(st.prep_mu);
+    if (st.prepared.load(std::memory_order_acquire)) return TLB_OK;
     cudaError_t e = static_cast<cudaError_t>(tlb::prepare_device());
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
-    st.prepared = true;
+    st.prepared.store(true, std::memory_order_release);
     return TLB_OK;
 }
 
@@ -123,23 +124,27 @@ int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl) {
     pl.n_col_tiles = (W + tlb::kMaxTileCols - 1) / tlb::kMaxTileCols;
     pl.tile_cols = std::min(tlb::kMaxTileCols, round_up((W + pl.n_col_tiles - 1) / pl.n_col_tiles, 16));
     pl.n_col_tiles = (W + pl.tile_cols - 1) / pl.tile_cols;
-    pl.tile_rows = std::clamp(env_int("TLB_TILE_ROWS", 16), 1, 1 << 20);
+    pl.threads = (tlb::kMaxThreads / pl.tile_cols) * pl.tile_cols;  // every thread owns one column
+    pl.tile_rows = std::clamp(env_int("TLB_TILE_ROWS", 32), 1, 1 << 20);
     pl.tile_rows = std::min(pl.tile_rows, H);
     pl.n_row_tiles = (H + pl.tile_rows - 1) / pl.tile_rows;
-    // Widest source footprint of one column tile (crop-local columns).
+    // Widest source footprint of one column tile (crop-local columns) -> worst-case row pitch.
     long long fw = std::min<long long>(max_crop_w, (static_cast<long long>(pl.tile_cols) * max_crop_w + W - 1) / W + 3);
     pl.pitch = round_up(static_cast<int>(fw) * 3 + 30, 16);
     pl.hpitch = 3 * pl.tile_cols;
-    const int per_row = pl.pitch + pl.hpitch * 4;
-    const int budget = std::clamp(env_int("TLB_SMEM_BUDGET", 48 * 1024), 8 * 1024, 200 * 1024);
-    int R = env_int("TLB_STAGED_ROWS", 0);
-    if (R <= 0) R = budget / per_row;
-    R = std::clamp(R, 2, tlb::kMaxStagedRows);
-    pl.staged_rows = R;
-    pl.smem_bytes = tlb::smem_layout(pl.tile_cols, R, pl.pitch, pl.hpitch).total;
-    if (pl.smem_bytes > 227 * 1024)
-        return fail(TLB_ERR_TOO_WIDE, "crop width %d needs %d bytes of shared memory per CTA (limit 232448)",
-                    max_crop_w, pl.smem_bytes);
+    // Shared memory: a CTA stages R = var / (2*own_pitch + hpitch*4) source rows per pass, using
+    // its own (usually narrower) footprint pitch.  Give the widest crop at least kMinRows rows.
+    constexpr int kMinRows = 6;
+    const int per_row_worst = 2 * pl.pitch + pl.hpitch * 4;
+    const int budget = std::clamp(env_int("TLB_SMEM_BUDGET", 56 * 1024), 8 * 1024, 226 * 1024);
+    int var = std::max(budget - tlb::kSmemVar, kMinRows * per_row_worst);
+    var = std::min(var, tlb::kMaxStagedRows * per_row_worst);
+    pl.smem_bytes = tlb::kSmemVar + var;
+    if (pl.smem_bytes > 227 * 1024) {
+        pl.smem_bytes = 227 * 1024;
+        if (tlb::staged_rows_for(pl.smem_bytes - tlb::kSmemVar, pl.pitch, pl.hpitch) < 2)
+            return fail(TLB_ERR_TOO_WIDE, "crop width %d does not fit the shared-memory staging buffers", max_crop_w);
+    }
     const bool base_ok = (reinterpret_cast<uintptr_t>(d.out) & 15u) == 0;
     if (d.out_layout == TLB_NCHW)
         pl.vec_ok = base_ok && (W % V == 0);
@@ -639,7 +644,7 @@ int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block
     tlb::Plan pl{};
     if (int rc = make_plan(*desc, mcw, pl)) return rc;
     if (grid) *grid = static_cast<int32_t>(pl.grid);
-    if (block) *block = tlb::kThreads;
+    if (block) *block = pl.threads;
     if (smem_bytes) *smem_bytes = pl.smem_bytes;
     if (tile_rows) *tile_rows = pl.tile_rows;
     if (tile_cols) *tile_cols = pl.tile_cols;

@@ -5,9 +5,9 @@
 
 namespace tlb {
 
-constexpr int kThreads = 256;      // threads per CTA
+constexpr int kMaxThreads = 256;   // threads per CTA = (256 / tile_cols) * tile_cols
 constexpr int kMaxStagedRows = 32; // one lane of warp 0 issues the copy of one staged row
-constexpr int kMaxTileCols = 256;  // output columns per CTA (== kThreads: one column per thread)
+constexpr int kMaxTileCols = 256;  // output columns per CTA
 
 // Launch geometry chosen on the host from sizes only (never from device data).
 struct Plan {
@@ -15,8 +15,8 @@ struct Plan {
     int tile_cols;    // output columns per CTA (multiple of 16, <= kMaxTileCols)
     int n_col_tiles;  // ceil(dst_w / tile_cols)
     int n_row_tiles;  // ceil(dst_h / tile_rows)
-    int staged_rows;  // source rows staged in shared memory per pass (R), <= kMaxStagedRows
-    int pitch;        // bytes per staged raw row (multiple of 16)
+    int threads;      // CTA size, a multiple of tile_cols
+    int pitch;        // bytes per staged raw row at the widest crop (multiple of 16)
     int hpitch;       // floats per row of horizontally-interpolated values (3 * tile_cols)
     int smem_bytes;   // dynamic shared memory per CTA
     int vec_ok;       // 1: every 16-byte output chunk is aligned and whole -> vector stores
@@ -47,29 +47,19 @@ struct FusedParams {
     Plan plan;
 };
 
-// Shared-memory layout (byte offsets from the dynamic shared base), derived from the plan.
-struct SmemLayout {
-    int mbar;   // 16 B
-    int colp;   // tile_cols * 16 B   per-column {off0, off1, dx, 1-dx}
-    int rowp;   // 32 * 16 B          per-row    {slot0, slot1, dy, 1-dy}
-    int rowsh;  // 32 * 4 B           byte phase of each staged row inside its slot
-    int ctab;   // 48 * 4 B           NHWC normalize constants by channel phase
-    int raw;    // staged_rows * pitch
-    int hbuf;   // staged_rows * hpitch * 4
-    int total;
-};
+// Shared-memory layout.  A fixed header is followed by a region the CTA carves up itself
+// from its own footprint width: two raw staging buffers of R rows (double buffering) and
+// one fp32 buffer of R horizontally-interpolated rows, with
+//   R = min(kMaxStagedRows, variable_bytes / (2 * own_pitch + hpitch * 4)).
+constexpr int kSmemMbar = 0;      // 2 x 8 B mbarriers
+constexpr int kSmemMeta = 16;     // 2 x int4 {rows of the pass, staged rows, -, -}
+constexpr int kSmemRowp = 48;     // 2 x 32 x float4 {h offset of y0 row, of y1 row, dy, 1-dy}
+constexpr int kSmemRowOff = 48 + 1024;        // 2 x 32 x int: byte offset of each staged row's first pixel
+constexpr int kSmemVar = 48 + 1024 + 256 + 80;  // = 1408, start of the carved region (128-byte multiple)
 
-inline __host__ __device__ SmemLayout smem_layout(int tile_cols, int staged_rows, int pitch, int hpitch) {
-    SmemLayout L;
-    L.mbar = 0;
-    L.colp = 16;
-    L.rowp = L.colp + tile_cols * 16;
-    L.rowsh = L.rowp + 32 * 16;
-    L.ctab = L.rowsh + 32 * 4;
-    L.raw = L.ctab + 48 * 4;
-    L.hbuf = L.raw + staged_rows * pitch;
-    L.total = L.hbuf + staged_rows * hpitch * 4;
-    return L;
+inline __host__ __device__ int staged_rows_for(int var_bytes, int own_pitch, int hpitch) {
+    int r = var_bytes / (2 * own_pitch + hpitch * 4);
+    return r > kMaxStagedRows ? kMaxStagedRows : r;
 }
 
 // Implemented in fused_transform.cu.  Returns a cudaError_t as int.

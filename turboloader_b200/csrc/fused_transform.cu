@@ -13,20 +13,26 @@
 // Every multiply and add is a separately rounded fp32 operation (no FMA contraction),
 // in the CPU path's order, so fp32 output is bit-identical to it.
 //
-// Structure of one CTA (256 threads) = one tile of `tile_rows` x `tile_cols` outputs of
-// one sample, processed in passes of at most R staged source rows:
-//   1. warp 0 works out which source rows the pass needs (one lane per output row, the
-//      first/last row exchanged with warp shuffles) and issues one 1-D bulk async copy
-//      (cp.async.bulk, global -> this CTA's shared memory, completion on an mbarrier)
-//      per source row, each rounded out to 16-byte boundaries.  Bytes that cannot be
-//      reached on a 16-byte grid inside the readable region are fetched with plain loads.
+// Structure of one CTA = one tile of `tile_rows` x `tile_cols` outputs of one sample,
+// processed in passes of at most R staged source rows (R is what fits in shared memory
+// for this tile's own footprint width):
+//   1. warp 0 plans the pass: one lane per output row computes (y0, y1, dy); the first and
+//      last rows are exchanged with warp shuffles to find the contiguous range of source
+//      rows (or, for a >2x vertical downscale, the exact (y0, y1) pairs).  It then issues
+//      one 1-D bulk async copy (cp.async.bulk, global -> this CTA's shared memory,
+//      completion on an mbarrier) per source row, each rounded out to 16-byte boundaries.
+//      Bytes that cannot be reached on a 16-byte grid inside the readable region are
+//      fetched with plain loads.  Raw rows are double buffered: the copies of pass i+1
+//      are in flight while pass i is computed.
 //   2. "H" phase: every staged row is interpolated horizontally once,
-//      h = p[x0]*(1-dx) + p[x1]*dx, into fp32 in shared memory.  Column weights are
-//      computed once per tile (one column per thread) and kept in shared memory.
-//   3. "V" phase: each thread produces one 16-byte output chunk at a time:
-//      v = h[y0]*(1-dy) + h[y1]*dy, truncate, normalize, cast, one 16-byte store.
-//      The layout of h in shared memory (planar for NCHW, interleaved for NHWC) makes
-//      the inputs of a chunk two 16-byte shared loads per source row.
+//      h = p[x0]*(1-dx) + p[x1]*dx, into fp32 in shared memory.  Each thread owns one
+//      output column for the whole tile and keeps its weights in registers.
+//   3. "V" phase: each thread owns a group of 4 (fp32) or 8 (bf16) adjacent pixels and
+//      walks down the rows of the pass: v = h[y0]*(1-dy) + h[y1]*dy, truncate, normalize,
+//      cast, three 16-byte stores per row.  The layout of h in shared memory (planar for
+//      NCHW, interleaved for NHWC) makes every input a 16-byte shared load.  The fp32
+//      arithmetic uses the packed two-lane forms (mul/add .f32x2) of sm_100; they round
+//      each lane exactly like the scalar instructions.
 // The bilinear blend is exactly separable in this order (top and bot depend on one
 // source row each), so sharing h between neighbouring output rows changes no bit.
 //
@@ -68,10 +74,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t mbar, uint32_t parity
         : "memory");
     return ok;
 }
-// Returns false if the phase did not complete within the polling limit.
+// Returns false if the phase did not complete within about one second of wall time (each
+// poll may suspend the warp for a while, so the bound is kept on the global timer, not on
+// the poll count).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity) {
-    for (unsigned it = 0; it < kWaitLimit; ++it)
+    if (mbar_try_wait(mbar, parity)) return true;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (unsigned it = 0; it < kWaitLimit; ++it) {
         if (mbar_try_wait(mbar, parity)) return true;
+        if ((it & 15u) == 15u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (now - t0 > 1000000000ull) return false;
+        }
+    }
     return false;
 }
 __device__ __forceinline__ void fence_proxy_async() {
@@ -92,32 +109,40 @@ __device__ __forceinline__ float src_coord(int i, float scale) {
     return s < 0.0f ? 0.0f : s;
 }
 
-// floor(v) for 0 <= v < 2^22 without a float->int->float round trip: adding 2^23 with
-// round-toward-zero drops the fraction, subtracting it back is exact.  The CPU path's
-// clamp to [0,255] before the uint8 cast cannot change the code: v is a convex blend of
-// values in [0,255], so v < 256 and v >= 0 always.
-__device__ __forceinline__ float trunc_code(float v) {
-    return __fsub_rn(__fadd_rz(v, 8388608.0f), 8388608.0f);
-}
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 
-__device__ __forceinline__ float blend(float a, float wa, float b, float wb) {
-    return __fadd_rn(__fmul_rn(a, wa), __fmul_rn(b, wb));
-}
-
-__device__ __forceinline__ float normalize(float code, float pre, float mean, float inv_std) {
-    return __fmul_rn(__fsub_rn(__fmul_rn(code, pre), mean), inv_std);
+// Packed two-lane fp32 multiply / add of sm_100 (mul.f32x2, add.f32x2) with explicit rounding.
+// Each lane rounds like the scalar instruction.  CAUTION: the assembler was observed to
+// contract a packed multiply feeding a packed add into one FMA even with explicit .rn and with
+// fmad disabled (it flips ~1e-5 of the 8-bit codes and the last bit of most normalized
+// values).  So wherever a product feeds a sum, the sum is done with the scalar __fadd_rn,
+// which is never contracted; packed adds are used only where no product is an input.
+#define TLB_F32X2_OP(name, op)                                                                   \
+    __device__ __forceinline__ float2 name(float2 a, float2 b) {                                 \
+        float2 d;                                                                                \
+        asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t" op    \
+            " rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"                                         \
+            : "=f"(d.x), "=f"(d.y)                                                               \
+            : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));                                           \
+        return d;                                                                                \
+    }
+TLB_F32X2_OP(mul2_rn, "mul.rn.f32x2")
+TLB_F32X2_OP(add2_rn, "add.rn.f32x2")
+TLB_F32X2_OP(add2_rz, "add.rz.f32x2")
+#undef TLB_F32X2_OP
+// Sum of two packed products, lane by lane, with scalar adds (see the caution above).
+__device__ __forceinline__ float2 add2_of_products(float2 a, float2 b) {
+    return f2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
 }
 
 template <int DTYPE>
 struct OutT;
 template <>
 struct OutT<0> {
-    using type = float;
     static constexpr int V = 4;
 };
 template <>
 struct OutT<1> {
-    using type = __nv_bfloat16;
     static constexpr int V = 8;
 };
 
@@ -131,15 +156,15 @@ __device__ __forceinline__ void store_scalar(void* out, long long idx, float v) 
 
 // One 16-byte store of V consecutive output elements starting at element index idx.
 template <int DTYPE>
-__device__ __forceinline__ void store_chunk(void* out, long long idx, const float* v) {
+__device__ __forceinline__ void store_chunk(void* out, long long idx, const float2* v) {
     if constexpr (DTYPE == 0) {
-        *reinterpret_cast<float4*>(static_cast<float*>(out) + idx) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(static_cast<float*>(out) + idx) = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
     } else {
-        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
-        __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
-        __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]);
-        __nv_bfloat162 d = __floats2bfloat162_rn(v[6], v[7]);
         uint4 u;
+        __nv_bfloat162 a = __float22bfloat162_rn(v[0]);
+        __nv_bfloat162 b = __float22bfloat162_rn(v[1]);
+        __nv_bfloat162 c = __float22bfloat162_rn(v[2]);
+        __nv_bfloat162 d = __float22bfloat162_rn(v[3]);
         u.x = *reinterpret_cast<uint32_t*>(&a);
         u.y = *reinterpret_cast<uint32_t*>(&b);
         u.z = *reinterpret_cast<uint32_t*>(&c);
@@ -148,20 +173,100 @@ __device__ __forceinline__ void store_chunk(void* out, long long idx, const floa
     }
 }
 
+// Two outputs at once: blend of the two source rows, truncation to the 8-bit code and
+// normalization, each lane rounded exactly like the scalar sequence
+//   v = a*(1-dy) + b*dy;  code = floor(v);  out = (code*pre - mean) * inv_std.
+// floor(v) for 0 <= v < 2^22 without a float->int->float round trip: adding 2^23 with
+// round-toward-zero drops the fraction, subtracting it back is exact.  The CPU path's clamp
+// to [0,255] before its uint8 cast cannot change the code: v is a convex blend of values in
+// [0,255], so 0 <= v < 256 always.
+__device__ __forceinline__ float2 finish2(float2 a, float2 b, float2 idy, float2 dy, float2 pre, float2 neg_mean,
+                                          float2 istd) {
+    const float2 k = f2(8388608.0f, 8388608.0f), nk = f2(-8388608.0f, -8388608.0f);
+    float2 v = add2_of_products(mul2_rn(a, idy), mul2_rn(b, dy));
+    v = add2_rn(add2_rz(v, k), nk);                                          // floor(v)
+    return mul2_rn(add2_of_products(mul2_rn(v, pre), neg_mean), istd);  // x - m == x + (-m) bit for bit
+}
+
+// Everything warp 0 needs to plan a pass and issue its copies.
+struct PassCtx {
+    int ty1, H, ch, iw, cx, cy, fx_lo, fw, R, pitch, hp;
+    float yscale;
+    const unsigned char* img;
+    unsigned long long reg_lo, reg_hi;
+};
+
+// Executed by all 32 lanes of warp 0.  Plans the pass that starts at output row yb, writes
+// its row tables into the `buf` half of the header and issues the bulk copies into rawbuf.
+__device__ __forceinline__ void plan_and_issue(const PassCtx& c, int yb, int buf, unsigned char* smem,
+                                               unsigned char* rawbuf, int lane) {
+    int4* meta = reinterpret_cast<int4*>(smem + kSmemMeta);
+    float4* rowp = reinterpret_cast<float4*>(smem + kSmemRowp) + buf * 32;
+    int* rowoff = reinterpret_cast<int*>(smem + kSmemRowOff) + buf * 32;
+    const uint32_t mbar = smem_addr(smem + kSmemMbar + 8 * buf);
+
+    const int y = yb + lane;
+    const float sy = src_coord(min(y, c.H - 1), c.yscale);
+    const int y0 = min(static_cast<int>(sy), c.ch - 1);
+    const int y1 = min(y0 + 1, c.ch - 1);
+    const float dy = __fsub_rn(sy, static_cast<float>(y0));
+    const int first = __shfl_sync(0xffffffffu, y0, 0);
+    // Contiguous staging: source rows first .. y1 of the last output row that still fits in R.
+    const unsigned fits = __ballot_sync(0xffffffffu, (y < c.ty1) && (y1 - first + 1 <= c.R));
+    int nrows = __popc(fits);  // the fitting rows form a prefix: y1 is non-decreasing in y
+    const int npair = min(c.R >> 1, c.ty1 - yb);
+    const bool pairs = nrows < npair;  // steep downscale: stage exactly (y0, y1) per output row
+    if (pairs) nrows = npair;
+    const int last_y1 = __shfl_sync(0xffffffffu, y1, nrows - 1);
+    const int nstaged = pairs ? 2 * nrows : (last_y1 - first + 1);
+    if (lane == 0) meta[buf] = make_int4(nrows, nstaged, 0, 0);
+    if (lane < nrows) {
+        const int s0 = pairs ? 2 * lane : (y0 - first);
+        const int s1 = pairs ? 2 * lane + 1 : (y1 - first);
+        rowp[lane] = make_float4(__int_as_float(s0 * c.hp), __int_as_float(s1 * c.hp), dy, __fsub_rn(1.0f, dy));
+    }
+    const int j = lane;  // slot staged by this lane
+    const int ya = __shfl_sync(0xffffffffu, y0, j >> 1);
+    const int yc = __shfl_sync(0xffffffffu, y1, j >> 1);
+    const int srow = pairs ? ((j & 1) ? yc : ya) : (first + j);
+    unsigned bytes = 0;
+    unsigned long long lo = 0, a0 = 0, a1 = 0, hi = 0;
+    if (j < nstaged) {
+        a0 = reinterpret_cast<unsigned long long>(c.img) +
+             (static_cast<unsigned long long>(c.cy + srow) * c.iw + (c.cx + c.fx_lo)) * 3ull;
+        a1 = a0 + static_cast<unsigned long long>(c.fw) * 3ull;
+        lo = a0 & ~15ull;
+        if (lo < c.reg_lo) lo += 16;               // region does not start on the 16-byte grid
+        hi = (a1 + 15ull) & ~15ull;
+        if (hi > c.reg_hi) hi = c.reg_hi & ~15ull;  // region does not end on the 16-byte grid
+        bytes = hi > lo ? static_cast<unsigned>(hi - lo) : 0u;
+        rowoff[j] = j * c.pitch + static_cast<int>(a0 & 15ull);
+    }
+    unsigned total = bytes;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    fence_proxy_async();  // earlier generic reads of this staging buffer precede the new copies
+    if (lane == 0) mbar_arrive_expect_tx(mbar, total);
+    __syncwarp();
+    if (j < nstaged) {
+        unsigned char* slot = rawbuf + j * c.pitch;
+        const unsigned long long origin = a0 & ~15ull;  // global address of slot byte 0
+        if (bytes) bulk_copy_g2s(smem_addr(slot + (lo - origin)), reinterpret_cast<const void*>(lo), bytes, mbar);
+        // Ragged edges outside the 16-byte grid of the readable region (rare).
+        const unsigned long long head_end = bytes ? lo : a1;
+        for (unsigned long long a = a0; a < head_end && a < a1; ++a)
+            slot[a - origin] = *reinterpret_cast<const unsigned char*>(a);
+        if (bytes)
+            for (unsigned long long a = (hi > a0 ? hi : a0); a < a1; ++a)
+                slot[a - origin] = *reinterpret_cast<const unsigned char*>(a);
+    }
+}
+
 template <int DTYPE, int LAYOUT>
-__global__ void __launch_bounds__(kThreads) fused_transform_kernel(const __grid_constant__ FusedParams p) {
+__global__ void __launch_bounds__(kMaxThreads, 3) fused_transform_kernel(const __grid_constant__ FusedParams p) {
     constexpr int V = OutT<DTYPE>::V;
     extern __shared__ __align__(128) unsigned char smem[];
     const Plan& pl = p.plan;
-    const SmemLayout L = smem_layout(pl.tile_cols, pl.staged_rows, pl.pitch, pl.hpitch);
-    float4* colp = reinterpret_cast<float4*>(smem + L.colp);
-    float4* rowp = reinterpret_cast<float4*>(smem + L.rowp);
-    int* rowsh = reinterpret_cast<int*>(smem + L.rowsh);
-    float* ctab = reinterpret_cast<float*>(smem + L.ctab);
-    unsigned char* raw = smem + L.raw;
-    float* hbuf = reinterpret_cast<float*>(smem + L.hbuf);
-    const uint32_t mbar = smem_addr(smem + L.mbar);
-
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
@@ -212,26 +317,28 @@ __global__ void __launch_bounds__(kThreads) fused_transform_kernel(const __grid_
         if (p.labels_out) p.labels_out[k] = (bad & kDevBadIndex) || !p.labels_in ? -1 : p.labels_in[s];
     }
 
-    // ---- column weights: one output column per thread, once per tile ----------------
     const float xscale = __fdiv_rn(static_cast<float>(cw), static_cast<float>(W > 0 ? W : 1));
     const float yscale = __fdiv_rn(static_cast<float>(ch), static_cast<float>(H > 0 ? H : 1));
     // Source-column footprint of the tile: resized columns [oxa, oxb] (mirrored when flipped).
     const int oxa = flip ? (W - 1 - (tx0 + tcw - 1)) : tx0;
     const int oxb = flip ? (W - 1 - tx0) : (tx0 + tcw - 1);
-    int fx_lo = 0, fw = 0;
+    int fx_lo = 0, fw = 0, own_pitch = 16, R = 0;
+    const int var_bytes = pl.smem_bytes - kSmemVar;
     if (!bad) {
         fx_lo = min(static_cast<int>(src_coord(oxa, xscale)), cw - 1);
         const int hi0 = min(static_cast<int>(src_coord(oxb, xscale)), cw - 1);
         const int fx_hi = min(hi0 + 1, cw - 1);
         fw = fx_hi - fx_lo + 1;
-        if (fw * 3 + 30 > pl.pitch) bad = kDevTooWide;
+        own_pitch = (fw * 3 + 30 + 15) & ~15;
+        R = staged_rows_for(var_bytes, own_pitch, pl.hpitch);
+        if (R < 2) bad = kDevTooWide;
     }
 
     if (bad) {
         // Defined behaviour for an invalid sample: zero-fill its tile, report, never trap.
         if (tid == 0 && p.status) atomicOr(p.status, bad);
         const int rows = ty1 - ty0;
-        for (int i = tid; i < rows * tcw * 3; i += kThreads) {
+        for (int i = tid; i < rows * tcw * 3; i += blockDim.x) {
             const int c = i % 3, x = (i / 3) % tcw, y = i / (3 * tcw);
             long long idx;
             if constexpr (LAYOUT == 0)
@@ -243,221 +350,153 @@ __global__ void __launch_bounds__(kThreads) fused_transform_kernel(const __grid_
         return;
     }
 
-    if (tid < tcw) {
-        const int x = tx0 + tid;
+    // ---- carve the variable part of shared memory for this tile's footprint ----------
+    const int hp = pl.hpitch, tcp = pl.tile_cols;
+    unsigned char* raw0 = smem + kSmemVar;
+    unsigned char* raw1 = raw0 + R * own_pitch;
+    float* hbuf = reinterpret_cast<float*>(raw1 + R * own_pitch);
+    const int4* meta = reinterpret_cast<const int4*>(smem + kSmemMeta);
+
+    // ---- H-phase ownership: one output column per thread, weights in registers -------
+    const int hx = tid % tcp;          // column inside the tile
+    const int hg = tid / tcp;          // row group of this thread
+    const int hgroups = blockDim.x / tcp;
+    int off0 = 0, off1 = 0;
+    float2 wx = f2(0.0f, 0.0f);        // (1-dx, dx)
+    if (hx < tcw) {
+        const int x = tx0 + hx;
         const int ox = flip ? (W - 1 - x) : x;
         const float sx = src_coord(ox, xscale);
         const int x0 = min(static_cast<int>(sx), cw - 1);
         const int x1 = min(x0 + 1, cw - 1);
         const float dx = __fsub_rn(sx, static_cast<float>(x0));
-        colp[tid] = make_float4(__int_as_float((x0 - fx_lo) * 3), __int_as_float((x1 - fx_lo) * 3), dx,
-                                __fsub_rn(1.0f, dx));
+        off0 = (x0 - fx_lo) * 3;
+        off1 = (x1 - fx_lo) * 3;
+        wx = f2(__fsub_rn(1.0f, dx), dx);
     }
-    if (LAYOUT == 1 && tid < 48) {
-        // NHWC chunks start at channel phase ph = (first element index) % 3; element i of the
-        // chunk has channel (ph + i) % 3.  ctab[ph*16 + i] = mean, ctab[ph*16 + 8 + i] = inv_std.
-        const int ph = tid >> 4, i = tid & 7, c = (ph + i) % 3;
-        ctab[tid] = (tid & 8) ? p.inv_std[c] : p.mean[c];
-    }
+    // ---- V-phase ownership: V adjacent pixels, three 16-byte chunks per row ------------
+    const int gp = tcp / V;            // pixel groups per tile row
+    const int vg = tid % gp;
+    const int vr = tid / gp;
+    const int vgroups = blockDim.x / gp;
+    const int px0 = vg * V;            // first pixel of the group inside the tile
+    const bool v_active = px0 < tcw;
+    const bool v_full = pl.vec_ok && (px0 + V <= tcw);
+    const float2 pre2 = f2(p.pre_scale, p.pre_scale);
+    long long obase;                    // element index of (row 0, this group) of the sample
+    if constexpr (LAYOUT == 0)
+        obase = static_cast<long long>(k) * 3 * H * W + tx0 + px0;
+    else
+        obase = (static_cast<long long>(k) * H * W + tx0 + px0) * 3;
+
     if (tid == 0) {
-        mbar_init(mbar, 1);
+        mbar_init(smem_addr(smem + kSmemMbar), 1);
+        mbar_init(smem_addr(smem + kSmemMbar + 8), 1);
         fence_proxy_async();
     }
     __syncthreads();
 
-    const int R = pl.staged_rows;
-    const int hp = pl.hpitch;
-    const int tcp = pl.tile_cols;
-    const unsigned char* img = p.src + img_off;
-    const unsigned long long reg_lo = reinterpret_cast<unsigned long long>(p.src);
-    const unsigned long long reg_hi = reg_lo + p.src_bytes;
+    PassCtx pc;
+    pc.ty1 = ty1; pc.H = H; pc.ch = ch; pc.iw = iw; pc.cx = cx; pc.cy = cy; pc.fx_lo = fx_lo; pc.fw = fw;
+    pc.R = R; pc.pitch = own_pitch; pc.hp = hp; pc.yscale = yscale;
+    pc.img = p.src + img_off;
+    pc.reg_lo = reinterpret_cast<unsigned long long>(p.src);
+    pc.reg_hi = pc.reg_lo + p.src_bytes;
+
+    if (warp == 0) plan_and_issue(pc, ty0, 0, smem, raw0, lane);
+
     void* const outp = p.out;
-    uint32_t parity = 0;
-
+    uint32_t phases = 0;  // bit b = parity to wait for on mbarrier b
+    int buf = 0;
     for (int yb = ty0; yb < ty1;) {
-        // ---- rows of this pass: lane l of every warp looks at output row yb + l -------
-        const int y = yb + lane;
-        const float sy = src_coord(min(y, H - 1), yscale);
-        const int y0 = min(static_cast<int>(sy), ch - 1);
-        const int y1 = min(y0 + 1, ch - 1);
-        const float dy = __fsub_rn(sy, static_cast<float>(y0));
-        const int first = __shfl_sync(0xffffffffu, y0, 0);
-        // Contiguous staging: rows first .. y1 of the last output row that still fits in R.
-        const unsigned fits = __ballot_sync(0xffffffffu, (y < ty1) && (y1 - first + 1 <= R));
-        int nrows = __popc(fits);  // the fitting rows form a prefix: y1 is non-decreasing in y
-        const int npair = min(R >> 1, ty1 - yb);
-        const bool pairs = nrows < npair;  // steep downscale: stage exactly (y0, y1) per row
-        if (pairs) nrows = npair;
-        const int last_y1 = __shfl_sync(0xffffffffu, y1, nrows - 1);
-        const int nstaged = pairs ? 2 * nrows : (last_y1 - first + 1);
-
-        if (warp == 0) {
-            if (lane < nrows) {
-                const int s0 = pairs ? 2 * lane : (y0 - first);
-                const int s1 = pairs ? 2 * lane + 1 : (y1 - first);
-                rowp[lane] = make_float4(__int_as_float(s0), __int_as_float(s1), dy, __fsub_rn(1.0f, dy));
-            }
-            // Source row staged in slot j (one slot per lane).
-            const int j = lane;
-            int srow;
-            if (pairs) {
-                const int ya = __shfl_sync(0xffffffffu, y0, j >> 1);
-                const int yb1 = __shfl_sync(0xffffffffu, y1, j >> 1);
-                srow = (j & 1) ? yb1 : ya;
-            } else {
-                srow = first + j;
-            }
-            unsigned bytes = 0;
-            unsigned long long lo = 0, a0 = 0, a1 = 0, hi = 0;
-            if (j < nstaged) {
-                a0 = reinterpret_cast<unsigned long long>(img) +
-                     (static_cast<unsigned long long>(cy + srow) * iw + (cx + fx_lo)) * 3ull;
-                a1 = a0 + static_cast<unsigned long long>(fw) * 3ull;
-                lo = a0 & ~15ull;
-                if (lo < reg_lo) lo += 16;           // region does not start on the 16-byte grid
-                hi = (a1 + 15ull) & ~15ull;
-                if (hi > reg_hi) hi = reg_hi & ~15ull;  // region does not end on the 16-byte grid
-                bytes = hi > lo ? static_cast<unsigned>(hi - lo) : 0u;
-                rowsh[j] = static_cast<int>(a0 & 15ull);
-            }
-            unsigned total = bytes;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-            fence_proxy_async();  // earlier generic reads of the staging buffer precede the new copies
-            if (lane == 0) mbar_arrive_expect_tx(mbar, total);
-            __syncwarp();
-            if (j < nstaged) {
-                unsigned char* slot = raw + j * pl.pitch;
-                const unsigned long long origin = a0 & ~15ull;  // global address of slot byte 0
-                if (bytes) bulk_copy_g2s(smem_addr(slot + (lo - origin)), reinterpret_cast<const void*>(lo), bytes, mbar);
-                // Ragged edges outside the 16-byte grid of the readable region (rare).
-                const unsigned long long head_end = bytes ? lo : a1;
-                for (unsigned long long a = a0; a < head_end && a < a1; ++a)
-                    slot[a - origin] = *reinterpret_cast<const unsigned char*>(a);
-                if (bytes)
-                    for (unsigned long long a = (hi > a0 ? hi : a0); a < a1; ++a)
-                        slot[a - origin] = *reinterpret_cast<const unsigned char*>(a);
-            }
+        __syncthreads();  // tables of this pass visible; previous V phase done with hbuf and rowp[buf^1]
+        const int4 m = meta[buf];
+        const int nrows = m.x, nstaged = m.y;
+        const int ynext = yb + nrows;
+        unsigned char* rawbuf = buf ? raw1 : raw0;
+        if (warp == 0 && ynext < ty1) plan_and_issue(pc, ynext, buf ^ 1, smem, buf ? raw0 : raw1, lane);
+        const uint32_t mbar = smem_addr(smem + kSmemMbar + 8 * buf);
+        if (!mbar_wait_bounded(mbar, (phases >> buf) & 1u)) {
+            // The copies did not land within the polling limit.  Report it and give them one more
+            // bounded chance; the CTA then carries on (every later wait is bounded too) so that no
+            // thread leaves while others sit at a barrier.  The status word marks the output invalid.
+            if (p.status) atomicOr(p.status, kDevCopyTimeout);
+            mbar_wait_bounded(mbar, (phases >> buf) & 1u);
         }
-        __syncthreads();  // rowp / rowsh / ragged bytes visible
-        if (!mbar_wait_bounded(mbar, parity)) {
-            if (tid == 0 && p.status) atomicOr(p.status, kDevCopyTimeout);
-            mbar_wait_bounded(mbar, parity);  // give in-flight copies a second bounded chance to land
-            return;
-        }
-        parity ^= 1u;
+        phases ^= 1u << buf;
 
         // ---- H phase: staged rows -> horizontally interpolated fp32 ---------------------
-        {
-            int j = tid / tcw;
-            int t = tid - j * tcw;
-            while (j < nstaged) {
-                const float4 cp = colp[t];
-                const unsigned char* row = raw + j * pl.pitch + rowsh[j];
-                const unsigned char* q0 = row + __float_as_int(cp.x);
-                const unsigned char* q1 = row + __float_as_int(cp.y);
-                const float h0 = blend(static_cast<float>(q0[0]), cp.w, static_cast<float>(q1[0]), cp.z);
-                const float h1 = blend(static_cast<float>(q0[1]), cp.w, static_cast<float>(q1[1]), cp.z);
-                const float h2 = blend(static_cast<float>(q0[2]), cp.w, static_cast<float>(q1[2]), cp.z);
+        if (hx < tcw) {
+            const int* rowoff = reinterpret_cast<const int*>(smem + kSmemRowOff) + buf * 32;
+            for (int j = hg; j < nstaged; j += hgroups) {
+                const unsigned char* row = rawbuf + rowoff[j];
+                const unsigned char* q0 = row + off0;
+                const unsigned char* q1 = row + off1;
+                const float2 t0 = mul2_rn(f2(static_cast<float>(q0[0]), static_cast<float>(q1[0])), wx);
+                const float2 t1 = mul2_rn(f2(static_cast<float>(q0[1]), static_cast<float>(q1[1])), wx);
+                const float2 t2 = mul2_rn(f2(static_cast<float>(q0[2]), static_cast<float>(q1[2])), wx);
                 float* h = hbuf + j * hp;
                 if constexpr (LAYOUT == 0) {
-                    h[t] = h0;
-                    h[tcp + t] = h1;
-                    h[2 * tcp + t] = h2;
+                    h[hx] = __fadd_rn(t0.x, t0.y);
+                    h[tcp + hx] = __fadd_rn(t1.x, t1.y);
+                    h[2 * tcp + hx] = __fadd_rn(t2.x, t2.y);
                 } else {
-                    h[3 * t] = h0;
-                    h[3 * t + 1] = h1;
-                    h[3 * t + 2] = h2;
-                }
-                t += kThreads;
-                while (t >= tcw) {
-                    t -= tcw;
-                    ++j;
+                    h[3 * hx] = __fadd_rn(t0.x, t0.y);
+                    h[3 * hx + 1] = __fadd_rn(t1.x, t1.y);
+                    h[3 * hx + 2] = __fadd_rn(t2.x, t2.y);
                 }
             }
         }
         __syncthreads();
 
-        // ---- V phase: one 16-byte output chunk per step ----------------------------------
-        if constexpr (LAYOUT == 0) {
-            const int G = (tcw + V - 1) / V;  // chunks per channel row
-            const int U = 3 * G;              // chunks per output row
-            int l = tid / U;
-            int u = tid - l * U;
-            const long long sample_base = static_cast<long long>(k) * 3 * H * W;
-            while (l < nrows) {
-                const int c = (u >= 2 * G) ? 2 : ((u >= G) ? 1 : 0);
-                const int g = u - c * G;
+        // ---- V phase --------------------------------------------------------------------
+        if (v_active) {
+            const float4* rowp = reinterpret_cast<const float4*>(smem + kSmemRowp) + buf * 32;
+            for (int l = vr; l < nrows; l += vgroups) {
                 const float4 rp = rowp[l];
-                const float* ha = hbuf + __float_as_int(rp.x) * hp + c * tcp + g * V;
-                const float* hb = hbuf + __float_as_int(rp.y) * hp + c * tcp + g * V;
-                const float mean = c == 0 ? p.mean[0] : (c == 1 ? p.mean[1] : p.mean[2]);
-                const float istd = c == 0 ? p.inv_std[0] : (c == 1 ? p.inv_std[1] : p.inv_std[2]);
-                float v[V];
+                const float2 dy2 = f2(rp.z, rp.z), idy2 = f2(rp.w, rp.w);
+                const int y = yb + l;
 #pragma unroll
-                for (int q = 0; q < V / 4; ++q) {
-                    const float4 a = *reinterpret_cast<const float4*>(ha + 4 * q);
-                    const float4 b = *reinterpret_cast<const float4*>(hb + 4 * q);
-                    v[4 * q + 0] = normalize(trunc_code(blend(a.x, rp.w, b.x, rp.z)), p.pre_scale, mean, istd);
-                    v[4 * q + 1] = normalize(trunc_code(blend(a.y, rp.w, b.y, rp.z)), p.pre_scale, mean, istd);
-                    v[4 * q + 2] = normalize(trunc_code(blend(a.z, rp.w, b.z, rp.z)), p.pre_scale, mean, istd);
-                    v[4 * q + 3] = normalize(trunc_code(blend(a.w, rp.w, b.w, rp.z)), p.pre_scale, mean, istd);
-                }
-                const long long idx = sample_base + (static_cast<long long>(c) * H + (yb + l)) * W + tx0 + g * V;
-                if (pl.vec_ok && g * V + V <= tcw) {
-                    store_chunk<DTYPE>(outp, idx, v);
-                } else {
+                for (int q = 0; q < 3; ++q) {
+                    // NCHW: chunk q = channel q of the group's V pixels.  NHWC: chunk q = elements
+                    // [q*V, q*V+V) of the group's 3V interleaved elements (element e has channel e % 3).
+                    const int hoff = LAYOUT == 0 ? (q * tcp + px0) : (3 * px0 + q * V);
+                    const float* ha = hbuf + __float_as_int(rp.x) + hoff;
+                    const float* hb = hbuf + __float_as_int(rp.y) + hoff;
+                    float2 v[V / 2];
 #pragma unroll
-                    for (int i = 0; i < V; ++i)
-                        if (g * V + i < tcw) store_scalar<DTYPE>(outp, idx + i, v[i]);
-                }
-                u += kThreads;
-                while (u >= U) {
-                    u -= U;
-                    ++l;
-                }
-            }
-        } else {
-            const int E = 3 * tcw;            // interleaved elements per output row of the tile
-            const int G = (E + V - 1) / V;    // chunks per output row
-            int l = tid / G;
-            int g = tid - l * G;
-            while (l < nrows) {
-                const float4 rp = rowp[l];
-                const float* ha = hbuf + __float_as_int(rp.x) * hp + g * V;
-                const float* hb = hbuf + __float_as_int(rp.y) * hp + g * V;
-                const int ph = (g * V) % 3;
-                const float* cm = ctab + ph * 16;
-                float v[V];
+                    for (int i = 0; i < V / 4; ++i) {
+                        const float4 a = *reinterpret_cast<const float4*>(ha + 4 * i);
+                        const float4 b = *reinterpret_cast<const float4*>(hb + 4 * i);
+                        const int c0 = LAYOUT == 0 ? q : (q * V + 4 * i + 0) % 3;
+                        const int c1 = LAYOUT == 0 ? q : (q * V + 4 * i + 1) % 3;
+                        const int c2 = LAYOUT == 0 ? q : (q * V + 4 * i + 2) % 3;
+                        const int c3 = LAYOUT == 0 ? q : (q * V + 4 * i + 3) % 3;
+                        v[2 * i] = finish2(f2(a.x, a.y), f2(b.x, b.y), idy2, dy2, pre2, f2(-p.mean[c0], -p.mean[c1]),
+                                           f2(p.inv_std[c0], p.inv_std[c1]));
+                        v[2 * i + 1] = finish2(f2(a.z, a.w), f2(b.z, b.w), idy2, dy2, pre2,
+                                               f2(-p.mean[c2], -p.mean[c3]), f2(p.inv_std[c2], p.inv_std[c3]));
+                    }
+                    long long idx;
+                    if constexpr (LAYOUT == 0)
+                        idx = obase + static_cast<long long>((q * H + y) * W);
+                    else
+                        idx = obase + static_cast<long long>(y) * W * 3 + q * V;
+                    if (v_full) {
+                        store_chunk<DTYPE>(outp, idx, v);
+                    } else {
 #pragma unroll
-                for (int q = 0; q < V / 4; ++q) {
-                    const float4 a = *reinterpret_cast<const float4*>(ha + 4 * q);
-                    const float4 b = *reinterpret_cast<const float4*>(hb + 4 * q);
-                    const float4 m = *reinterpret_cast<const float4*>(cm + 4 * q);
-                    const float4 is = *reinterpret_cast<const float4*>(cm + 8 + 4 * q);
-                    v[4 * q + 0] = normalize(trunc_code(blend(a.x, rp.w, b.x, rp.z)), p.pre_scale, m.x, is.x);
-                    v[4 * q + 1] = normalize(trunc_code(blend(a.y, rp.w, b.y, rp.z)), p.pre_scale, m.y, is.y);
-                    v[4 * q + 2] = normalize(trunc_code(blend(a.z, rp.w, b.z, rp.z)), p.pre_scale, m.z, is.z);
-                    v[4 * q + 3] = normalize(trunc_code(blend(a.w, rp.w, b.w, rp.z)), p.pre_scale, m.w, is.w);
-                }
-                const long long idx =
-                    ((static_cast<long long>(k) * H + (yb + l)) * W + tx0) * 3 + static_cast<long long>(g) * V;
-                if (pl.vec_ok && g * V + V <= E) {
-                    store_chunk<DTYPE>(outp, idx, v);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < V; ++i)
-                        if (g * V + i < E) store_scalar<DTYPE>(outp, idx + i, v[i]);
-                }
-                g += kThreads;
-                while (g >= G) {
-                    g -= G;
-                    ++l;
+                        for (int i = 0; i < V; ++i) {
+                            const float val = (i & 1) ? v[i >> 1].y : v[i >> 1].x;
+                            const bool in = LAYOUT == 0 ? (px0 + i < tcw) : (3 * px0 + q * V + i < 3 * tcw);
+                            if (in) store_scalar<DTYPE>(outp, idx + i, val);
+                        }
+                    }
                 }
             }
         }
-        yb += nrows;
-        if (yb < ty1) __syncthreads();  // staging buffers are reused by the next pass
+        yb = ynext;
+        buf ^= 1;
     }
 }
 
@@ -466,7 +505,7 @@ std::atomic<unsigned long long> g_launches{0};
 template <int DTYPE, int LAYOUT>
 int launch_one(const FusedParams& p, cudaStream_t st) {
     auto kern = fused_transform_kernel<DTYPE, LAYOUT>;
-    kern<<<static_cast<unsigned>(p.plan.grid), kThreads, p.plan.smem_bytes, st>>>(p);
+    kern<<<static_cast<unsigned>(p.plan.grid), p.plan.threads, p.plan.smem_bytes, st>>>(p);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return static_cast<int>(cudaGetLastError());
 }
