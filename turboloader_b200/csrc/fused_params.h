@@ -5,8 +5,9 @@
 
 namespace tlb {
 
-constexpr int kMaxThreads = 256;   // threads per CTA = (256 / tile_cols) * tile_cols
-constexpr int kMaxStagedRows = 32; // one lane of warp 0 issues the copy of one staged row
+constexpr int kMaxConsumers = 256; // compute threads per CTA = (256 / tile_cols) * tile_cols
+constexpr int kProducerThreads = 32; // one extra warp plans passes and issues the bulk copies
+constexpr int kMaxNewRows = 32;    // one producer lane issues the copy of one staged row
 constexpr int kMaxTileCols = 256;  // output columns per CTA
 
 // Launch geometry chosen on the host from sizes only (never from device data).
@@ -15,9 +16,11 @@ struct Plan {
     int tile_cols;    // output columns per CTA (multiple of 16, <= kMaxTileCols)
     int n_col_tiles;  // ceil(dst_w / tile_cols)
     int n_row_tiles;  // ceil(dst_h / tile_rows)
-    int threads;      // CTA size, a multiple of tile_cols
+    int consumers;    // compute threads, a multiple of tile_cols; CTA size = consumers + 32
     int pitch;        // bytes per staged raw row at the widest crop (multiple of 16)
-    int hpitch;       // floats per row of horizontally-interpolated values (3 * tile_cols)
+    int plane;        // NCHW: floats per channel plane of one h row (tile_cols, padded for bf16)
+    int half_off;     // NCHW bf16: float offset of the odd 16-byte chunks inside a plane (else 0)
+    int hpitch;       // floats per row of horizontally-interpolated values
     int smem_bytes;   // dynamic shared memory per CTA
     int vec_ok;       // 1: every 16-byte output chunk is aligned and whole -> vector stores
     long long grid;   // CTAs
@@ -48,18 +51,18 @@ struct FusedParams {
 };
 
 // Shared-memory layout.  A fixed header is followed by a region the CTA carves up itself
-// from its own footprint width: two raw staging buffers of R rows (double buffering) and
-// one fp32 buffer of R horizontally-interpolated rows, with
-//   R = min(kMaxStagedRows, variable_bytes / (2 * own_pitch + hpitch * 4)).
-constexpr int kSmemMbar = 0;      // 2 x 8 B mbarriers
-constexpr int kSmemMeta = 16;     // 2 x int4 {rows of the pass, staged rows, -, -}
-constexpr int kSmemRowp = 48;     // 2 x 32 x float4 {h offset of y0 row, of y1 row, dy, 1-dy}
-constexpr int kSmemRowOff = 48 + 1024;        // 2 x 32 x int: byte offset of each staged row's first pixel
-constexpr int kSmemVar = 48 + 1024 + 256 + 80;  // = 1408, start of the carved region (128-byte multiple)
+// from its own footprint width: two raw staging buffers of Rr rows each (double buffering)
+// and a ring of Rh = 2*Rr + 2 rows of horizontally-interpolated fp32 values.  The ring is that
+// deep so that the h rows of pass i+1 can be produced while pass i is still being consumed.
+constexpr int kSmemMbar = 0;       // 2 x 8 B mbarriers (one per raw buffer)
+constexpr int kSmemMeta = 16;      // 3 x int4 {output rows, new source rows, last pass?, first output row}
+constexpr int kSmemRowp = 64;      // 3 x 32 x float4 {h offset of y0 row, of y1 row, dy, 1-dy}
+constexpr int kSmemRowOff = 64 + 1536;         // 3 x 32 x int2 {raw byte offset, h float offset} per new row
+constexpr int kSmemVar = 64 + 1536 + 768 + 64; // = 2432, start of the carved region (128-byte multiple)
 
-inline __host__ __device__ int staged_rows_for(int var_bytes, int own_pitch, int hpitch) {
-    int r = var_bytes / (2 * own_pitch + hpitch * 4);
-    return r > kMaxStagedRows ? kMaxStagedRows : r;
+inline __host__ __device__ int raw_rows_for(int var_bytes, int own_pitch, int hpitch) {
+    int r = (var_bytes - 2 * hpitch * 4) / (2 * own_pitch + 2 * hpitch * 4);
+    return r > kMaxNewRows ? kMaxNewRows : r;
 }
 
 // Implemented in fused_transform.cu.  Returns a cudaError_t as int.

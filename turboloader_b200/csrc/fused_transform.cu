@@ -130,6 +130,25 @@ TLB_F32X2_OP(mul2_rn, "mul.rn.f32x2")
 TLB_F32X2_OP(add2_rn, "add.rn.f32x2")
 TLB_F32X2_OP(add2_rz, "add.rz.f32x2")
 #undef TLB_F32X2_OP
+// Packed FMA.  Used only where the fused result is exactly the wanted singly-rounded product
+// (see byte_product2).
+__device__ __forceinline__ float2 fma2_rn(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+// (RN(b0 * w.x), RN(b1 * w.y)) for two bytes b0, b1 in [0,255] WITHOUT an integer-to-float
+// conversion (those run at a fraction of the fp32 rate on this GPU and were the busiest pipe).
+// OR-ing a byte into the mantissa of 2^23 gives the float 2^23 + b exactly; with
+// negw = -2^23 * w (exact: a power-of-two scaling), fma(2^23 + b, w, negw) evaluates
+// (2^23 + b)*w - 2^23*w = b*w exactly and rounds once, i.e. it IS RN(b*w), bit for bit
+// (and +0 when b or w is 0, like the plain product of non-negative operands).
+__device__ __forceinline__ float2 byte_product2(unsigned b0, unsigned b1, float2 w, float2 negw) {
+    return fma2_rn(f2(__uint_as_float(b0 | 0x4B000000u), __uint_as_float(b1 | 0x4B000000u)), w, negw);
+}
 // Sum of two packed products, lane by lane, with scalar adds (see the caution above).
 __device__ __forceinline__ float2 add2_of_products(float2 a, float2 b) {
     return f2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
@@ -188,22 +207,36 @@ __device__ __forceinline__ float2 finish2(float2 a, float2 b, float2 idy, float2
     return mul2_rn(add2_of_products(mul2_rn(v, pre), neg_mean), istd);  // x - m == x + (-m) bit for bit
 }
 
-// Everything warp 0 needs to plan a pass and issue its copies.
+// Everything the producer warp needs to plan a pass and issue its copies.
 struct PassCtx {
-    int ty1, H, ch, iw, cx, cy, fx_lo, fw, R, pitch, hp;
+    int ty0, ty1, H, ch, iw, cx, cy, fx_lo, fw, Rr, Rh, pitch, hp;
+    bool pairs;  // vertical downscale steeper than 2x: output rows share no source row
     float yscale;
     const unsigned char* img;
     unsigned long long reg_lo, reg_hi;
 };
 
-// Executed by all 32 lanes of warp 0.  Plans the pass that starts at output row yb, writes
-// its row tables into the `buf` half of the header and issues the bulk copies into rawbuf.
-__device__ __forceinline__ void plan_and_issue(const PassCtx& c, int yb, int buf, unsigned char* smem,
-                                               unsigned char* rawbuf, int lane) {
+// Producer state carried from one pass to the next (uniform across the warp).
+struct PassState {
+    int yb;           // first output row of the next pass to plan
+    int staged_last;  // last source row already present in the h ring (contiguous mode), or -1
+    int index;        // number of passes planned so far
+};
+
+// Executed by all 32 lanes of the producer warp.  Plans the pass that starts at output row
+// st.yb: one lane per output row computes (y0, y1, dy); the first row's y0 and the last row's y1
+// are exchanged with warp shuffles to find the range of NEW source rows (rows the h ring does
+// not hold yet).  Writes the pass tables into slot (index % 3) of the header and issues one bulk
+// copy per new source row into raw buffer (index % 2).
+__device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, unsigned char* smem,
+                                               unsigned char* raw0, unsigned char* raw1, int lane) {
+    const int slot3 = st.index % 3, buf = st.index & 1;
     int4* meta = reinterpret_cast<int4*>(smem + kSmemMeta);
-    float4* rowp = reinterpret_cast<float4*>(smem + kSmemRowp) + buf * 32;
-    int* rowoff = reinterpret_cast<int*>(smem + kSmemRowOff) + buf * 32;
+    float4* rowp = reinterpret_cast<float4*>(smem + kSmemRowp) + slot3 * 32;
+    int2* rowoff = reinterpret_cast<int2*>(smem + kSmemRowOff) + slot3 * 32;
+    unsigned char* rawbuf = buf ? raw1 : raw0;
     const uint32_t mbar = smem_addr(smem + kSmemMbar + 8 * buf);
+    const int yb = st.yb;
 
     const int y = yb + lane;
     const float sy = src_coord(min(y, c.H - 1), c.yscale);
@@ -211,27 +244,38 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, int yb, int buf
     const int y1 = min(y0 + 1, c.ch - 1);
     const float dy = __fsub_rn(sy, static_cast<float>(y0));
     const int first = __shfl_sync(0xffffffffu, y0, 0);
-    // Contiguous staging: source rows first .. y1 of the last output row that still fits in R.
-    const unsigned fits = __ballot_sync(0xffffffffu, (y < c.ty1) && (y1 - first + 1 <= c.R));
-    int nrows = __popc(fits);  // the fitting rows form a prefix: y1 is non-decreasing in y
-    const int npair = min(c.R >> 1, c.ty1 - yb);
-    const bool pairs = nrows < npair;  // steep downscale: stage exactly (y0, y1) per output row
-    if (pairs) nrows = npair;
-    const int last_y1 = __shfl_sync(0xffffffffu, y1, nrows - 1);
-    const int nstaged = pairs ? 2 * nrows : (last_y1 - first + 1);
-    if (lane == 0) meta[buf] = make_int4(nrows, nstaged, 0, 0);
-    if (lane < nrows) {
-        const int s0 = pairs ? 2 * lane : (y0 - first);
-        const int s1 = pairs ? 2 * lane + 1 : (y1 - first);
-        rowp[lane] = make_float4(__int_as_float(s0 * c.hp), __int_as_float(s1 * c.hp), dy, __fsub_rn(1.0f, dy));
+    int nrows, nnew, new_first = 0;
+    if (c.pairs) {
+        nrows = min(c.Rr >> 1, min(c.ty1 - yb, 32));
+        nnew = 2 * nrows;
+    } else {
+        new_first = max(first, st.staged_last + 1);
+        // Output rows whose source rows fit among the Rr rows this pass may add form a prefix
+        // (y1 is non-decreasing in y).
+        const unsigned fits = __ballot_sync(0xffffffffu, (y < c.ty1) && (y1 - new_first + 1 <= c.Rr));
+        nrows = __popc(fits);
+        const int last_y1 = __shfl_sync(0xffffffffu, y1, nrows - 1);
+        nnew = max(last_y1 - new_first + 1, 0);
+        st.staged_last = max(st.staged_last, last_y1);
     }
-    const int j = lane;  // slot staged by this lane
+    const int ynext = yb + nrows;
+    if (lane == 0) meta[slot3] = make_int4(nrows, nnew, ynext >= c.ty1 ? 1 : 0, yb);
+    if (lane < nrows) {
+        // Ring position of a source row: its row number (contiguous mode) or its sequence number
+        // 2*(y - ty0) + {0,1} (pairs mode), modulo the ring depth.
+        const int q0 = c.pairs ? 2 * (y - c.ty0) : y0;
+        const int q1 = c.pairs ? q0 + 1 : y1;
+        rowp[lane] = make_float4(__int_as_float((q0 % c.Rh) * c.hp), __int_as_float((q1 % c.Rh) * c.hp), dy,
+                                 __fsub_rn(1.0f, dy));
+    }
+    const int j = lane;  // new source row staged by this lane
     const int ya = __shfl_sync(0xffffffffu, y0, j >> 1);
     const int yc = __shfl_sync(0xffffffffu, y1, j >> 1);
-    const int srow = pairs ? ((j & 1) ? yc : ya) : (first + j);
+    const int srow = c.pairs ? ((j & 1) ? yc : ya) : (new_first + j);
+    const int q = c.pairs ? 2 * (yb - c.ty0) + j : srow;
     unsigned bytes = 0;
     unsigned long long lo = 0, a0 = 0, a1 = 0, hi = 0;
-    if (j < nstaged) {
+    if (j < nnew) {
         a0 = reinterpret_cast<unsigned long long>(c.img) +
              (static_cast<unsigned long long>(c.cy + srow) * c.iw + (c.cx + c.fx_lo)) * 3ull;
         a1 = a0 + static_cast<unsigned long long>(c.fw) * 3ull;
@@ -240,7 +284,7 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, int yb, int buf
         hi = (a1 + 15ull) & ~15ull;
         if (hi > c.reg_hi) hi = c.reg_hi & ~15ull;  // region does not end on the 16-byte grid
         bytes = hi > lo ? static_cast<unsigned>(hi - lo) : 0u;
-        rowoff[j] = j * c.pitch + static_cast<int>(a0 & 15ull);
+        rowoff[j] = make_int2(j * c.pitch + static_cast<int>(a0 & 15ull), (q % c.Rh) * c.hp);
     }
     unsigned total = bytes;
 #pragma unroll
@@ -248,7 +292,7 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, int yb, int buf
     fence_proxy_async();  // earlier generic reads of this staging buffer precede the new copies
     if (lane == 0) mbar_arrive_expect_tx(mbar, total);
     __syncwarp();
-    if (j < nstaged) {
+    if (j < nnew) {
         unsigned char* slot = rawbuf + j * c.pitch;
         const unsigned long long origin = a0 & ~15ull;  // global address of slot byte 0
         if (bytes) bulk_copy_g2s(smem_addr(slot + (lo - origin)), reinterpret_cast<const void*>(lo), bytes, mbar);
@@ -260,16 +304,23 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, int yb, int buf
             for (unsigned long long a = (hi > a0 ? hi : a0); a < a1; ++a)
                 slot[a - origin] = *reinterpret_cast<const unsigned char*>(a);
     }
+    st.yb = ynext;
+    st.index += 1;
 }
 
 template <int DTYPE, int LAYOUT>
-__global__ void __launch_bounds__(kMaxThreads, 3) fused_transform_kernel(const __grid_constant__ FusedParams p) {
+__global__ void __launch_bounds__(kMaxConsumers + kProducerThreads, 3)
+fused_transform_kernel(const __grid_constant__ FusedParams p) {
     constexpr int V = OutT<DTYPE>::V;
     extern __shared__ __align__(128) unsigned char smem[];
     const Plan& pl = p.plan;
     const int tid = threadIdx.x;
     const int lane = tid & 31;
-    const int warp = tid >> 5;
+    const int nc = pl.consumers;
+    // The last warp plans passes and issues copies.  It starts on a warp boundary; compute threads
+    // are tid < nc, and threads in between (nc not a multiple of 32) only take part in barriers.
+    const int pbase = (nc + 31) & ~31;
+    const bool producer = tid >= pbase;
 
     // ---- which tile of which sample ------------------------------------------------
     unsigned bid = blockIdx.x;
@@ -322,16 +373,16 @@ __global__ void __launch_bounds__(kMaxThreads, 3) fused_transform_kernel(const _
     // Source-column footprint of the tile: resized columns [oxa, oxb] (mirrored when flipped).
     const int oxa = flip ? (W - 1 - (tx0 + tcw - 1)) : tx0;
     const int oxb = flip ? (W - 1 - tx0) : (tx0 + tcw - 1);
-    int fx_lo = 0, fw = 0, own_pitch = 16, R = 0;
-    const int var_bytes = pl.smem_bytes - kSmemVar;
+    int fx_lo = 0, fw = 0, own_pitch = 16, Rr = 0;
+    const int hp = pl.hpitch, tcp = pl.tile_cols;
     if (!bad) {
         fx_lo = min(static_cast<int>(src_coord(oxa, xscale)), cw - 1);
         const int hi0 = min(static_cast<int>(src_coord(oxb, xscale)), cw - 1);
         const int fx_hi = min(hi0 + 1, cw - 1);
         fw = fx_hi - fx_lo + 1;
         own_pitch = (fw * 3 + 30 + 15) & ~15;
-        R = staged_rows_for(var_bytes, own_pitch, pl.hpitch);
-        if (R < 2) bad = kDevTooWide;
+        Rr = raw_rows_for(pl.smem_bytes - kSmemVar, own_pitch, hp);
+        if (Rr < 2) bad = kDevTooWide;
     }
 
     if (bad) {
@@ -351,19 +402,52 @@ __global__ void __launch_bounds__(kMaxThreads, 3) fused_transform_kernel(const _
     }
 
     // ---- carve the variable part of shared memory for this tile's footprint ----------
-    const int hp = pl.hpitch, tcp = pl.tile_cols;
+    const int Rh = 2 * Rr + 2;
     unsigned char* raw0 = smem + kSmemVar;
-    unsigned char* raw1 = raw0 + R * own_pitch;
-    float* hbuf = reinterpret_cast<float*>(raw1 + R * own_pitch);
+    unsigned char* raw1 = raw0 + Rr * own_pitch;
+    float* hbuf = reinterpret_cast<float*>(raw1 + Rr * own_pitch);
     const int4* meta = reinterpret_cast<const int4*>(smem + kSmemMeta);
 
+    if (tid == 0) {
+        mbar_init(smem_addr(smem + kSmemMbar), 1);
+        mbar_init(smem_addr(smem + kSmemMbar + 8), 1);
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    if (producer) {
+        // ================= producer warp: plan passes, issue copies, keep two passes ahead =========
+        PassCtx pc;
+        pc.ty0 = ty0; pc.ty1 = ty1; pc.H = H; pc.ch = ch; pc.iw = iw; pc.cx = cx; pc.cy = cy;
+        pc.fx_lo = fx_lo; pc.fw = fw; pc.Rr = Rr; pc.Rh = Rh; pc.pitch = own_pitch; pc.hp = hp;
+        pc.pairs = ch > 2 * H;
+        pc.yscale = yscale;
+        pc.img = p.src + img_off;
+        pc.reg_lo = reinterpret_cast<unsigned long long>(p.src);
+        pc.reg_hi = pc.reg_lo + p.src_bytes;
+        PassState st;
+        st.yb = ty0; st.staged_last = -1; st.index = 0;
+        plan_and_issue(pc, st, smem, raw0, raw1, lane);              // pass 0
+        __syncthreads();                                              // (P) tables of pass 0 visible
+        if (st.yb < ty1) plan_and_issue(pc, st, smem, raw0, raw1, lane);  // pass 1
+        // Main loop: after barrier i the raw buffer and table slot of pass i+2 are free.
+        for (int i = 0;; ++i) {
+            __syncthreads();                                          // barrier i
+            if (meta[i % 3].z) break;                                 // pass i is the last one
+            if (st.index == i + 2 && st.yb < ty1) plan_and_issue(pc, st, smem, raw0, raw1, lane);
+        }
+        return;
+    }
+
+    // ================= consumer warps ==============================================================
     // ---- H-phase ownership: one output column per thread, weights in registers -------
     const int hx = tid % tcp;          // column inside the tile
     const int hg = tid / tcp;          // row group of this thread
-    const int hgroups = blockDim.x / tcp;
+    const int hgroups = nc / tcp;
     int off0 = 0, off1 = 0;
     float2 wx = f2(0.0f, 0.0f);        // (1-dx, dx)
-    if (hx < tcw) {
+    const bool h_active = tid < nc && hx < tcw;
+    if (h_active) {
         const int x = tx0 + hx;
         const int ox = flip ? (W - 1 - x) : x;
         const float sx = src_coord(ox, xscale);
@@ -374,13 +458,21 @@ __global__ void __launch_bounds__(kMaxThreads, 3) fused_transform_kernel(const _
         off1 = (x1 - fx_lo) * 3;
         wx = f2(__fsub_rn(1.0f, dx), dx);
     }
+    const float2 nwx = f2(__fmul_rn(-8388608.0f, wx.x), __fmul_rn(-8388608.0f, wx.y));
+    // Position of this thread's column inside one h row.
+    int hpos;
+    if constexpr (LAYOUT == 0)
+        hpos = (DTYPE == 1) ? (((hx >> 2) & 1) * pl.half_off + (hx >> 3) * 4 + (hx & 3)) : hx;
+    else
+        hpos = 3 * hx;
+    const int plane = pl.plane;
     // ---- V-phase ownership: V adjacent pixels, three 16-byte chunks per row ------------
     const int gp = tcp / V;            // pixel groups per tile row
     const int vg = tid % gp;
     const int vr = tid / gp;
-    const int vgroups = blockDim.x / gp;
+    const int vgroups = nc / gp;
     const int px0 = vg * V;            // first pixel of the group inside the tile
-    const bool v_active = px0 < tcw;
+    const bool v_active = tid < nc && px0 < tcw;
     const bool v_full = pl.vec_ok && (px0 + V <= tcw);
     const float2 pre2 = f2(p.pre_scale, p.pre_scale);
     long long obase;                    // element index of (row 0, this group) of the sample
@@ -388,115 +480,109 @@ __global__ void __launch_bounds__(kMaxThreads, 3) fused_transform_kernel(const _
         obase = static_cast<long long>(k) * 3 * H * W + tx0 + px0;
     else
         obase = (static_cast<long long>(k) * H * W + tx0 + px0) * 3;
-
-    if (tid == 0) {
-        mbar_init(smem_addr(smem + kSmemMbar), 1);
-        mbar_init(smem_addr(smem + kSmemMbar + 8), 1);
-        fence_proxy_async();
-    }
-    __syncthreads();
-
-    PassCtx pc;
-    pc.ty1 = ty1; pc.H = H; pc.ch = ch; pc.iw = iw; pc.cx = cx; pc.cy = cy; pc.fx_lo = fx_lo; pc.fw = fw;
-    pc.R = R; pc.pitch = own_pitch; pc.hp = hp; pc.yscale = yscale;
-    pc.img = p.src + img_off;
-    pc.reg_lo = reinterpret_cast<unsigned long long>(p.src);
-    pc.reg_hi = pc.reg_lo + p.src_bytes;
-
-    if (warp == 0) plan_and_issue(pc, ty0, 0, smem, raw0, lane);
-
+    // Float offset of this group's first 16-byte chunk inside an h row (plane 0 for NCHW).
+    const int vpos = LAYOUT == 0 ? vg * 4 : 3 * px0;
     void* const outp = p.out;
-    uint32_t phases = 0;  // bit b = parity to wait for on mbarrier b
-    int buf = 0;
-    for (int yb = ty0; yb < ty1;) {
-        __syncthreads();  // tables of this pass visible; previous V phase done with hbuf and rowp[buf^1]
-        const int4 m = meta[buf];
-        const int nrows = m.x, nstaged = m.y;
-        const int ynext = yb + nrows;
-        unsigned char* rawbuf = buf ? raw1 : raw0;
-        if (warp == 0 && ynext < ty1) plan_and_issue(pc, ynext, buf ^ 1, smem, buf ? raw0 : raw1, lane);
-        const uint32_t mbar = smem_addr(smem + kSmemMbar + 8 * buf);
-        if (!mbar_wait_bounded(mbar, (phases >> buf) & 1u)) {
-            // The copies did not land within the polling limit.  Report it and give them one more
+
+    // H phase of pass `pi`: wait for its copies, interpolate its new source rows into the ring.
+    auto h_phase = [&](int pi) {
+        const int4 m = meta[pi % 3];
+        const int b = pi & 1;
+        const uint32_t mbar = smem_addr(smem + kSmemMbar + 8 * b);
+        const uint32_t parity = static_cast<uint32_t>(pi >> 1) & 1u;
+        if (!mbar_wait_bounded(mbar, parity)) {
+            // The copies did not land within the time limit.  Report it and give them one more
             // bounded chance; the CTA then carries on (every later wait is bounded too) so that no
             // thread leaves while others sit at a barrier.  The status word marks the output invalid.
             if (p.status) atomicOr(p.status, kDevCopyTimeout);
-            mbar_wait_bounded(mbar, (phases >> buf) & 1u);
+            mbar_wait_bounded(mbar, parity);
         }
-        phases ^= 1u << buf;
-
-        // ---- H phase: staged rows -> horizontally interpolated fp32 ---------------------
-        if (hx < tcw) {
-            const int* rowoff = reinterpret_cast<const int*>(smem + kSmemRowOff) + buf * 32;
-            for (int j = hg; j < nstaged; j += hgroups) {
-                const unsigned char* row = rawbuf + rowoff[j];
-                const unsigned char* q0 = row + off0;
-                const unsigned char* q1 = row + off1;
-                const float2 t0 = mul2_rn(f2(static_cast<float>(q0[0]), static_cast<float>(q1[0])), wx);
-                const float2 t1 = mul2_rn(f2(static_cast<float>(q0[1]), static_cast<float>(q1[1])), wx);
-                const float2 t2 = mul2_rn(f2(static_cast<float>(q0[2]), static_cast<float>(q1[2])), wx);
-                float* h = hbuf + j * hp;
+        if (h_active) {
+            const unsigned char* rawbuf = b ? raw1 : raw0;
+            const int2* rowoff = reinterpret_cast<const int2*>(smem + kSmemRowOff) + (pi % 3) * 32;
+#pragma unroll 2
+            for (int j = hg; j < m.y; j += hgroups) {
+                const int2 ro = rowoff[j];
+                const unsigned char* q0 = rawbuf + ro.x + off0;
+                const unsigned char* q1 = rawbuf + ro.x + off1;
+                const float2 t0 = byte_product2(q0[0], q1[0], wx, nwx);
+                const float2 t1 = byte_product2(q0[1], q1[1], wx, nwx);
+                const float2 t2 = byte_product2(q0[2], q1[2], wx, nwx);
+                float* h = hbuf + ro.y + hpos;
                 if constexpr (LAYOUT == 0) {
-                    h[hx] = __fadd_rn(t0.x, t0.y);
-                    h[tcp + hx] = __fadd_rn(t1.x, t1.y);
-                    h[2 * tcp + hx] = __fadd_rn(t2.x, t2.y);
+                    h[0] = __fadd_rn(t0.x, t0.y);
+                    h[plane] = __fadd_rn(t1.x, t1.y);
+                    h[2 * plane] = __fadd_rn(t2.x, t2.y);
                 } else {
-                    h[3 * hx] = __fadd_rn(t0.x, t0.y);
-                    h[3 * hx + 1] = __fadd_rn(t1.x, t1.y);
-                    h[3 * hx + 2] = __fadd_rn(t2.x, t2.y);
+                    h[0] = __fadd_rn(t0.x, t0.y);
+                    h[1] = __fadd_rn(t1.x, t1.y);
+                    h[2] = __fadd_rn(t2.x, t2.y);
                 }
             }
         }
-        __syncthreads();
+    };
 
-        // ---- V phase --------------------------------------------------------------------
-        if (v_active) {
-            const float4* rowp = reinterpret_cast<const float4*>(smem + kSmemRowp) + buf * 32;
-            for (int l = vr; l < nrows; l += vgroups) {
-                const float4 rp = rowp[l];
-                const float2 dy2 = f2(rp.z, rp.z), idy2 = f2(rp.w, rp.w);
-                const int y = yb + l;
+    // V phase of pass `pi`: blend the two h rows of every output row, finish, store.
+    auto v_phase = [&](int pi) {
+        if (!v_active) return;
+        const int4 m = meta[pi % 3];
+        const float4* rowp = reinterpret_cast<const float4*>(smem + kSmemRowp) + (pi % 3) * 32;
+        for (int l = vr; l < m.x; l += vgroups) {
+            const float4 rp = rowp[l];
+            const float2 dy2 = f2(rp.z, rp.z), idy2 = f2(rp.w, rp.w);
+            const int y = m.w + l;
+            const float* ra = hbuf + __float_as_int(rp.x) + vpos;
+            const float* rb = hbuf + __float_as_int(rp.y) + vpos;
 #pragma unroll
-                for (int q = 0; q < 3; ++q) {
-                    // NCHW: chunk q = channel q of the group's V pixels.  NHWC: chunk q = elements
-                    // [q*V, q*V+V) of the group's 3V interleaved elements (element e has channel e % 3).
-                    const int hoff = LAYOUT == 0 ? (q * tcp + px0) : (3 * px0 + q * V);
-                    const float* ha = hbuf + __float_as_int(rp.x) + hoff;
-                    const float* hb = hbuf + __float_as_int(rp.y) + hoff;
-                    float2 v[V / 2];
+            for (int q = 0; q < 3; ++q) {
+                // NCHW: chunk q = channel q of the group's V pixels.  NHWC: chunk q = elements
+                // [q*V, q*V+V) of the group's 3V interleaved elements (element e has channel e % 3).
+                float2 v[V / 2];
 #pragma unroll
-                    for (int i = 0; i < V / 4; ++i) {
-                        const float4 a = *reinterpret_cast<const float4*>(ha + 4 * i);
-                        const float4 b = *reinterpret_cast<const float4*>(hb + 4 * i);
-                        const int c0 = LAYOUT == 0 ? q : (q * V + 4 * i + 0) % 3;
-                        const int c1 = LAYOUT == 0 ? q : (q * V + 4 * i + 1) % 3;
-                        const int c2 = LAYOUT == 0 ? q : (q * V + 4 * i + 2) % 3;
-                        const int c3 = LAYOUT == 0 ? q : (q * V + 4 * i + 3) % 3;
-                        v[2 * i] = finish2(f2(a.x, a.y), f2(b.x, b.y), idy2, dy2, pre2, f2(-p.mean[c0], -p.mean[c1]),
-                                           f2(p.inv_std[c0], p.inv_std[c1]));
-                        v[2 * i + 1] = finish2(f2(a.z, a.w), f2(b.z, b.w), idy2, dy2, pre2,
-                                               f2(-p.mean[c2], -p.mean[c3]), f2(p.inv_std[c2], p.inv_std[c3]));
-                    }
-                    long long idx;
-                    if constexpr (LAYOUT == 0)
-                        idx = obase + static_cast<long long>((q * H + y) * W);
-                    else
-                        idx = obase + static_cast<long long>(y) * W * 3 + q * V;
-                    if (v_full) {
-                        store_chunk<DTYPE>(outp, idx, v);
-                    } else {
+                for (int i = 0; i < V / 4; ++i) {
+                    // NCHW bf16: the second 4 pixels of the group sit half_off floats further on.
+                    const int hoff = LAYOUT == 0 ? (q * plane + i * pl.half_off) : (q * V + 4 * i);
+                    const float4 a = *reinterpret_cast<const float4*>(ra + hoff);
+                    const float4 b = *reinterpret_cast<const float4*>(rb + hoff);
+                    const int c0 = LAYOUT == 0 ? q : (q * V + 4 * i + 0) % 3;
+                    const int c1 = LAYOUT == 0 ? q : (q * V + 4 * i + 1) % 3;
+                    const int c2 = LAYOUT == 0 ? q : (q * V + 4 * i + 2) % 3;
+                    const int c3 = LAYOUT == 0 ? q : (q * V + 4 * i + 3) % 3;
+                    v[2 * i] = finish2(f2(a.x, a.y), f2(b.x, b.y), idy2, dy2, pre2, f2(-p.mean[c0], -p.mean[c1]),
+                                       f2(p.inv_std[c0], p.inv_std[c1]));
+                    v[2 * i + 1] = finish2(f2(a.z, a.w), f2(b.z, b.w), idy2, dy2, pre2,
+                                           f2(-p.mean[c2], -p.mean[c3]), f2(p.inv_std[c2], p.inv_std[c3]));
+                }
+                long long idx;
+                if constexpr (LAYOUT == 0)
+                    idx = obase + static_cast<long long>((q * H + y) * W);
+                else
+                    idx = obase + static_cast<long long>(y) * W * 3 + q * V;
+                if (v_full) {
+                    store_chunk<DTYPE>(outp, idx, v);
+                } else {
 #pragma unroll
-                        for (int i = 0; i < V; ++i) {
-                            const float val = (i & 1) ? v[i >> 1].y : v[i >> 1].x;
-                            const bool in = LAYOUT == 0 ? (px0 + i < tcw) : (3 * px0 + q * V + i < 3 * tcw);
-                            if (in) store_scalar<DTYPE>(outp, idx + i, val);
-                        }
+                    for (int i = 0; i < V; ++i) {
+                        const float val = (i & 1) ? v[i >> 1].y : v[i >> 1].x;
+                        const bool in = LAYOUT == 0 ? (px0 + i < tcw) : (3 * px0 + q * V + i < 3 * tcw);
+                        if (in) store_scalar<DTYPE>(outp, idx + i, val);
                     }
                 }
             }
         }
-        yb = ynext;
-        buf ^= 1;
+    };
+
+    // Software pipeline: the h rows of pass i+1 are produced in the same barrier interval in
+    // which pass i is consumed (the ring is deep enough for both), so there is one CTA barrier
+    // per pass and the load-heavy H work and the math-heavy V work of different warps overlap.
+    __syncthreads();  // (P) tables of pass 0 visible
+    h_phase(0);
+    for (int i = 0;; ++i) {
+        __syncthreads();  // barrier i: h rows of pass i and tables of pass i+1 visible; pass i-1 consumed
+        const bool last = meta[i % 3].z != 0;
+        if (!last) h_phase(i + 1);
+        v_phase(i);
+        if (last) break;
     }
 }
 
@@ -505,7 +591,7 @@ std::atomic<unsigned long long> g_launches{0};
 template <int DTYPE, int LAYOUT>
 int launch_one(const FusedParams& p, cudaStream_t st) {
     auto kern = fused_transform_kernel<DTYPE, LAYOUT>;
-    kern<<<static_cast<unsigned>(p.plan.grid), p.plan.threads, p.plan.smem_bytes, st>>>(p);
+    kern<<<static_cast<unsigned>(p.plan.grid), ((p.plan.consumers + 31) & ~31) + kProducerThreads, p.plan.smem_bytes, st>>>(p);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return static_cast<int>(cudaGetLastError());
 }
