@@ -12,7 +12,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-LIB = os.path.join(HERE, "libturboloader_b200.so")
+LIB = os.environ.get("TLB_LIB") or os.path.join(HERE, "libturboloader_b200.so")
 SOURCES = ["fused_transform.cu", "capi.cu", "sharding.cpp"]
 HEADERS = ["fused_params.h", os.path.join("..", "..", "include", "turboloader_b200.h")]
 
@@ -20,7 +20,7 @@ NVCC_FLAGS = [
     "-std=c++20", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-O2",
-    "--fmad=false",  # belt and braces: every fp32 op in the kernels is an explicit _rn intrinsic anyway
+    "--fmad=false", *[f"-D{m}" for m in os.environ.get("TLB_DEFINES", "").split() if m],  # belt and braces: every fp32 op in the kernels is an explicit _rn intrinsic anyway
     "-shared", "-cudart", "static",
 ]
 

@@ -125,8 +125,10 @@ int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl) {
     pl.tile_cols = std::min(tlb::kMaxTileCols, round_up((W + pl.n_col_tiles - 1) / pl.n_col_tiles, 16));
     pl.n_col_tiles = (W + pl.tile_cols - 1) / pl.tile_cols;
     pl.consumers = (tlb::kMaxConsumers / pl.tile_cols) * pl.tile_cols;  // every compute thread owns one column
-    pl.tile_rows = std::clamp(env_int("TLB_TILE_ROWS", 32), 1, 1 << 20);
-    pl.tile_rows = std::min(pl.tile_rows, H);
+    // Row tiles of equal height, at most kMaxTileRows (or TLB_TILE_ROWS) rows each.
+    const int max_rows = std::clamp(env_int("TLB_TILE_ROWS", tlb::kMaxTileRows), 1, tlb::kMaxTileRows);
+    pl.n_row_tiles = (H + max_rows - 1) / max_rows;
+    pl.tile_rows = (H + pl.n_row_tiles - 1) / pl.n_row_tiles;
     pl.n_row_tiles = (H + pl.tile_rows - 1) / pl.tile_rows;
     // Widest source footprint of one column tile (crop-local columns) -> worst-case row pitch.
     long long fw = std::min<long long>(max_crop_w, (static_cast<long long>(pl.tile_cols) * max_crop_w + W - 1) / W + 3);
@@ -216,6 +218,7 @@ void fill_params(const tlb_transform_desc& d, tlb::FusedParams& p) {
         p.inv_std[c] = 1.0f / d.std[c];
     }
     p.pre_scale = d.normalize_01 ? (1.0f / 255.0f) : 1.0f;
+    p.one = 1.0f;
     p.status = d.status;
 }
 

@@ -46,6 +46,7 @@ struct FusedParams {
     float mean[3];
     float inv_std[3];  // 1.0f / std formed on the host in fp32 (direct_batch_loader.hpp:57)
     float pre_scale;   // 1/255 when normalize_01 else 1
+    float one;         // 1.0f, deliberately a run-time value (see add2_exact in the kernel)
     unsigned int* status;
     Plan plan;
 };
@@ -54,11 +55,13 @@ struct FusedParams {
 // from its own footprint width: two raw staging buffers of Rr rows each (double buffering)
 // and a ring of Rh = 2*Rr + 2 rows of horizontally-interpolated fp32 values.  The ring is that
 // deep so that the h rows of pass i+1 can be produced while pass i is still being consumed.
+constexpr int kMaxTileRows = 64;   // output rows per CTA (row tables are sized for this)
 constexpr int kSmemMbar = 0;       // 2 x 8 B mbarriers (one per raw buffer)
 constexpr int kSmemMeta = 16;      // 3 x int4 {output rows, new source rows, last pass?, first output row}
-constexpr int kSmemRowp = 64;      // 3 x 32 x float4 {h offset of y0 row, of y1 row, dy, 1-dy}
-constexpr int kSmemRowOff = 64 + 1536;         // 3 x 32 x int2 {raw byte offset, h float offset} per new row
-constexpr int kSmemVar = 64 + 1536 + 768 + 64; // = 2432, start of the carved region (128-byte multiple)
+constexpr int kSmemRowOff = 64;    // 3 x 32 x int2 {raw byte offset, h byte offset} per new source row of a pass
+constexpr int kSmemRowp = 64 + 768;            // kMaxTileRows x float4 {h byte offset of y0 row, of y1 row, dy, 1-dy}
+constexpr int kSmemRowY = 64 + 768 + 1024;     // kMaxTileRows x int2 {y0, y1} crop-local source rows
+constexpr int kSmemVar = 64 + 768 + 1024 + 512 + 64;  // = 2432, start of the carved region (128-byte multiple)
 
 inline __host__ __device__ int raw_rows_for(int var_bytes, int own_pitch, int hpitch) {
     int r = (var_bytes - 2 * hpitch * 4) / (2 * own_pitch + 2 * hpitch * 4);

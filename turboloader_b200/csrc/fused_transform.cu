@@ -117,6 +117,11 @@ __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b
 // fmad disabled (it flips ~1e-5 of the 8-bit codes and the last bit of most normalized
 // values).  So wherever a product feeds a sum, the sum is done with the scalar __fadd_rn,
 // which is never contracted; packed adds are used only where no product is an input.
+#ifdef TLB_NO_PACKED
+__device__ __forceinline__ float2 mul2_rn(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 add2_rn(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 add2_rz(float2 a, float2 b) { return make_float2(__fadd_rz(a.x, b.x), __fadd_rz(a.y, b.y)); }
+#else
 #define TLB_F32X2_OP(name, op)                                                                   \
     __device__ __forceinline__ float2 name(float2 a, float2 b) {                                 \
         float2 d;                                                                                \
@@ -130,9 +135,13 @@ TLB_F32X2_OP(mul2_rn, "mul.rn.f32x2")
 TLB_F32X2_OP(add2_rn, "add.rn.f32x2")
 TLB_F32X2_OP(add2_rz, "add.rz.f32x2")
 #undef TLB_F32X2_OP
+#endif
 // Packed FMA.  Used only where the fused result is exactly the wanted singly-rounded product
 // (see byte_product2).
 __device__ __forceinline__ float2 fma2_rn(float2 a, float2 b, float2 c) {
+#ifdef TLB_NO_PACKED
+    return make_float2(__fmaf_rn(a.x, b.x, c.x), __fmaf_rn(a.y, b.y, c.y));
+#endif
     float2 d;
     asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
         "mov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
@@ -149,10 +158,12 @@ __device__ __forceinline__ float2 fma2_rn(float2 a, float2 b, float2 c) {
 __device__ __forceinline__ float2 byte_product2(unsigned b0, unsigned b1, float2 w, float2 negw) {
     return fma2_rn(f2(__uint_as_float(b0 | 0x4B000000u), __uint_as_float(b1 | 0x4B000000u)), w, negw);
 }
-// Sum of two packed products, lane by lane, with scalar adds (see the caution above).
-__device__ __forceinline__ float2 add2_of_products(float2 a, float2 b) {
-    return f2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
-}
+// Packed sum a + b where a is a packed product: issued as fma(a, one, b) with `one` = 1.0f
+// held in a register the assembler cannot see through (it comes from the kernel parameters).
+// a*1 is exact, so the result is RN(a + b) lane by lane; and because the instruction already
+// is an FMA whose multiplicand is a finished (rounded) product, nothing can be contracted
+// into it.  This is what a packed add of products would be if it were safe (see above).
+__device__ __forceinline__ float2 add2_exact(float2 a, float2 b, float2 one) { return fma2_rn(a, one, b); }
 
 template <int DTYPE>
 struct OutT;
@@ -200,18 +211,17 @@ __device__ __forceinline__ void store_chunk(void* out, long long idx, const floa
 // to [0,255] before its uint8 cast cannot change the code: v is a convex blend of values in
 // [0,255], so 0 <= v < 256 always.
 __device__ __forceinline__ float2 finish2(float2 a, float2 b, float2 idy, float2 dy, float2 pre, float2 neg_mean,
-                                          float2 istd) {
+                                          float2 istd, float2 one) {
     const float2 k = f2(8388608.0f, 8388608.0f), nk = f2(-8388608.0f, -8388608.0f);
-    float2 v = add2_of_products(mul2_rn(a, idy), mul2_rn(b, dy));
-    v = add2_rn(add2_rz(v, k), nk);                                          // floor(v)
-    return mul2_rn(add2_of_products(mul2_rn(v, pre), neg_mean), istd);  // x - m == x + (-m) bit for bit
+    float2 v = add2_exact(mul2_rn(a, idy), mul2_rn(b, dy), one);
+    v = add2_rn(add2_rz(v, k), nk);                                        // floor(v)
+    return mul2_rn(add2_exact(mul2_rn(v, pre), neg_mean, one), istd);  // x - m == x + (-m) bit for bit
 }
 
 // Everything the producer warp needs to plan a pass and issue its copies.
 struct PassCtx {
-    int ty0, ty1, H, ch, iw, cx, cy, fx_lo, fw, Rr, Rh, pitch, hp;
+    int ty0, ty1, iw, cx, cy, fx_lo, fw, Rr, Rh, pitch, hp;
     bool pairs;  // vertical downscale steeper than 2x: output rows share no source row
-    float yscale;
     const unsigned char* img;
     unsigned long long reg_lo, reg_hi;
 };
@@ -224,67 +234,62 @@ struct PassState {
 };
 
 // Executed by all 32 lanes of the producer warp.  Plans the pass that starts at output row
-// st.yb: one lane per output row computes (y0, y1, dy); the first row's y0 and the last row's y1
-// are exchanged with warp shuffles to find the range of NEW source rows (rows the h ring does
-// not hold yet).  Writes the pass tables into slot (index % 3) of the header and issues one bulk
-// copy per new source row into raw buffer (index % 2).
+// st.yb from the per-tile row table (y0, y1 of every output row, computed once per tile): one
+// lane per output row; the first row's y0 and the last row's y1 are exchanged with warp
+// shuffles to find the range of NEW source rows (rows the h ring does not hold yet).  Writes
+// the pass record into slot (index % 3) of the header and issues one bulk copy per new source
+// row into raw buffer (index % 2).
 __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, unsigned char* smem,
                                                unsigned char* raw0, unsigned char* raw1, int lane) {
     const int slot3 = st.index % 3, buf = st.index & 1;
     int4* meta = reinterpret_cast<int4*>(smem + kSmemMeta);
-    float4* rowp = reinterpret_cast<float4*>(smem + kSmemRowp) + slot3 * 32;
     int2* rowoff = reinterpret_cast<int2*>(smem + kSmemRowOff) + slot3 * 32;
+    const int2* rowy = reinterpret_cast<const int2*>(smem + kSmemRowY);
     unsigned char* rawbuf = buf ? raw1 : raw0;
     const uint32_t mbar = smem_addr(smem + kSmemMbar + 8 * buf);
     const int yb = st.yb;
 
     const int y = yb + lane;
-    const float sy = src_coord(min(y, c.H - 1), c.yscale);
-    const int y0 = min(static_cast<int>(sy), c.ch - 1);
-    const int y1 = min(y0 + 1, c.ch - 1);
-    const float dy = __fsub_rn(sy, static_cast<float>(y0));
-    const int first = __shfl_sync(0xffffffffu, y0, 0);
+    const bool valid = y < c.ty1;
+    const int2 yy = rowy[min(y, c.ty1 - 1) - c.ty0];  // {y0, y1} of this lane's output row
     int nrows, nnew, new_first = 0;
     if (c.pairs) {
         nrows = min(c.Rr >> 1, min(c.ty1 - yb, 32));
         nnew = 2 * nrows;
     } else {
+        const int first = __shfl_sync(0xffffffffu, yy.x, 0);
         new_first = max(first, st.staged_last + 1);
         // Output rows whose source rows fit among the Rr rows this pass may add form a prefix
         // (y1 is non-decreasing in y).
-        const unsigned fits = __ballot_sync(0xffffffffu, (y < c.ty1) && (y1 - new_first + 1 <= c.Rr));
+        const unsigned fits = __ballot_sync(0xffffffffu, valid && (yy.y - new_first + 1 <= c.Rr));
         nrows = __popc(fits);
-        const int last_y1 = __shfl_sync(0xffffffffu, y1, nrows - 1);
+        const int last_y1 = __shfl_sync(0xffffffffu, yy.y, nrows - 1);
         nnew = max(last_y1 - new_first + 1, 0);
         st.staged_last = max(st.staged_last, last_y1);
     }
     const int ynext = yb + nrows;
     if (lane == 0) meta[slot3] = make_int4(nrows, nnew, ynext >= c.ty1 ? 1 : 0, yb);
-    if (lane < nrows) {
-        // Ring position of a source row: its row number (contiguous mode) or its sequence number
-        // 2*(y - ty0) + {0,1} (pairs mode), modulo the ring depth.
-        const int q0 = c.pairs ? 2 * (y - c.ty0) : y0;
-        const int q1 = c.pairs ? q0 + 1 : y1;
-        rowp[lane] = make_float4(__int_as_float((q0 % c.Rh) * c.hp), __int_as_float((q1 % c.Rh) * c.hp), dy,
-                                 __fsub_rn(1.0f, dy));
-    }
     const int j = lane;  // new source row staged by this lane
-    const int ya = __shfl_sync(0xffffffffu, y0, j >> 1);
-    const int yc = __shfl_sync(0xffffffffu, y1, j >> 1);
+    const int ya = __shfl_sync(0xffffffffu, yy.x, j >> 1);
+    const int yc = __shfl_sync(0xffffffffu, yy.y, j >> 1);
     const int srow = c.pairs ? ((j & 1) ? yc : ya) : (new_first + j);
-    const int q = c.pairs ? 2 * (yb - c.ty0) + j : srow;
+    // Ring position of a source row: its row number (contiguous mode) or its sequence number
+    // 2*(y - ty0) + {0,1} (pairs mode), modulo the ring depth -- the same rule the row table uses.
+    const int q0 = (c.pairs ? 2 * (yb - c.ty0) : new_first) % c.Rh;  // uniform
+    int q = q0 + j;
+    if (q >= c.Rh) q -= c.Rh;  // j < Rr <= Rh / 2
     unsigned bytes = 0;
     unsigned long long lo = 0, a0 = 0, a1 = 0, hi = 0;
     if (j < nnew) {
-        a0 = reinterpret_cast<unsigned long long>(c.img) +
-             (static_cast<unsigned long long>(c.cy + srow) * c.iw + (c.cx + c.fx_lo)) * 3ull;
-        a1 = a0 + static_cast<unsigned long long>(c.fw) * 3ull;
+        const unsigned off = (static_cast<unsigned>(c.cy + srow) * c.iw + (c.cx + c.fx_lo)) * 3u;
+        a0 = reinterpret_cast<unsigned long long>(c.img) + off;
+        a1 = a0 + static_cast<unsigned>(c.fw) * 3u;
         lo = a0 & ~15ull;
         if (lo < c.reg_lo) lo += 16;               // region does not start on the 16-byte grid
         hi = (a1 + 15ull) & ~15ull;
         if (hi > c.reg_hi) hi = c.reg_hi & ~15ull;  // region does not end on the 16-byte grid
         bytes = hi > lo ? static_cast<unsigned>(hi - lo) : 0u;
-        rowoff[j] = make_int2(j * c.pitch + static_cast<int>(a0 & 15ull), (q % c.Rh) * c.hp);
+        rowoff[j] = make_int2(j * c.pitch + static_cast<int>(a0 & 15ull), q * c.hp);
     }
     unsigned total = bytes;
 #pragma unroll
@@ -309,7 +314,10 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, 
 }
 
 template <int DTYPE, int LAYOUT>
-__global__ void __launch_bounds__(kMaxConsumers + kProducerThreads, 3)
+#ifndef TLB_MIN_CTAS
+#define TLB_MIN_CTAS 3
+#endif
+__global__ void __launch_bounds__(kMaxConsumers + kProducerThreads, TLB_MIN_CTAS)
 fused_transform_kernel(const __grid_constant__ FusedParams p) {
     constexpr int V = OutT<DTYPE>::V;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -358,7 +366,7 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         }
         const long long img_bytes = static_cast<long long>(iw) * ih * 3;
         if (iw <= 0 || ih <= 0 || cw <= 0 || ch <= 0 || cx < 0 || cy < 0 || cx > iw - cw || cy > ih - ch ||
-            img_off < 0 || static_cast<unsigned long long>(img_off) + img_bytes > p.src_bytes)
+            img_off < 0 || img_bytes > 0x7fffffffll || static_cast<unsigned long long>(img_off) + img_bytes > p.src_bytes)
             bad = kDevBadBox;
     }
     const bool flip = p.flips ? (p.flips[k] != 0) : false;
@@ -413,15 +421,29 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         mbar_init(smem_addr(smem + kSmemMbar + 8), 1);
         fence_proxy_async();
     }
+    // ---- row table of the tile: one thread per output row, once ------------------------
+    const bool pairs = ch > 2 * H;  // steeper than 2x: every output row has its own two source rows
+    if (tid < ty1 - ty0) {
+        const int y = ty0 + tid;
+        const float sy = src_coord(y, yscale);
+        const int y0 = min(static_cast<int>(sy), ch - 1);
+        const int y1 = min(y0 + 1, ch - 1);
+        const float dy = __fsub_rn(sy, static_cast<float>(y0));
+        // Ring slot of a source row: row number (or, in pairs mode, sequence number) modulo Rh.
+        const int q0 = pairs ? 2 * tid : y0;
+        const int q1 = pairs ? 2 * tid + 1 : y1;
+        reinterpret_cast<float4*>(smem + kSmemRowp)[tid] =
+            make_float4(__int_as_float((q0 % Rh) * hp), __int_as_float((q1 % Rh) * hp), dy, __fsub_rn(1.0f, dy));
+        reinterpret_cast<int2*>(smem + kSmemRowY)[tid] = make_int2(y0, y1);
+    }
     __syncthreads();
 
     if (producer) {
         // ================= producer warp: plan passes, issue copies, keep two passes ahead =========
         PassCtx pc;
-        pc.ty0 = ty0; pc.ty1 = ty1; pc.H = H; pc.ch = ch; pc.iw = iw; pc.cx = cx; pc.cy = cy;
+        pc.ty0 = ty0; pc.ty1 = ty1; pc.iw = iw; pc.cx = cx; pc.cy = cy;
         pc.fx_lo = fx_lo; pc.fw = fw; pc.Rr = Rr; pc.Rh = Rh; pc.pitch = own_pitch; pc.hp = hp;
-        pc.pairs = ch > 2 * H;
-        pc.yscale = yscale;
+        pc.pairs = pairs;
         pc.img = p.src + img_off;
         pc.reg_lo = reinterpret_cast<unsigned long long>(p.src);
         pc.reg_hi = pc.reg_lo + p.src_bytes;
@@ -475,6 +497,7 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
     const bool v_active = tid < nc && px0 < tcw;
     const bool v_full = pl.vec_ok && (px0 + V <= tcw);
     const float2 pre2 = f2(p.pre_scale, p.pre_scale);
+    const float2 one2 = f2(p.one, p.one);
     long long obase;                    // element index of (row 0, this group) of the sample
     if constexpr (LAYOUT == 0)
         obase = static_cast<long long>(k) * 3 * H * W + tx0 + px0;
@@ -497,6 +520,7 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
             if (p.status) atomicOr(p.status, kDevCopyTimeout);
             mbar_wait_bounded(mbar, parity);
         }
+#ifndef TLB_EXP_SKIP_H
         if (h_active) {
             const unsigned char* rawbuf = b ? raw1 : raw0;
             const int2* rowoff = reinterpret_cast<const int2*>(smem + kSmemRowOff) + (pi % 3) * 32;
@@ -520,13 +544,17 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
                 }
             }
         }
+#endif
     };
 
     // V phase of pass `pi`: blend the two h rows of every output row, finish, store.
     auto v_phase = [&](int pi) {
+#ifdef TLB_EXP_SKIP_V
+        return;
+#endif
         if (!v_active) return;
         const int4 m = meta[pi % 3];
-        const float4* rowp = reinterpret_cast<const float4*>(smem + kSmemRowp) + (pi % 3) * 32;
+        const float4* rowp = reinterpret_cast<const float4*>(smem + kSmemRowp) + (m.w - ty0);
         for (int l = vr; l < m.x; l += vgroups) {
             const float4 rp = rowp[l];
             const float2 dy2 = f2(rp.z, rp.z), idy2 = f2(rp.w, rp.w);
@@ -549,9 +577,9 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
                     const int c2 = LAYOUT == 0 ? q : (q * V + 4 * i + 2) % 3;
                     const int c3 = LAYOUT == 0 ? q : (q * V + 4 * i + 3) % 3;
                     v[2 * i] = finish2(f2(a.x, a.y), f2(b.x, b.y), idy2, dy2, pre2, f2(-p.mean[c0], -p.mean[c1]),
-                                       f2(p.inv_std[c0], p.inv_std[c1]));
+                                       f2(p.inv_std[c0], p.inv_std[c1]), one2);
                     v[2 * i + 1] = finish2(f2(a.z, a.w), f2(b.z, b.w), idy2, dy2, pre2,
-                                           f2(-p.mean[c2], -p.mean[c3]), f2(p.inv_std[c2], p.inv_std[c3]));
+                                           f2(-p.mean[c2], -p.mean[c3]), f2(p.inv_std[c2], p.inv_std[c3]), one2);
                 }
                 long long idx;
                 if constexpr (LAYOUT == 0)
