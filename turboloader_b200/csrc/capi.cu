@@ -122,9 +122,9 @@ int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl) {
     const int esz = d.out_dtype == TLB_F32 ? 4 : 2;
     const int V = 16 / esz;
     pl.n_col_tiles = (W + tlb::kMaxTileCols - 1) / tlb::kMaxTileCols;
-    pl.tile_cols = std::min(tlb::kMaxTileCols, round_up((W + pl.n_col_tiles - 1) / pl.n_col_tiles, 16));
+    pl.tile_cols = std::min(tlb::kMaxTileCols, round_up((W + pl.n_col_tiles - 1) / pl.n_col_tiles, tlb::kStripCols));
     pl.n_col_tiles = (W + pl.tile_cols - 1) / pl.tile_cols;
-    pl.consumers = (tlb::kMaxConsumers / pl.tile_cols) * pl.tile_cols;  // every compute thread owns one column
+    pl.strips = pl.tile_cols / tlb::kStripCols;  // one compute warp per 32 output columns
     // Row tiles of equal height, at most kMaxTileRows (or TLB_TILE_ROWS) rows each.
     const int max_rows = std::clamp(env_int("TLB_TILE_ROWS", tlb::kMaxTileRows), 1, tlb::kMaxTileRows);
     pl.n_row_tiles = (H + max_rows - 1) / max_rows;
@@ -133,30 +133,18 @@ int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl) {
     // Widest source footprint of one column tile (crop-local columns) -> worst-case row pitch.
     long long fw = std::min<long long>(max_crop_w, (static_cast<long long>(pl.tile_cols) * max_crop_w + W - 1) / W + 3);
     pl.pitch = round_up(static_cast<int>(fw) * 3 + 30, 16);
-    // Layout of one row of horizontally-interpolated values.  NCHW: three planes; for bf16 the
-    // odd 16-byte chunks of a plane live half_off floats further on (half_off = 16 mod 32) so that
-    // both the column-per-thread stores and the 8-pixels-per-thread loads are bank-conflict free.
-    pl.plane = pl.tile_cols;
-    pl.half_off = 0;
-    if (d.out_layout == TLB_NCHW && d.out_dtype == TLB_BF16) {
-        int ho = pl.tile_cols / 2;
-        ho += ((16 - ho % 32) + 32) % 32;
-        pl.half_off = ho;
-        pl.plane = ho + pl.tile_cols / 2;
-    }
-    pl.hpitch = d.out_layout == TLB_NCHW ? 3 * pl.plane : 3 * pl.tile_cols;
-    // Shared memory: a CTA stages Rr = (var - 2*hrow) / (2*own_pitch + 2*hrow) new source rows per
+    // Shared memory: a CTA stages Rr = (var - 2*hrow) / (2*own_pitch + hrow) new source rows per
     // pass, using its own (usually narrower) footprint pitch.  The widest crop gets >= kMinRows.
     constexpr int kMinRows = 4;
-    const int hrow = pl.hpitch * 4;
-    const int per_row_worst = 2 * pl.pitch + 2 * hrow;
+    const int hrow = pl.strips * tlb::kStripRowBytes;
+    const int per_row_worst = 2 * pl.pitch + hrow;
     const int budget = std::clamp(env_int("TLB_SMEM_BUDGET", 56 * 1024), 8 * 1024, 226 * 1024);
     int var = std::max(budget - tlb::kSmemVar, kMinRows * per_row_worst + 2 * hrow);
     var = std::min(var, tlb::kMaxNewRows * per_row_worst + 2 * hrow);
     pl.smem_bytes = tlb::kSmemVar + var;
     if (pl.smem_bytes > 227 * 1024) {
         pl.smem_bytes = 227 * 1024;
-        if (tlb::raw_rows_for(pl.smem_bytes - tlb::kSmemVar, pl.pitch, pl.hpitch) < 2)
+        if (tlb::raw_rows_for(pl.smem_bytes - tlb::kSmemVar, pl.pitch, pl.strips) < 2)
             return fail(TLB_ERR_TOO_WIDE, "crop width %d does not fit the shared-memory staging buffers", max_crop_w);
     }
     const bool base_ok = (reinterpret_cast<uintptr_t>(d.out) & 15u) == 0;
@@ -659,7 +647,7 @@ int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block
     tlb::Plan pl{};
     if (int rc = make_plan(*desc, mcw, pl)) return rc;
     if (grid) *grid = static_cast<int32_t>(pl.grid);
-    if (block) *block = ((pl.consumers + 31) & ~31) + tlb::kProducerThreads;
+    if (block) *block = 32 * (pl.strips + 1);
     if (smem_bytes) *smem_bytes = pl.smem_bytes;
     if (tile_rows) *tile_rows = pl.tile_rows;
     if (tile_cols) *tile_cols = pl.tile_cols;

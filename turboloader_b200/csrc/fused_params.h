@@ -5,22 +5,19 @@
 
 namespace tlb {
 
-constexpr int kMaxConsumers = 256; // compute threads per CTA = (256 / tile_cols) * tile_cols
-constexpr int kProducerThreads = 32; // one extra warp plans passes and issues the bulk copies
-constexpr int kMaxNewRows = 32;    // one producer lane issues the copy of one staged row
-constexpr int kMaxTileCols = 256;  // output columns per CTA
+constexpr int kStripCols = 32;     // output columns owned by one compute warp
+constexpr int kStripRowBytes = 400; // one h row of a strip: 3 x 32 floats + 16 B of bank stagger
+constexpr int kMaxNewRows = 32;    // one planner lane issues the copy of one new source row
+constexpr int kMaxTileCols = 256;  // output columns per CTA (8 strips)
 
 // Launch geometry chosen on the host from sizes only (never from device data).
 struct Plan {
     int tile_rows;    // output rows per CTA
-    int tile_cols;    // output columns per CTA (multiple of 16, <= kMaxTileCols)
+    int tile_cols;    // output columns per CTA (multiple of 32, <= kMaxTileCols)
     int n_col_tiles;  // ceil(dst_w / tile_cols)
     int n_row_tiles;  // ceil(dst_h / tile_rows)
-    int consumers;    // compute threads, a multiple of tile_cols; CTA size = consumers + 32
+    int strips;       // compute warps = tile_cols / 32; CTA size = 32 * (strips + 1)
     int pitch;        // bytes per staged raw row at the widest crop (multiple of 16)
-    int plane;        // NCHW: floats per channel plane of one h row (tile_cols, padded for bf16)
-    int half_off;     // NCHW bf16: float offset of the odd 16-byte chunks inside a plane (else 0)
-    int hpitch;       // floats per row of horizontally-interpolated values
     int smem_bytes;   // dynamic shared memory per CTA
     int vec_ok;       // 1: every 16-byte output chunk is aligned and whole -> vector stores
     long long grid;   // CTAs
@@ -52,19 +49,21 @@ struct FusedParams {
 };
 
 // Shared-memory layout.  A fixed header is followed by a region the CTA carves up itself
-// from its own footprint width: two raw staging buffers of Rr rows each (double buffering)
-// and a ring of Rh = 2*Rr + 2 rows of horizontally-interpolated fp32 values.  The ring is that
-// deep so that the h rows of pass i+1 can be produced while pass i is still being consumed.
+// from its own footprint width: two raw staging buffers of Rr source rows each (double
+// buffering, filled by bulk async copies) and, per 32-column strip, a ring of Rh = Rr + 2 rows
+// of horizontally-interpolated fp32 values (kStripRowBytes each).
 constexpr int kMaxTileRows = 64;   // output rows per CTA (row tables are sized for this)
-constexpr int kSmemMbar = 0;       // 2 x 8 B mbarriers (one per raw buffer)
-constexpr int kSmemMeta = 16;      // 3 x int4 {output rows, new source rows, last pass?, first output row}
-constexpr int kSmemRowOff = 64;    // 3 x 32 x int2 {raw byte offset, h byte offset} per new source row of a pass
-constexpr int kSmemRowp = 64 + 768;            // kMaxTileRows x float4 {h byte offset of y0 row, of y1 row, dy, 1-dy}
-constexpr int kSmemRowY = 64 + 768 + 1024;     // kMaxTileRows x int2 {y0, y1} crop-local source rows
-constexpr int kSmemVar = 64 + 768 + 1024 + 512 + 64;  // = 2432, start of the carved region (128-byte multiple)
+constexpr int kSmemFull = 0;       // 2 x 8 B mbarriers: raw buffer b filled (transaction count)
+constexpr int kSmemEmpty = 16;     // 2 x 8 B mbarriers: raw buffer b consumed by every compute warp
+constexpr int kSmemMeta = 32;      // 3 x int4 {output rows, new source rows, last pass?, first output row}
+constexpr int kSmemRowOff = 128;   // 3 x 32 x int2 {raw byte offset, ring byte offset} per new source row of a pass
+constexpr int kSmemRowp = 128 + 768;           // kMaxTileRows x float4 {ring byte offset of y0 row, of y1 row, dy, 1-dy}
+constexpr int kSmemRowY = 128 + 768 + 1024;    // kMaxTileRows x int2 {y0, y1} crop-local source rows
+constexpr int kSmemVar = 128 + 768 + 1024 + 512;  // = 2432, start of the carved region (128-byte multiple)
 
-inline __host__ __device__ int raw_rows_for(int var_bytes, int own_pitch, int hpitch) {
-    int r = (var_bytes - 2 * hpitch * 4) / (2 * own_pitch + 2 * hpitch * 4);
+inline __host__ __device__ int raw_rows_for(int var_bytes, int own_pitch, int strips) {
+    const int hrow = strips * kStripRowBytes;
+    int r = (var_bytes - 2 * hrow) / (2 * own_pitch + hrow);
     return r > kMaxNewRows ? kMaxNewRows : r;
 }
 

@@ -13,26 +13,26 @@
 // Every multiply and add is a separately rounded fp32 operation (no FMA contraction),
 // in the CPU path's order, so fp32 output is bit-identical to it.
 //
-// Structure of one CTA = one tile of `tile_rows` x `tile_cols` outputs of one sample,
-// processed in passes of at most R staged source rows (R is what fits in shared memory
-// for this tile's own footprint width):
-//   1. warp 0 plans the pass: one lane per output row computes (y0, y1, dy); the first and
-//      last rows are exchanged with warp shuffles to find the contiguous range of source
-//      rows (or, for a >2x vertical downscale, the exact (y0, y1) pairs).  It then issues
-//      one 1-D bulk async copy (cp.async.bulk, global -> this CTA's shared memory,
-//      completion on an mbarrier) per source row, each rounded out to 16-byte boundaries.
-//      Bytes that cannot be reached on a 16-byte grid inside the readable region are
-//      fetched with plain loads.  Raw rows are double buffered: the copies of pass i+1
-//      are in flight while pass i is computed.
-//   2. "H" phase: every staged row is interpolated horizontally once,
-//      h = p[x0]*(1-dx) + p[x1]*dx, into fp32 in shared memory.  Each thread owns one
-//      output column for the whole tile and keeps its weights in registers.
-//   3. "V" phase: each thread owns a group of 4 (fp32) or 8 (bf16) adjacent pixels and
-//      walks down the rows of the pass: v = h[y0]*(1-dy) + h[y1]*dy, truncate, normalize,
-//      cast, three 16-byte stores per row.  The layout of h in shared memory (planar for
-//      NCHW, interleaved for NHWC) makes every input a 16-byte shared load.  The fp32
-//      arithmetic uses the packed two-lane forms (mul/add .f32x2) of sm_100; they round
-//      each lane exactly like the scalar instructions.
+// Structure of one CTA = one tile of `tile_rows` x `tile_cols` outputs of one sample.  One
+// warp per 32-column strip computes; one more warp only plans and copies.  No CTA-wide barrier
+// is used after the prologue: the warps meet through mbarriers only.
+//   planner warp: walks down the tile in passes of at most Rr NEW source rows (rows the strips
+//      do not hold yet).  One lane per output row looks up (y0, y1) in a per-tile row table; the
+//      first and last rows are exchanged with warp shuffles to find the range of new rows.  It
+//      issues one 1-D bulk async copy (cp.async.bulk, global -> this CTA's shared memory,
+//      completion on a "full" mbarrier) per new source row, each rounded out to 16-byte
+//      boundaries; bytes that cannot be reached on a 16-byte grid inside the readable region are
+//      fetched with plain loads.  Raw rows are double buffered; a buffer is refilled once every
+//      compute warp has arrived on its "empty" mbarrier.
+//   compute warp, "H" step: every new source row is interpolated horizontally once,
+//      h = p[x0]*(1-dx) + p[x1]*dx, into a ring of fp32 rows private to the strip.  Each lane owns
+//      one output column for the whole tile and keeps its weights in registers.
+//   compute warp, "V" step: each lane owns 4 (fp32) or 8 (bf16) adjacent pixels of the strip and
+//      the warp covers 8 / 4 output rows at a time: v = h[y0]*(1-dy) + h[y1]*dy, truncate,
+//      normalize, cast, three 16-byte stores per row.  The layout of a ring row (planar for
+//      NCHW, interleaved for NHWC, rows staggered by 16 bytes) makes every input a
+//      conflict-free 16-byte shared load.  The fp32 arithmetic uses the packed two-lane forms
+//      (mul/fma .f32x2) of sm_100; they round each lane exactly like the scalar instructions.
 // The bilinear blend is exactly separable in this order (top and bot depend on one
 // source row each), so sharing h between neighbouring output rows changes no bit.
 //
@@ -44,6 +44,7 @@
 
 #include <atomic>
 #include <cstdint>
+#include <type_traits>
 
 #include "fused_params.h"
 
@@ -184,11 +185,11 @@ __device__ __forceinline__ void store_scalar(void* out, long long idx, float v) 
         static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
 }
 
-// One 16-byte store of V consecutive output elements starting at element index idx.
+// One 16-byte store of V finished outputs (fp32: 4 values, bf16: 8 values rounded RNE).
 template <int DTYPE>
-__device__ __forceinline__ void store_chunk(void* out, long long idx, const float2* v) {
+__device__ __forceinline__ void store_chunk(char* ptr, const float2* v) {
     if constexpr (DTYPE == 0) {
-        *reinterpret_cast<float4*>(static_cast<float*>(out) + idx) = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
+        *reinterpret_cast<float4*>(ptr) = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
     } else {
         uint4 u;
         __nv_bfloat162 a = __float22bfloat162_rn(v[0]);
@@ -199,7 +200,7 @@ __device__ __forceinline__ void store_chunk(void* out, long long idx, const floa
         u.y = *reinterpret_cast<uint32_t*>(&b);
         u.z = *reinterpret_cast<uint32_t*>(&c);
         u.w = *reinterpret_cast<uint32_t*>(&d);
-        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out) + idx) = u;
+        *reinterpret_cast<uint4*>(ptr) = u;
     }
 }
 
@@ -218,27 +219,31 @@ __device__ __forceinline__ float2 finish2(float2 a, float2 b, float2 idy, float2
     return mul2_rn(add2_exact(mul2_rn(v, pre), neg_mean, one), istd);  // x - m == x + (-m) bit for bit
 }
 
-// Everything the producer warp needs to plan a pass and issue its copies.
+// Plain (release) arrival on an mbarrier.
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar) : "memory");
+}
+
+// Everything the planner warp needs to plan a pass and issue its copies.
 struct PassCtx {
-    int ty0, ty1, iw, cx, cy, fx_lo, fw, Rr, Rh, pitch, hp;
+    int ty0, ty1, iw, cx, cy, fx_lo, fw, Rr, Rh, pitch, rpi;
     bool pairs;  // vertical downscale steeper than 2x: output rows share no source row
     const unsigned char* img;
     unsigned long long reg_lo, reg_hi;
 };
 
-// Producer state carried from one pass to the next (uniform across the warp).
+// Planner state carried from one pass to the next (uniform across the warp).
 struct PassState {
     int yb;           // first output row of the next pass to plan
-    int staged_last;  // last source row already present in the h ring (contiguous mode), or -1
+    int staged_last;  // last source row already present in the strips' rings (contiguous mode), or -1
     int index;        // number of passes planned so far
 };
 
-// Executed by all 32 lanes of the producer warp.  Plans the pass that starts at output row
-// st.yb from the per-tile row table (y0, y1 of every output row, computed once per tile): one
-// lane per output row; the first row's y0 and the last row's y1 are exchanged with warp
-// shuffles to find the range of NEW source rows (rows the h ring does not hold yet).  Writes
-// the pass record into slot (index % 3) of the header and issues one bulk copy per new source
-// row into raw buffer (index % 2).
+// Executed by all 32 lanes of the planner warp.  Plans the pass that starts at output row st.yb
+// from the per-tile row table: one lane per output row; the first row's y0 and the last row's
+// y1 are exchanged with warp shuffles to find the range of NEW source rows.  Writes the pass
+// record into slot (index % 3) of the header and issues one bulk copy per new source row into
+// raw buffer (index % 2), completing on that buffer's "full" mbarrier.
 __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, unsigned char* smem,
                                                unsigned char* raw0, unsigned char* raw1, int lane) {
     const int slot3 = st.index % 3, buf = st.index & 1;
@@ -246,7 +251,7 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, 
     int2* rowoff = reinterpret_cast<int2*>(smem + kSmemRowOff) + slot3 * 32;
     const int2* rowy = reinterpret_cast<const int2*>(smem + kSmemRowY);
     unsigned char* rawbuf = buf ? raw1 : raw0;
-    const uint32_t mbar = smem_addr(smem + kSmemMbar + 8 * buf);
+    const uint32_t mbar = smem_addr(smem + kSmemFull + 8 * buf);
     const int yb = st.yb;
 
     const int y = yb + lane;
@@ -255,6 +260,7 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, 
     int nrows, nnew, new_first = 0;
     if (c.pairs) {
         nrows = min(c.Rr >> 1, min(c.ty1 - yb, 32));
+        if (nrows > c.rpi) nrows -= nrows % c.rpi;
         nnew = 2 * nrows;
     } else {
         const int first = __shfl_sync(0xffffffffu, yy.x, 0);
@@ -263,6 +269,8 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, 
         // (y1 is non-decreasing in y).
         const unsigned fits = __ballot_sync(0xffffffffu, valid && (yy.y - new_first + 1 <= c.Rr));
         nrows = __popc(fits);
+        // Whole groups of `rpi` rows keep every lane of the V step busy; the tile's tail is exempt.
+        if (nrows > c.rpi && yb + nrows < c.ty1) nrows -= nrows % c.rpi;
         const int last_y1 = __shfl_sync(0xffffffffu, yy.y, nrows - 1);
         nnew = max(last_y1 - new_first + 1, 0);
         st.staged_last = max(st.staged_last, last_y1);
@@ -277,7 +285,7 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, 
     // 2*(y - ty0) + {0,1} (pairs mode), modulo the ring depth -- the same rule the row table uses.
     const int q0 = (c.pairs ? 2 * (yb - c.ty0) : new_first) % c.Rh;  // uniform
     int q = q0 + j;
-    if (q >= c.Rh) q -= c.Rh;  // j < Rr <= Rh / 2
+    if (q >= c.Rh) q -= c.Rh;  // j < Rr < Rh
     unsigned bytes = 0;
     unsigned long long lo = 0, a0 = 0, a1 = 0, hi = 0;
     if (j < nnew) {
@@ -289,19 +297,11 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, 
         hi = (a1 + 15ull) & ~15ull;
         if (hi > c.reg_hi) hi = c.reg_hi & ~15ull;  // region does not end on the 16-byte grid
         bytes = hi > lo ? static_cast<unsigned>(hi - lo) : 0u;
-        rowoff[j] = make_int2(j * c.pitch + static_cast<int>(a0 & 15ull), q * c.hp);
-    }
-    unsigned total = bytes;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-    fence_proxy_async();  // earlier generic reads of this staging buffer precede the new copies
-    if (lane == 0) mbar_arrive_expect_tx(mbar, total);
-    __syncwarp();
-    if (j < nnew) {
+        rowoff[j] = make_int2(j * c.pitch + static_cast<int>(a0 & 15ull), q * kStripRowBytes);
+        // Ragged edges outside the 16-byte grid of the readable region (rare): plain loads, stored
+        // before the arrival below so that the "full" barrier publishes them too.
         unsigned char* slot = rawbuf + j * c.pitch;
         const unsigned long long origin = a0 & ~15ull;  // global address of slot byte 0
-        if (bytes) bulk_copy_g2s(smem_addr(slot + (lo - origin)), reinterpret_cast<const void*>(lo), bytes, mbar);
-        // Ragged edges outside the 16-byte grid of the readable region (rare).
         const unsigned long long head_end = bytes ? lo : a1;
         for (unsigned long long a = a0; a < head_end && a < a1; ++a)
             slot[a - origin] = *reinterpret_cast<const unsigned char*>(a);
@@ -309,26 +309,35 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, 
             for (unsigned long long a = (hi > a0 ? hi : a0); a < a1; ++a)
                 slot[a - origin] = *reinterpret_cast<const unsigned char*>(a);
     }
+    unsigned total = bytes;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    fence_proxy_async();  // earlier generic reads of this staging buffer precede the new copies
+    __syncwarp();         // the record and the row offsets are written before the arrival publishes them
+    if (lane == 0) mbar_arrive_expect_tx(mbar, total);
+    __syncwarp();
+    if (j < nnew) {
+        unsigned char* slot = rawbuf + j * c.pitch;
+        const unsigned long long origin = a0 & ~15ull;  // global address of slot byte 0
+        if (bytes) bulk_copy_g2s(smem_addr(slot + (lo - origin)), reinterpret_cast<const void*>(lo), bytes, mbar);
+    }
     st.yb = ynext;
     st.index += 1;
 }
 
 template <int DTYPE, int LAYOUT>
-#ifndef TLB_MIN_CTAS
-#define TLB_MIN_CTAS 3
-#endif
-__global__ void __launch_bounds__(kMaxConsumers + kProducerThreads, TLB_MIN_CTAS)
+__global__ void __launch_bounds__(32 * (kMaxTileCols / kStripCols + 1))
 fused_transform_kernel(const __grid_constant__ FusedParams p) {
-    constexpr int V = OutT<DTYPE>::V;
+    constexpr int V = OutT<DTYPE>::V;       // outputs per 16-byte chunk
+    constexpr int G = kStripCols / V;       // pixel groups per strip row (8 fp32, 4 bf16)
+    constexpr int RPI = 32 / G;             // output rows one V step covers (4 fp32, 8 bf16)
+    constexpr int ESZ = DTYPE == 0 ? 4 : 2;
     extern __shared__ __align__(128) unsigned char smem[];
     const Plan& pl = p.plan;
     const int tid = threadIdx.x;
     const int lane = tid & 31;
-    const int nc = pl.consumers;
-    // The last warp plans passes and issues copies.  It starts on a warp boundary; compute threads
-    // are tid < nc, and threads in between (nc not a multiple of 32) only take part in barriers.
-    const int pbase = (nc + 31) & ~31;
-    const bool producer = tid >= pbase;
+    const int warp = tid >> 5;
+    const int strips = pl.strips;
 
     // ---- which tile of which sample ------------------------------------------------
     unsigned bid = blockIdx.x;
@@ -366,7 +375,8 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         }
         const long long img_bytes = static_cast<long long>(iw) * ih * 3;
         if (iw <= 0 || ih <= 0 || cw <= 0 || ch <= 0 || cx < 0 || cy < 0 || cx > iw - cw || cy > ih - ch ||
-            img_off < 0 || img_bytes > 0x7fffffffll || static_cast<unsigned long long>(img_off) + img_bytes > p.src_bytes)
+            img_off < 0 || img_bytes > 0x7fffffffll ||
+            static_cast<unsigned long long>(img_off) + img_bytes > p.src_bytes)
             bad = kDevBadBox;
     }
     const bool flip = p.flips ? (p.flips[k] != 0) : false;
@@ -382,14 +392,13 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
     const int oxa = flip ? (W - 1 - (tx0 + tcw - 1)) : tx0;
     const int oxb = flip ? (W - 1 - tx0) : (tx0 + tcw - 1);
     int fx_lo = 0, fw = 0, own_pitch = 16, Rr = 0;
-    const int hp = pl.hpitch, tcp = pl.tile_cols;
     if (!bad) {
         fx_lo = min(static_cast<int>(src_coord(oxa, xscale)), cw - 1);
         const int hi0 = min(static_cast<int>(src_coord(oxb, xscale)), cw - 1);
         const int fx_hi = min(hi0 + 1, cw - 1);
         fw = fx_hi - fx_lo + 1;
         own_pitch = (fw * 3 + 30 + 15) & ~15;
-        Rr = raw_rows_for(pl.smem_bytes - kSmemVar, own_pitch, hp);
+        Rr = raw_rows_for(pl.smem_bytes - kSmemVar, own_pitch, strips);
         if (Rr < 2) bad = kDevTooWide;
     }
 
@@ -410,15 +419,17 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
     }
 
     // ---- carve the variable part of shared memory for this tile's footprint ----------
-    const int Rh = 2 * Rr + 2;
+    const int Rh = Rr + 2;  // ring depth: the new rows of a pass plus at most two carried rows
     unsigned char* raw0 = smem + kSmemVar;
     unsigned char* raw1 = raw0 + Rr * own_pitch;
-    float* hbuf = reinterpret_cast<float*>(raw1 + Rr * own_pitch);
+    unsigned char* rings = raw1 + Rr * own_pitch;  // strips x Rh x kStripRowBytes
     const int4* meta = reinterpret_cast<const int4*>(smem + kSmemMeta);
 
     if (tid == 0) {
-        mbar_init(smem_addr(smem + kSmemMbar), 1);
-        mbar_init(smem_addr(smem + kSmemMbar + 8), 1);
+        mbar_init(smem_addr(smem + kSmemFull), 1);
+        mbar_init(smem_addr(smem + kSmemFull + 8), 1);
+        mbar_init(smem_addr(smem + kSmemEmpty), strips);
+        mbar_init(smem_addr(smem + kSmemEmpty + 8), strips);
         fence_proxy_async();
     }
     // ---- row table of the tile: one thread per output row, once ------------------------
@@ -433,42 +444,45 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         const int q0 = pairs ? 2 * tid : y0;
         const int q1 = pairs ? 2 * tid + 1 : y1;
         reinterpret_cast<float4*>(smem + kSmemRowp)[tid] =
-            make_float4(__int_as_float((q0 % Rh) * hp), __int_as_float((q1 % Rh) * hp), dy, __fsub_rn(1.0f, dy));
+            make_float4(__int_as_float((q0 % Rh) * kStripRowBytes), __int_as_float((q1 % Rh) * kStripRowBytes), dy,
+                        __fsub_rn(1.0f, dy));
         reinterpret_cast<int2*>(smem + kSmemRowY)[tid] = make_int2(y0, y1);
     }
-    __syncthreads();
+    __syncthreads();  // the only CTA-wide barrier: tables and mbarriers are ready
 
-    if (producer) {
-        // ================= producer warp: plan passes, issue copies, keep two passes ahead =========
+    if (warp == strips) {
+        // ================= planner warp =================================================================
         PassCtx pc;
         pc.ty0 = ty0; pc.ty1 = ty1; pc.iw = iw; pc.cx = cx; pc.cy = cy;
-        pc.fx_lo = fx_lo; pc.fw = fw; pc.Rr = Rr; pc.Rh = Rh; pc.pitch = own_pitch; pc.hp = hp;
+        pc.fx_lo = fx_lo; pc.fw = fw; pc.Rr = Rr; pc.Rh = Rh; pc.pitch = own_pitch; pc.rpi = RPI;
         pc.pairs = pairs;
         pc.img = p.src + img_off;
         pc.reg_lo = reinterpret_cast<unsigned long long>(p.src);
         pc.reg_hi = pc.reg_lo + p.src_bytes;
         PassState st;
         st.yb = ty0; st.staged_last = -1; st.index = 0;
-        plan_and_issue(pc, st, smem, raw0, raw1, lane);              // pass 0
-        __syncthreads();                                              // (P) tables of pass 0 visible
-        if (st.yb < ty1) plan_and_issue(pc, st, smem, raw0, raw1, lane);  // pass 1
-        // Main loop: after barrier i the raw buffer and table slot of pass i+2 are free.
-        for (int i = 0;; ++i) {
-            __syncthreads();                                          // barrier i
-            if (meta[i % 3].z) break;                                 // pass i is the last one
-            if (st.index == i + 2 && st.yb < ty1) plan_and_issue(pc, st, smem, raw0, raw1, lane);
+        plan_and_issue(pc, st, smem, raw0, raw1, lane);                       // pass 0 -> buffer 0
+        if (st.yb < ty1) plan_and_issue(pc, st, smem, raw0, raw1, lane);  // pass 1 -> buffer 1
+        while (st.yb < ty1) {
+            // Pass n reuses the raw buffer (and, one pass later, the record slot) of pass n-2: wait
+            // until every compute warp has finished reading that buffer.
+            const int n = st.index;
+            const uint32_t mb = smem_addr(smem + kSmemEmpty + 8 * (n & 1));
+            if (!mbar_wait_bounded(mb, static_cast<uint32_t>((n >> 1) - 1) & 1u)) {
+                if (lane == 0 && p.status) atomicOr(p.status, kDevCopyTimeout);
+            }
+            plan_and_issue(pc, st, smem, raw0, raw1, lane);
         }
         return;
     }
 
-    // ================= consumer warps ==============================================================
-    // ---- H-phase ownership: one output column per thread, weights in registers -------
-    const int hx = tid % tcp;          // column inside the tile
-    const int hg = tid / tcp;          // row group of this thread
-    const int hgroups = nc / tcp;
+    // ================= compute warps: one 32-column strip each ===========================================
+    unsigned char* ring = rings + warp * Rh * kStripRowBytes;
+    // ---- H step ownership: one output column per lane, weights in registers ---------
+    const int hx = warp * kStripCols + lane;  // column inside the tile
     int off0 = 0, off1 = 0;
-    float2 wx = f2(0.0f, 0.0f);        // (1-dx, dx)
-    const bool h_active = tid < nc && hx < tcw;
+    float2 wx = f2(0.0f, 0.0f);                // (1-dx, dx)
+    const bool h_active = hx < tcw;
     if (h_active) {
         const int x = tx0 + hx;
         const int ox = flip ? (W - 1 - x) : x;
@@ -481,62 +495,83 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         wx = f2(__fsub_rn(1.0f, dx), dx);
     }
     const float2 nwx = f2(__fmul_rn(-8388608.0f, wx.x), __fmul_rn(-8388608.0f, wx.y));
-    // Position of this thread's column inside one h row.
-    int hpos;
-    if constexpr (LAYOUT == 0)
-        hpos = (DTYPE == 1) ? (((hx >> 2) & 1) * pl.half_off + (hx >> 3) * 4 + (hx & 3)) : hx;
-    else
-        hpos = 3 * hx;
-    const int plane = pl.plane;
-    // ---- V-phase ownership: V adjacent pixels, three 16-byte chunks per row ------------
-    const int gp = tcp / V;            // pixel groups per tile row
-    const int vg = tid % gp;
-    const int vr = tid / gp;
-    const int vgroups = nc / gp;
-    const int px0 = vg * V;            // first pixel of the group inside the tile
-    const bool v_active = tid < nc && px0 < tcw;
+    // Ring row layout.  NCHW: three planes of 32 floats.  NHWC: 32 x 3 interleaved floats.
+    float* const h_store = reinterpret_cast<float*>(ring) + (LAYOUT == 0 ? lane : 3 * lane);
+    // ---- V step ownership: V adjacent pixels x RPI rows per step ------------------------
+    const int vg = lane % G;
+    const int vr = lane / G;
+    const int px0 = warp * kStripCols + vg * V;  // first pixel of the group inside the tile
+    const bool v_active = px0 < tcw;
     const bool v_full = pl.vec_ok && (px0 + V <= tcw);
     const float2 pre2 = f2(p.pre_scale, p.pre_scale);
     const float2 one2 = f2(p.one, p.one);
-    long long obase;                    // element index of (row 0, this group) of the sample
+    long long obase;                              // element index of (row 0, this group) of the sample
     if constexpr (LAYOUT == 0)
         obase = static_cast<long long>(k) * 3 * H * W + tx0 + px0;
     else
         obase = (static_cast<long long>(k) * H * W + tx0 + px0) * 3;
-    // Float offset of this group's first 16-byte chunk inside an h row (plane 0 for NCHW).
-    const int vpos = LAYOUT == 0 ? vg * 4 : 3 * px0;
+    // Byte offset of this group's first 16-byte chunk inside a ring row (plane 0 for NCHW).
+    const unsigned char* const h_load = ring + (LAYOUT == 0 ? vg * V * 4 : vg * V * 12);
     void* const outp = p.out;
+    char* const obytes = static_cast<char*>(p.out) + obase * ESZ;
+    const long long row_bytes = static_cast<long long>(W) * ESZ * (LAYOUT == 0 ? 1 : 3);
+    const long long chan_bytes = static_cast<long long>(H) * W * ESZ;  // NCHW plane stride
+    const float4* const rowp_tile = reinterpret_cast<const float4*>(smem + kSmemRowp);
 
-    // H phase of pass `pi`: wait for its copies, interpolate its new source rows into the ring.
-    auto h_phase = [&](int pi) {
-        const int4 m = meta[pi % 3];
-        const int b = pi & 1;
-        const uint32_t mbar = smem_addr(smem + kSmemMbar + 8 * b);
-        const uint32_t parity = static_cast<uint32_t>(pi >> 1) & 1u;
-        if (!mbar_wait_bounded(mbar, parity)) {
-            // The copies did not land within the time limit.  Report it and give them one more
-            // bounded chance; the CTA then carries on (every later wait is bounded too) so that no
-            // thread leaves while others sit at a barrier.  The status word marks the output invalid.
-            if (p.status) atomicOr(p.status, kDevCopyTimeout);
-            mbar_wait_bounded(mbar, parity);
+    // One 16-byte chunk q of an output row: blend the two ring rows ra / rb, truncate, normalize.
+    // NCHW: chunk q = channel q of the group's V pixels.  NHWC: chunk q = elements [q*V, q*V+V) of
+    // the group's 3V interleaved elements (element e has channel e % 3).
+    auto chunk = [&](const unsigned char* ra, const unsigned char* rb, float2 idy2, float2 dy2, auto qc, float2* v) {
+        constexpr int q = decltype(qc)::value;
+#pragma unroll
+        for (int i = 0; i < V / 4; ++i) {
+            constexpr int base = LAYOUT == 0 ? q * kStripCols * 4 : q * V * 4;
+            const float4 a = *reinterpret_cast<const float4*>(ra + base + 16 * i);
+            const float4 b = *reinterpret_cast<const float4*>(rb + base + 16 * i);
+            const int c0 = LAYOUT == 0 ? q : (q * V + 4 * i + 0) % 3;
+            const int c1 = LAYOUT == 0 ? q : (q * V + 4 * i + 1) % 3;
+            const int c2 = LAYOUT == 0 ? q : (q * V + 4 * i + 2) % 3;
+            const int c3 = LAYOUT == 0 ? q : (q * V + 4 * i + 3) % 3;
+            v[2 * i] = finish2(f2(a.x, a.y), f2(b.x, b.y), idy2, dy2, pre2, f2(-p.mean[c0], -p.mean[c1]),
+                               f2(p.inv_std[c0], p.inv_std[c1]), one2);
+            v[2 * i + 1] = finish2(f2(a.z, a.w), f2(b.z, b.w), idy2, dy2, pre2, f2(-p.mean[c2], -p.mean[c3]),
+                                   f2(p.inv_std[c2], p.inv_std[c3]), one2);
         }
+    };
+
+    for (int i = 0;; ++i) {
+        // ---- wait for the raw rows of pass i ---------------------------------------------
+        const int b = i & 1;
+        const uint32_t full = smem_addr(smem + kSmemFull + 8 * b);
+        if (!mbar_wait_bounded(full, static_cast<uint32_t>(i >> 1) & 1u)) {
+            // The copies did not land within the time limit.  Report it and give them one more
+            // bounded chance; the warp then carries on (every later wait is bounded too).  The
+            // status word marks the output invalid.
+            if (lane == 0 && p.status) atomicOr(p.status, kDevCopyTimeout);
+            mbar_wait_bounded(full, static_cast<uint32_t>(i >> 1) & 1u);
+        }
+        const int4 m = meta[i % 3];  // {output rows, new source rows, last?, first output row}
+
+        // ---- H step: new source rows -> horizontally interpolated fp32 in the strip's ring ----
 #ifndef TLB_EXP_SKIP_H
         if (h_active) {
-            const unsigned char* rawbuf = b ? raw1 : raw0;
-            const int2* rowoff = reinterpret_cast<const int2*>(smem + kSmemRowOff) + (pi % 3) * 32;
+            const unsigned char* rawb = b ? raw1 : raw0;
+            const unsigned char* tap0 = rawb + off0;
+            const unsigned char* tap1 = rawb + off1;
+            const int2* rowoff = reinterpret_cast<const int2*>(smem + kSmemRowOff) + (i % 3) * 32;
 #pragma unroll 2
-            for (int j = hg; j < m.y; j += hgroups) {
-                const int2 ro = rowoff[j];
-                const unsigned char* q0 = rawbuf + ro.x + off0;
-                const unsigned char* q1 = rawbuf + ro.x + off1;
+            for (int j = 0; j < m.y; ++j) {
+                const int2 ro = rowoff[j];  // {raw byte offset of the row, byte offset of its ring slot}
+                const unsigned char* q0 = tap0 + ro.x;
+                const unsigned char* q1 = tap1 + ro.x;
                 const float2 t0 = byte_product2(q0[0], q1[0], wx, nwx);
                 const float2 t1 = byte_product2(q0[1], q1[1], wx, nwx);
                 const float2 t2 = byte_product2(q0[2], q1[2], wx, nwx);
-                float* h = hbuf + ro.y + hpos;
+                float* h = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(h_store) + ro.y);
                 if constexpr (LAYOUT == 0) {
                     h[0] = __fadd_rn(t0.x, t0.y);
-                    h[plane] = __fadd_rn(t1.x, t1.y);
-                    h[2 * plane] = __fadd_rn(t2.x, t2.y);
+                    h[kStripCols] = __fadd_rn(t1.x, t1.y);
+                    h[2 * kStripCols] = __fadd_rn(t2.x, t2.y);
                 } else {
                     h[0] = __fadd_rn(t0.x, t0.y);
                     h[1] = __fadd_rn(t1.x, t1.y);
@@ -545,72 +580,62 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
             }
         }
 #endif
-    };
+        __syncwarp();  // the strip's new h rows are visible to the whole warp; raw reads are done
+        if (lane == 0) mbar_arrive(smem_addr(smem + kSmemEmpty + 8 * b));  // this warp is done with raw buffer b
 
-    // V phase of pass `pi`: blend the two h rows of every output row, finish, store.
-    auto v_phase = [&](int pi) {
-#ifdef TLB_EXP_SKIP_V
-        return;
-#endif
-        if (!v_active) return;
-        const int4 m = meta[pi % 3];
-        const float4* rowp = reinterpret_cast<const float4*>(smem + kSmemRowp) + (m.w - ty0);
-        for (int l = vr; l < m.x; l += vgroups) {
-            const float4 rp = rowp[l];
-            const float2 dy2 = f2(rp.z, rp.z), idy2 = f2(rp.w, rp.w);
-            const int y = m.w + l;
-            const float* ra = hbuf + __float_as_int(rp.x) + vpos;
-            const float* rb = hbuf + __float_as_int(rp.y) + vpos;
-#pragma unroll
-            for (int q = 0; q < 3; ++q) {
-                // NCHW: chunk q = channel q of the group's V pixels.  NHWC: chunk q = elements
-                // [q*V, q*V+V) of the group's 3V interleaved elements (element e has channel e % 3).
-                float2 v[V / 2];
-#pragma unroll
-                for (int i = 0; i < V / 4; ++i) {
-                    // NCHW bf16: the second 4 pixels of the group sit half_off floats further on.
-                    const int hoff = LAYOUT == 0 ? (q * plane + i * pl.half_off) : (q * V + 4 * i);
-                    const float4 a = *reinterpret_cast<const float4*>(ra + hoff);
-                    const float4 b = *reinterpret_cast<const float4*>(rb + hoff);
-                    const int c0 = LAYOUT == 0 ? q : (q * V + 4 * i + 0) % 3;
-                    const int c1 = LAYOUT == 0 ? q : (q * V + 4 * i + 1) % 3;
-                    const int c2 = LAYOUT == 0 ? q : (q * V + 4 * i + 2) % 3;
-                    const int c3 = LAYOUT == 0 ? q : (q * V + 4 * i + 3) % 3;
-                    v[2 * i] = finish2(f2(a.x, a.y), f2(b.x, b.y), idy2, dy2, pre2, f2(-p.mean[c0], -p.mean[c1]),
-                                       f2(p.inv_std[c0], p.inv_std[c1]), one2);
-                    v[2 * i + 1] = finish2(f2(a.z, a.w), f2(b.z, b.w), idy2, dy2, pre2,
-                                           f2(-p.mean[c2], -p.mean[c3]), f2(p.inv_std[c2], p.inv_std[c3]), one2);
+        // ---- V step: blend, truncate, normalize, store --------------------------------------
+#ifndef TLB_EXP_SKIP_V
+        if (v_active) {
+            const float4* rowp = rowp_tile + (m.w - ty0);
+            if (v_full) {
+                char* orow = obytes + (m.w + vr) * row_bytes;
+                const long long ostep = RPI * row_bytes;
+                for (int l = vr; l < m.x; l += RPI, orow += ostep) {
+                    const float4 rp = rowp[l];  // {ring byte offset of y0 row, of y1 row, dy, 1-dy}
+                    const float2 dy2 = f2(rp.z, rp.z), idy2 = f2(rp.w, rp.w);
+                    const unsigned char* ra = h_load + __float_as_int(rp.x);
+                    const unsigned char* rb = h_load + __float_as_int(rp.y);
+                    float2 v[V / 2];
+                    chunk(ra, rb, idy2, dy2, std::integral_constant<int, 0>{}, v);
+                    store_chunk<DTYPE>(orow, v);
+                    chunk(ra, rb, idy2, dy2, std::integral_constant<int, 1>{}, v);
+                    store_chunk<DTYPE>(orow + (LAYOUT == 0 ? chan_bytes : 16), v);
+                    chunk(ra, rb, idy2, dy2, std::integral_constant<int, 2>{}, v);
+                    store_chunk<DTYPE>(orow + (LAYOUT == 0 ? 2 * chan_bytes : 32), v);
                 }
-                long long idx;
-                if constexpr (LAYOUT == 0)
-                    idx = obase + static_cast<long long>((q * H + y) * W);
-                else
-                    idx = obase + static_cast<long long>(y) * W * 3 + q * V;
-                if (v_full) {
-                    store_chunk<DTYPE>(outp, idx, v);
-                } else {
+            } else {
+                // Ragged or unaligned rows: element-wise guarded stores.
+                for (int l = vr; l < m.x; l += RPI) {
+                    const float4 rp = rowp[l];
+                    const float2 dy2 = f2(rp.z, rp.z), idy2 = f2(rp.w, rp.w);
+                    const unsigned char* ra = h_load + __float_as_int(rp.x);
+                    const unsigned char* rb = h_load + __float_as_int(rp.y);
+                    const int y = m.w + l;
+                    auto emit = [&](auto qc) {
+                        constexpr int q = decltype(qc)::value;
+                        float2 v[V / 2];
+                        chunk(ra, rb, idy2, dy2, qc, v);
+                        long long idx;
+                        if constexpr (LAYOUT == 0)
+                            idx = obase + static_cast<long long>((q * H + y) * W);
+                        else
+                            idx = obase + static_cast<long long>(y) * W * 3 + q * V;
 #pragma unroll
-                    for (int i = 0; i < V; ++i) {
-                        const float val = (i & 1) ? v[i >> 1].y : v[i >> 1].x;
-                        const bool in = LAYOUT == 0 ? (px0 + i < tcw) : (3 * px0 + q * V + i < 3 * tcw);
-                        if (in) store_scalar<DTYPE>(outp, idx + i, val);
-                    }
+                        for (int e = 0; e < V; ++e) {
+                            const float val = (e & 1) ? v[e >> 1].y : v[e >> 1].x;
+                            const bool in = LAYOUT == 0 ? (px0 + e < tcw) : (3 * px0 + q * V + e < 3 * tcw);
+                            if (in) store_scalar<DTYPE>(outp, idx + e, val);
+                        }
+                    };
+                    emit(std::integral_constant<int, 0>{});
+                    emit(std::integral_constant<int, 1>{});
+                    emit(std::integral_constant<int, 2>{});
                 }
             }
         }
-    };
-
-    // Software pipeline: the h rows of pass i+1 are produced in the same barrier interval in
-    // which pass i is consumed (the ring is deep enough for both), so there is one CTA barrier
-    // per pass and the load-heavy H work and the math-heavy V work of different warps overlap.
-    __syncthreads();  // (P) tables of pass 0 visible
-    h_phase(0);
-    for (int i = 0;; ++i) {
-        __syncthreads();  // barrier i: h rows of pass i and tables of pass i+1 visible; pass i-1 consumed
-        const bool last = meta[i % 3].z != 0;
-        if (!last) h_phase(i + 1);
-        v_phase(i);
-        if (last) break;
+#endif
+        if (m.z) break;
+        __syncwarp();  // every lane has consumed pass i before the ring slots are rewritten
     }
 }
 
@@ -619,7 +644,7 @@ std::atomic<unsigned long long> g_launches{0};
 template <int DTYPE, int LAYOUT>
 int launch_one(const FusedParams& p, cudaStream_t st) {
     auto kern = fused_transform_kernel<DTYPE, LAYOUT>;
-    kern<<<static_cast<unsigned>(p.plan.grid), ((p.plan.consumers + 31) & ~31) + kProducerThreads, p.plan.smem_bytes, st>>>(p);
+    kern<<<static_cast<unsigned>(p.plan.grid), 32 * (p.plan.strips + 1), p.plan.smem_bytes, st>>>(p);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return static_cast<int>(cudaGetLastError());
 }
