@@ -133,11 +133,11 @@ int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl) {
     // Widest source footprint of one column tile (crop-local columns) -> worst-case row pitch.
     long long fw = std::min<long long>(max_crop_w, (static_cast<long long>(pl.tile_cols) * max_crop_w + W - 1) / W + 3);
     pl.pitch = round_up(static_cast<int>(fw) * 3 + 30, 16);
-    // Shared memory: a CTA stages Rr = (var - 2*hrow) / (2*own_pitch + hrow) new source rows per
+    // Shared memory: a CTA stages Rr = (var - 2*hrow) / (kNBuf*own_pitch + hrow) new source rows per
     // pass, using its own (usually narrower) footprint pitch.  The widest crop gets >= kMinRows.
     constexpr int kMinRows = 4;
     const int hrow = pl.strips * tlb::kStripRowBytes;
-    const int per_row_worst = 2 * pl.pitch + hrow;
+    const int per_row_worst = tlb::kNBuf * pl.pitch + hrow;
     const int budget = std::clamp(env_int("TLB_SMEM_BUDGET", 56 * 1024), 8 * 1024, 226 * 1024);
     int var = std::max(budget - tlb::kSmemVar, kMinRows * per_row_worst + 2 * hrow);
     var = std::min(var, tlb::kMaxNewRows * per_row_worst + 2 * hrow);
@@ -255,7 +255,6 @@ public:
         std::unique_lock<std::mutex> lk(mu_);
         done_cv_.wait(lk, [this] { return busy_ == 0; });
     }
-    size_t threads() const { return workers_.size() + 1; }
 
 private:
     Pool() {

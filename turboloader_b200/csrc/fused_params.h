@@ -49,21 +49,27 @@ struct FusedParams {
 };
 
 // Shared-memory layout.  A fixed header is followed by a region the CTA carves up itself
-// from its own footprint width: two raw staging buffers of Rr source rows each (double
-// buffering, filled by bulk async copies) and, per 32-column strip, a ring of Rh = Rr + 2 rows
+// from its own footprint width: kNBuf raw staging buffers of Rr source rows each (filled by
+// bulk async copies, the planner runs that many passes ahead) and, per 32-column strip, a ring of Rh = Rr + 2 rows
 // of horizontally-interpolated fp32 values (kStripRowBytes each).
 constexpr int kMaxTileRows = 64;   // output rows per CTA (row tables are sized for this)
-constexpr int kSmemFull = 0;       // 2 x 8 B mbarriers: raw buffer b filled (transaction count)
-constexpr int kSmemEmpty = 16;     // 2 x 8 B mbarriers: raw buffer b consumed by every compute warp
-constexpr int kSmemMeta = 32;      // 3 x int4 {output rows, new source rows, last pass?, first output row}
-constexpr int kSmemRowOff = 128;   // 3 x 32 x int2 {raw byte offset, ring byte offset} per new source row of a pass
-constexpr int kSmemRowp = 128 + 768;           // kMaxTileRows x float4 {ring byte offset of y0 row, of y1 row, dy, 1-dy}
-constexpr int kSmemRowY = 128 + 768 + 1024;    // kMaxTileRows x int2 {y0, y1} crop-local source rows
-constexpr int kSmemVar = 128 + 768 + 1024 + 512;  // = 2432, start of the carved region (128-byte multiple)
+#ifndef TLB_NBUF
+#define TLB_NBUF 3
+#endif
+constexpr int kNBuf = TLB_NBUF;    // raw staging buffers = passes the planner may run ahead (<= 4)
+constexpr int kSlots = kNBuf + 1;  // pass records kept (a record outlives its raw buffer by one pass)
+constexpr int kSmemFull = 0;       // kNBuf x 8 B mbarriers: raw buffer b filled (transaction count)
+constexpr int kSmemEmpty = 32;     // kNBuf x 8 B mbarriers: raw buffer b consumed by every compute warp
+constexpr int kSmemMeta = 64;      // kSlots x int4 {output rows, new source rows, last pass?, first output row}
+constexpr int kSmemRowOff = 256;   // kSlots x 32 x int2 {raw byte offset, ring byte offset} per new source row of a pass
+constexpr int kSmemRowp = 256 + 1280;          // kMaxTileRows x float4 {ring byte offset of y0 row, of y1 row, dy, 1-dy}
+constexpr int kSmemRowY = 256 + 1280 + 1024;   // kMaxTileRows x int2 {y0, y1} crop-local source rows
+constexpr int kSmemVar = 256 + 1280 + 1024 + 512;  // = 3072, start of the carved region (128-byte multiple)
+static_assert(kNBuf >= 2 && kNBuf <= 4 && kSlots * 256 <= 1280, "header slots are sized for at most 4 buffers");
 
 inline __host__ __device__ int raw_rows_for(int var_bytes, int own_pitch, int strips) {
     const int hrow = strips * kStripRowBytes;
-    int r = (var_bytes - 2 * hrow) / (2 * own_pitch + hrow);
+    int r = (var_bytes - 2 * hrow) / (kNBuf * own_pitch + hrow);
     return r > kMaxNewRows ? kMaxNewRows : r;
 }
 

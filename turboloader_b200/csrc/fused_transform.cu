@@ -242,15 +242,15 @@ struct PassState {
 // Executed by all 32 lanes of the planner warp.  Plans the pass that starts at output row st.yb
 // from the per-tile row table: one lane per output row; the first row's y0 and the last row's
 // y1 are exchanged with warp shuffles to find the range of NEW source rows.  Writes the pass
-// record into slot (index % 3) of the header and issues one bulk copy per new source row into
-// raw buffer (index % 2), completing on that buffer's "full" mbarrier.
+// record into slot (index % kSlots) of the header and issues one bulk copy per new source row
+// into raw buffer (index % kNBuf), completing on that buffer's "full" mbarrier.
 __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, unsigned char* smem,
-                                               unsigned char* raw0, unsigned char* raw1, int lane) {
-    const int slot3 = st.index % 3, buf = st.index & 1;
+                                               unsigned char* raw, int lane) {
+    const int slot3 = st.index % kSlots, buf = st.index % kNBuf;
     int4* meta = reinterpret_cast<int4*>(smem + kSmemMeta);
     int2* rowoff = reinterpret_cast<int2*>(smem + kSmemRowOff) + slot3 * 32;
     const int2* rowy = reinterpret_cast<const int2*>(smem + kSmemRowY);
-    unsigned char* rawbuf = buf ? raw1 : raw0;
+    unsigned char* rawbuf = raw + buf * c.Rr * c.pitch;
     const uint32_t mbar = smem_addr(smem + kSmemFull + 8 * buf);
     const int yb = st.yb;
 
@@ -420,16 +420,15 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
 
     // ---- carve the variable part of shared memory for this tile's footprint ----------
     const int Rh = Rr + 2;  // ring depth: the new rows of a pass plus at most two carried rows
-    unsigned char* raw0 = smem + kSmemVar;
-    unsigned char* raw1 = raw0 + Rr * own_pitch;
-    unsigned char* rings = raw1 + Rr * own_pitch;  // strips x Rh x kStripRowBytes
+    unsigned char* raw = smem + kSmemVar;                    // kNBuf buffers of Rr x own_pitch bytes
+    unsigned char* rings = raw + kNBuf * Rr * own_pitch;    // strips x Rh x kStripRowBytes
     const int4* meta = reinterpret_cast<const int4*>(smem + kSmemMeta);
 
     if (tid == 0) {
-        mbar_init(smem_addr(smem + kSmemFull), 1);
-        mbar_init(smem_addr(smem + kSmemFull + 8), 1);
-        mbar_init(smem_addr(smem + kSmemEmpty), strips);
-        mbar_init(smem_addr(smem + kSmemEmpty + 8), strips);
+        for (int b = 0; b < kNBuf; ++b) {
+            mbar_init(smem_addr(smem + kSmemFull + 8 * b), 1);
+            mbar_init(smem_addr(smem + kSmemEmpty + 8 * b), strips);
+        }
         fence_proxy_async();
     }
     // ---- row table of the tile: one thread per output row, once ------------------------
@@ -461,17 +460,16 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         pc.reg_hi = pc.reg_lo + p.src_bytes;
         PassState st;
         st.yb = ty0; st.staged_last = -1; st.index = 0;
-        plan_and_issue(pc, st, smem, raw0, raw1, lane);                       // pass 0 -> buffer 0
-        if (st.yb < ty1) plan_and_issue(pc, st, smem, raw0, raw1, lane);  // pass 1 -> buffer 1
+        for (int n = 0; n < kNBuf && st.yb < ty1; ++n) plan_and_issue(pc, st, smem, raw, lane);  // passes 0 .. kNBuf-1
         while (st.yb < ty1) {
-            // Pass n reuses the raw buffer (and, one pass later, the record slot) of pass n-2: wait
-            // until every compute warp has finished reading that buffer.
+            // Pass n reuses the raw buffer of pass n - kNBuf: wait until every compute warp has
+            // finished reading that buffer.
             const int n = st.index;
-            const uint32_t mb = smem_addr(smem + kSmemEmpty + 8 * (n & 1));
-            if (!mbar_wait_bounded(mb, static_cast<uint32_t>((n >> 1) - 1) & 1u)) {
+            const uint32_t mb = smem_addr(smem + kSmemEmpty + 8 * (n % kNBuf));
+            if (!mbar_wait_bounded(mb, static_cast<uint32_t>(n / kNBuf - 1) & 1u)) {
                 if (lane == 0 && p.status) atomicOr(p.status, kDevCopyTimeout);
             }
-            plan_and_issue(pc, st, smem, raw0, raw1, lane);
+            plan_and_issue(pc, st, smem, raw, lane);
         }
         return;
     }
@@ -541,24 +539,25 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
 
     for (int i = 0;; ++i) {
         // ---- wait for the raw rows of pass i ---------------------------------------------
-        const int b = i & 1;
+        const int b = i % kNBuf;
         const uint32_t full = smem_addr(smem + kSmemFull + 8 * b);
-        if (!mbar_wait_bounded(full, static_cast<uint32_t>(i >> 1) & 1u)) {
+        const uint32_t full_parity = static_cast<uint32_t>(i / kNBuf) & 1u;
+        if (!mbar_wait_bounded(full, full_parity)) {
             // The copies did not land within the time limit.  Report it and give them one more
             // bounded chance; the warp then carries on (every later wait is bounded too).  The
             // status word marks the output invalid.
             if (lane == 0 && p.status) atomicOr(p.status, kDevCopyTimeout);
-            mbar_wait_bounded(full, static_cast<uint32_t>(i >> 1) & 1u);
+            mbar_wait_bounded(full, full_parity);
         }
-        const int4 m = meta[i % 3];  // {output rows, new source rows, last?, first output row}
+        const int4 m = meta[i % kSlots];  // {output rows, new source rows, last?, first output row}
 
         // ---- H step: new source rows -> horizontally interpolated fp32 in the strip's ring ----
 #ifndef TLB_EXP_SKIP_H
         if (h_active) {
-            const unsigned char* rawb = b ? raw1 : raw0;
+            const unsigned char* rawb = raw + b * Rr * own_pitch;
             const unsigned char* tap0 = rawb + off0;
             const unsigned char* tap1 = rawb + off1;
-            const int2* rowoff = reinterpret_cast<const int2*>(smem + kSmemRowOff) + (i % 3) * 32;
+            const int2* rowoff = reinterpret_cast<const int2*>(smem + kSmemRowOff) + (i % kSlots) * 32;
 #pragma unroll 2
             for (int j = 0; j < m.y; ++j) {
                 const int2 ro = rowoff[j];  // {raw byte offset of the row, byte offset of its ring slot}
