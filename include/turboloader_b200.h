@@ -156,6 +156,36 @@ TLB_API int tlb_crop_resize_normalize_to_device(const tlb_image_ref* imgs, const
                                                 int32_t normalize_01, void* out_dev, int32_t out_dtype,
                                                 int32_t out_layout, uint32_t* status_dev, void* stream);
 
+/* Allocation-free form of tlb_crop_resize_normalize_to_device.  It has no counterpart in
+ * the reference.  It exists for callers that are not allowed to allocate device or pinned
+ * memory at the point of the call -- a loader thread running inside a training process whose
+ * memory pool is already sized to the GPU, a real-time or embedded host that forbids
+ * allocation after start-up, a process sharing the GPU under a fixed memory budget.  This entry
+ * point calls no cudaMalloc / cudaMallocHost / cudaFree and no allocating library routine: the
+ * packed crop pixels and the per-sample tables are staged in one fixed device array that lives
+ * in the library image (TLB_STATIC_SCRATCH_BYTES, held by every GPU that loads the library
+ * until the process exits), and the host pixels are copied straight from the caller's memory.
+ *
+ * Limits: n <= TLB_STATIC_MAX_SAMPLES, and the packed crops (each crop's w*h*3 bytes rounded up
+ * to 16) plus 33 bytes of tables per sample must fit TLB_STATIC_SCRATCH_BYTES; otherwise
+ * TLB_ERR_TOO_LARGE is returned and nothing is enqueued.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
+ * opts the kernels in to large shared memory; make that first call outside any stream capture.
+ * Every call on a device uses the same array: it keeps the previous call's bytes (nothing in it
+ * needs to start at zero -- each call overwrites what it reads), and two calls whose GPU work
+ * overlaps (different streams, or concurrent host threads) race on it.  Issue the calls of one
+ * device on one stream, one host thread at a time.  The tables are built in a fixed host buffer
+ * of the library, which is a second reason for that rule.  Same arguments and results as
+ * tlb_crop_resize_normalize_to_device. */
+#define TLB_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+#define TLB_STATIC_MAX_SAMPLES 4096
+TLB_API int tlb_crop_resize_normalize_to_device_static(const tlb_image_ref* imgs, const tlb_crop_params* crops,
+                                                       int32_t n, int32_t dst_h, int32_t dst_w,
+                                                       const float mean[3], const float std_[3],
+                                                       int32_t normalize_01, void* out_dev, int32_t out_dtype,
+                                                       int32_t out_layout, uint32_t* status_dev, void* stream);
+
 /* ---- resident-dataset forms returning a library-owned device pointer -------------------
  * normalize_resident_batch / normalize_resident_gather_batch
  * (cuda_transforms.hpp:49-55): src_dev = [N,H,W,3] uint8 on the device; returns the

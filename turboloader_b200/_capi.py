@@ -15,6 +15,8 @@ ERR_NAMES = {1: "INVALID_ARG", 2: "BAD_BOX", 3: "BAD_INDEX", 4: "TOO_WIDE", 5: "
              7: "TOO_LARGE"}
 TLB_F32, TLB_BF16 = 0, 1
 TLB_NCHW, TLB_NHWC = 0, 1
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024  # TLB_STATIC_SCRATCH_BYTES
+STATIC_MAX_SAMPLES = 4096                # TLB_STATIC_MAX_SAMPLES
 DEV_BAD_INDEX, DEV_BAD_BOX, DEV_TOO_WIDE, DEV_COPY_TIMEOUT = 1, 2, 4, 8
 
 
@@ -99,6 +101,8 @@ def load() -> C.CDLL:
     lib.tlb_crop_resize_normalize_to_device.argtypes = [C.POINTER(ImageRef), C.POINTER(CropParams), C.c_int32,
                                                         C.c_int32, C.c_int32, _F3, _F3, C.c_int32, C.c_void_p,
                                                         C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+    lib.tlb_crop_resize_normalize_to_device_static.restype = C.c_int
+    lib.tlb_crop_resize_normalize_to_device_static.argtypes = lib.tlb_crop_resize_normalize_to_device.argtypes
     lib.tlb_normalize_resident_batch.restype = C.c_size_t
     lib.tlb_normalize_resident_batch.argtypes = [C.c_size_t, C.c_int32, C.c_int32, C.c_int32, _F3, _F3]
     lib.tlb_normalize_resident_gather_batch.restype = C.c_size_t

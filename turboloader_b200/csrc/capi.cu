@@ -656,3 +656,142 @@ int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block
 uint64_t tlb_launch_count(void) { return tlb::launch_count(); }
 
 }  // extern "C"
+
+// ---- allocation-free host-image entry point ------------------------------------------------
+// Some callers may not allocate when they call us: a loader thread inside a process whose
+// device memory is already fully committed to a training pool, a host that forbids
+// allocation after start-up, a GPU shared under a fixed memory budget.  For them the device
+// staging that tlb_crop_resize_normalize_to_device takes from a growable ring lives here in
+// one fixed array of the library image, and the tables are built in a fixed host buffer.
+namespace {
+
+// Device scratch shared by every call on a device; it keeps the last call's bytes.  In host
+// code this name is only a handle for the symbol, not a device address: the address each
+// device gave the array is looked up once with cudaGetSymbolAddress (below) and passed to the
+// kernel as its source pointer.
+static __device__ __align__(256) unsigned char g_static_scratch[TLB_STATIC_SCRATCH_BYTES];
+
+unsigned char* g_static_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device
+std::mutex g_static_mu;
+
+// Fixed host-side staging for the per-sample tables (no heap use on the success path).
+struct StaticTables {
+    long long offs[TLB_STATIC_MAX_SAMPLES];
+    int sizes[2 * TLB_STATIC_MAX_SAMPLES];
+    int boxes[4 * TLB_STATIC_MAX_SAMPLES];
+    unsigned char flips[TLB_STATIC_MAX_SAMPLES];
+    IntBox rect[TLB_STATIC_MAX_SAMPLES];
+};
+StaticTables g_static_tables;
+
+// First use on a device, with that device current: find where the array lives there.
+int static_scratch_address(int dev, unsigned char** out) {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_addr[dev]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        g_static_addr[dev] = static_cast<unsigned char*>(ptr);
+    }
+    *out = g_static_addr[dev];
+    return TLB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tlb_crop_resize_normalize_to_device_static(const tlb_image_ref* imgs, const tlb_crop_params* crops, int32_t n,
+                                               int32_t dst_h, int32_t dst_w, const float mean[3],
+                                               const float std_[3], int32_t normalize_01, void* out_dev,
+                                               int32_t out_dtype, int32_t out_layout, uint32_t* status_dev,
+                                               void* stream) {
+    if (n <= 0) return fail(TLB_ERR_INVALID_ARG, "empty image list");
+    if (!imgs || !mean || !std_ || !out_dev) return fail(TLB_ERR_INVALID_ARG, "NULL argument");
+    if (dst_h <= 0 || dst_w <= 0) return fail(TLB_ERR_INVALID_ARG, "dst size must be positive");
+    if (n > TLB_STATIC_MAX_SAMPLES)
+        return fail(TLB_ERR_TOO_LARGE, "n = %d exceeds the %d samples the allocation-free entry point supports", n,
+                    TLB_STATIC_MAX_SAMPLES);
+    StaticTables& t = g_static_tables;
+    // ---- validate every crop on the host and lay the packed crops out ------------------------
+    size_t pix = 0;
+    int max_cw = 1;
+    for (int i = 0; i < n; ++i) {
+        if (!imgs[i].data || imgs[i].w <= 0 || imgs[i].h <= 0)
+            return fail(TLB_ERR_INVALID_ARG, "image %d: NULL data or non-positive size", i);
+        IntBox b{0, 0, imgs[i].w, imgs[i].h, 0};
+        if (crops) {
+            const tlb_crop_params& c = crops[i];
+            if (c.x != std::floor(c.x) || c.y != std::floor(c.y) || c.w != std::floor(c.w) || c.h != std::floor(c.h))
+                return fail(TLB_ERR_INVALID_ARG, "crop %d: (%g,%g,%g,%g) must be whole pixels", i, c.x, c.y, c.w, c.h);
+            b = IntBox{static_cast<int>(c.x), static_cast<int>(c.y), static_cast<int>(c.w), static_cast<int>(c.h), c.flip != 0};
+            if (b.w <= 0 || b.h <= 0 || b.x < 0 || b.y < 0 || b.x > imgs[i].w - b.w || b.y > imgs[i].h - b.h)
+                return fail(TLB_ERR_BAD_BOX, "crop %d: (%d,%d,%d,%d) leaves the %dx%d image", i, b.x, b.y, b.w, b.h, imgs[i].w, imgs[i].h);
+        }
+        t.rect[i] = b;
+        t.offs[i] = static_cast<long long>(pix);
+        t.sizes[2 * i] = b.w;
+        t.sizes[2 * i + 1] = b.h;
+        t.boxes[4 * i] = 0;
+        t.boxes[4 * i + 1] = 0;
+        t.boxes[4 * i + 2] = b.w;
+        t.boxes[4 * i + 3] = b.h;
+        t.flips[i] = static_cast<unsigned char>(b.flip);
+        pix += (static_cast<size_t>(b.w) * b.h * 3 + 15) & ~static_cast<size_t>(15);
+        max_cw = std::max(max_cw, b.w);
+    }
+    const size_t off_tab = pix;                        // int64 offsets[n]
+    const size_t size_tab = off_tab + 8 * size_t(n);   // int32 sizes[n][2]
+    const size_t box_tab = size_tab + 8 * size_t(n);   // int32 boxes[n][4]
+    const size_t flip_tab = box_tab + 16 * size_t(n);  // u8 flips[n]
+    const size_t total = (flip_tab + n + 15) & ~static_cast<size_t>(15);
+    if (total > TLB_STATIC_SCRATCH_BYTES)
+        return fail(TLB_ERR_TOO_LARGE,
+                    "batch needs %zu bytes of device staging; the allocation-free entry point has %u (use "
+                    "tlb_crop_resize_normalize_to_device or split the batch)",
+                    total, static_cast<unsigned>(TLB_STATIC_SCRATCH_BYTES));
+    // ---- one-time set-up on this device (no allocation: address look-up + kernel attributes) --
+    int dev;
+    if (int rc = current_device(&dev)) return rc;
+    unsigned char* base = nullptr;
+    if (int rc = static_scratch_address(dev, &base)) return rc;
+    if (int rc = ensure_prepared(g_dev[dev])) return rc;
+    // ---- copy the crop rectangles straight from the caller's memory, then the tables ----------
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    for (int i = 0; i < n; ++i) {
+        const IntBox& b = t.rect[i];
+        const unsigned char* src = imgs[i].data + (static_cast<size_t>(b.y) * imgs[i].w + b.x) * 3;
+        TLB_CUDA(cudaMemcpy2DAsync(base + t.offs[i], static_cast<size_t>(b.w) * 3, src, static_cast<size_t>(imgs[i].w) * 3,
+                                   static_cast<size_t>(b.w) * 3, static_cast<size_t>(b.h), cudaMemcpyHostToDevice, cs));
+    }
+    TLB_CUDA(cudaMemcpyAsync(base + off_tab, t.offs, 8 * size_t(n), cudaMemcpyHostToDevice, cs));
+    TLB_CUDA(cudaMemcpyAsync(base + size_tab, t.sizes, 8 * size_t(n), cudaMemcpyHostToDevice, cs));
+    TLB_CUDA(cudaMemcpyAsync(base + box_tab, t.boxes, 16 * size_t(n), cudaMemcpyHostToDevice, cs));
+    TLB_CUDA(cudaMemcpyAsync(base + flip_tab, t.flips, size_t(n), cudaMemcpyHostToDevice, cs));
+
+    tlb_transform_desc d{};
+    d.src = base;
+    d.src_bytes = pix;
+    d.n_src = n;
+    d.src_offsets = reinterpret_cast<const int64_t*>(base + off_tab);
+    d.src_sizes = reinterpret_cast<const int32_t*>(base + size_tab);
+    d.n = n;
+    d.boxes = reinterpret_cast<const int32_t*>(base + box_tab);
+    d.flips = base + flip_tab;
+    d.dst_h = dst_h;
+    d.dst_w = dst_w;
+    d.out = out_dev;
+    d.out_dtype = out_dtype;
+    d.out_layout = out_layout;
+    for (int c = 0; c < 3; ++c) {
+        d.mean[c] = mean[c];
+        d.std[c] = std_[c];
+    }
+    d.normalize_01 = normalize_01;
+    d.max_crop_w = max_cw;
+    d.status = status_dev;
+    if (int rc = check_common(&d)) return rc;
+    return launch_desc(d, max_cw, stream);
+}
+
+}  // extern "C"
