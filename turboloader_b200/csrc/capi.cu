@@ -327,7 +327,7 @@ int to_int_boxes(const tlb_image_ref* imgs, const tlb_crop_params* crops, int n,
 }
 
 // Packs the crop rectangle of every host image (rows of cw*3 bytes, 16-byte aligned starts)
-// plus the per-sample tables into one pinned buffer, uploads it with ONE copy and launches.
+// plus the per-sample tables into one pinned buffer and uploads and launches it chunk by chunk.
 int host_images_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crops, int n, int dst_h, int dst_w,
                           const float mean[3], const float std_[3], int normalize_01, void* out_dev, int out_dtype,
                           int out_layout, uint32_t* status_dev, cudaStream_t stream) {
@@ -347,11 +347,15 @@ int host_images_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crop
         pix += (static_cast<size_t>(boxes[i].w) * boxes[i].h * 3 + 15) & ~static_cast<size_t>(15);
         max_cw = std::max(max_cw, boxes[i].w);
     }
-    const size_t off_tab = pix;                       // int64 offsets[n]
-    const size_t size_tab = off_tab + 8 * size_t(n);  // int32 sizes[n][2]
-    const size_t box_tab = size_tab + 8 * size_t(n);  // int32 boxes[n][4]
-    const size_t flip_tab = box_tab + 16 * size_t(n); // u8 flips[n]
-    const size_t total = (flip_tab + n + 15) & ~static_cast<size_t>(15);
+    // Buffer layout: [boxes | offsets | sizes | flips | pixels].  The tables go up first, then the
+    // batch is cut into chunks: while the DMA engine uploads chunk c the host threads pack chunk
+    // c+1, and each chunk's kernel starts as soon as its own pixels have landed.
+    const size_t box_tab = 0;                          // int32 boxes[n][4] (16-byte aligned per sample)
+    const size_t off_tab = box_tab + 16 * size_t(n);   // int64 offsets[n]
+    const size_t size_tab = off_tab + 8 * size_t(n);   // int32 sizes[n][2]
+    const size_t flip_tab = size_tab + 8 * size_t(n);  // u8 flips[n]
+    const size_t pix_base = (flip_tab + n + 255) & ~static_cast<size_t>(255);
+    const size_t total = pix_base + pix;
 
     std::unique_lock<std::mutex> lk(st.mu);
     Buffer& buf = st.images[st.images_next];
@@ -374,32 +378,14 @@ int host_images_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crop
         h_box[4 * i + 3] = boxes[i].h;
         h_flip[i] = static_cast<unsigned char>(boxes[i].flip);
     }
-    Pool::get().run(static_cast<size_t>(n), [&](size_t i) {
-        const IntBox& b = boxes[i];
-        const unsigned char* s = imgs[i].data + (static_cast<size_t>(b.y) * imgs[i].w + b.x) * 3;
-        unsigned char* d = base + offs[i];
-        const size_t row = static_cast<size_t>(b.w) * 3, pitch = static_cast<size_t>(imgs[i].w) * 3;
-        if (b.w == imgs[i].w) {
-            std::memcpy(d, s, row * b.h);
-        } else {
-            for (int y = 0; y < b.h; ++y) std::memcpy(d + y * row, s + y * pitch, row);
-        }
-    });
-    TLB_CUDA(cudaMemcpyAsync(buf.dev, buf.host, total, cudaMemcpyHostToDevice, stream));
+    auto* dbase = static_cast<unsigned char*>(buf.dev);
+    TLB_CUDA(cudaMemcpyAsync(dbase, base, flip_tab + n, cudaMemcpyHostToDevice, stream));
 
     tlb_transform_desc d{};
-    auto* dbase = static_cast<unsigned char*>(buf.dev);
-    d.src = dbase;
+    d.src = dbase + pix_base;
     d.src_bytes = pix;
-    d.n_src = n;
-    d.src_offsets = reinterpret_cast<const int64_t*>(dbase + off_tab);
-    d.src_sizes = reinterpret_cast<const int32_t*>(dbase + size_tab);
-    d.n = n;
-    d.boxes = reinterpret_cast<const int32_t*>(dbase + box_tab);
-    d.flips = dbase + flip_tab;
     d.dst_h = dst_h;
     d.dst_w = dst_w;
-    d.out = out_dev;
     d.out_dtype = out_dtype;
     d.out_layout = out_layout;
     for (int c = 0; c < 3; ++c) {
@@ -409,9 +395,46 @@ int host_images_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crop
     d.normalize_01 = normalize_01;
     d.max_crop_w = max_cw;
     d.status = status_dev;
-    if (int rc = check_common(&d)) return rc;
-    const int rc = launch_desc(d, max_cw, stream);
-    // The buffer pair is reusable once the kernel that reads the device half has finished.
+    const size_t out_stride = static_cast<size_t>(3) * dst_h * dst_w * (out_dtype == TLB_F32 ? 4 : 2);
+
+    const size_t chunk_bytes = static_cast<size_t>(std::max(1, env_int("TLB_H2D_CHUNK_MB", 8))) << 20;
+    int rc = TLB_OK;
+    for (int i0 = 0; i0 < n && rc == TLB_OK;) {
+        int i1 = i0;
+        const size_t start = static_cast<size_t>(offs[i0]);
+        size_t end = start;
+        while (i1 < n && (i1 == i0 || end - start < chunk_bytes)) {
+            end = static_cast<size_t>(offs[i1]) +
+                  ((static_cast<size_t>(boxes[i1].w) * boxes[i1].h * 3 + 15) & ~static_cast<size_t>(15));
+            ++i1;
+        }
+        Pool::get().run(static_cast<size_t>(i1 - i0), [&](size_t j) {
+            const size_t i = static_cast<size_t>(i0) + j;
+            const IntBox& b = boxes[i];
+            const unsigned char* s = imgs[i].data + (static_cast<size_t>(b.y) * imgs[i].w + b.x) * 3;
+            unsigned char* dst = base + pix_base + offs[i];
+            const size_t row = static_cast<size_t>(b.w) * 3, pitch = static_cast<size_t>(imgs[i].w) * 3;
+            if (b.w == imgs[i].w) {
+                std::memcpy(dst, s, row * b.h);
+            } else {
+                for (int y = 0; y < b.h; ++y) std::memcpy(dst + y * row, s + y * pitch, row);
+            }
+        });
+        TLB_CUDA(cudaMemcpyAsync(dbase + pix_base + start, base + pix_base + start, end - start,
+                                 cudaMemcpyHostToDevice, stream));
+        // Samples i0 .. i1-1: their images are dataset entries 0 .. (i1-i0)-1 of the shifted tables.
+        d.n = i1 - i0;
+        d.n_src = i1 - i0;
+        d.src_offsets = reinterpret_cast<const int64_t*>(dbase + off_tab) + i0;
+        d.src_sizes = reinterpret_cast<const int32_t*>(dbase + size_tab) + 2 * i0;
+        d.boxes = reinterpret_cast<const int32_t*>(dbase + box_tab) + 4 * i0;
+        d.flips = dbase + flip_tab + i0;
+        d.out = static_cast<unsigned char*>(out_dev) + static_cast<size_t>(i0) * out_stride;
+        rc = check_common(&d);
+        if (rc == TLB_OK) rc = launch_desc(d, max_cw, stream);
+        i0 = i1;
+    }
+    // The buffer pair is reusable once the last kernel that reads the device half has finished.
     TLB_CUDA(cudaEventRecord(buf.done, stream));
     buf.pending = true;
     return rc;

@@ -555,14 +555,12 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
 #ifndef TLB_EXP_SKIP_H
         if (h_active) {
             const unsigned char* rawb = raw + b * Rr * own_pitch;
-            const unsigned char* tap0 = rawb + off0;
-            const unsigned char* tap1 = rawb + off1;
             const int2* rowoff = reinterpret_cast<const int2*>(smem + kSmemRowOff) + (i % kSlots) * 32;
 #pragma unroll 2
             for (int j = 0; j < m.y; ++j) {
                 const int2 ro = rowoff[j];  // {raw byte offset of the row, byte offset of its ring slot}
-                const unsigned char* q0 = tap0 + ro.x;
-                const unsigned char* q1 = tap1 + ro.x;
+                const unsigned char* q0 = rawb + off0 + ro.x;
+                const unsigned char* q1 = rawb + off1 + ro.x;
                 const float2 t0 = byte_product2(q0[0], q1[0], wx, nwx);
                 const float2 t1 = byte_product2(q0[1], q1[1], wx, nwx);
                 const float2 t2 = byte_product2(q0[2], q1[2], wx, nwx);
