@@ -12,7 +12,7 @@ shard with no collective ("weak" scaling: per-rank work is fixed).
 
 Prints ONE JSON line (rank 0).  ``value`` is images/s over all ranks with inputs resident
 in HBM; ``e2e`` is the same metric through the host-image C-ABI entry point (pinned host
-pixels -> H2D -> kernel -> device batch, status word read back every step); ``roofline``
+pixels -> crop rows pulled across PCIe -> kernel -> device batch, status word read back every step); ``roofline``
 compares the kernel's algorithmic bytes per second with the measured HBM copy bandwidth;
 ``cpu_baseline`` times the reference's own CPU fused path on this box's host cores.
 """
@@ -457,7 +457,7 @@ def main():
             es, h2d, d2h = e2e_steps(host_sets, lib, stream, e_steps, 3, torch, device)
             line["e2e"] = {"value": e_steps * wl.n / es, "unit": UNIT, "h2d_bytes_per_step": h2d,
                            "d2h_bytes_per_step": d2h, "steps": e_steps,
-                           "path": "tlb_crop_resize_normalize_to_device: pinned host pixels -> crop pack -> one H2D -> kernel"}
+                           "path": "tlb_crop_resize_normalize_to_device: pinned host pixels -> GPU-side gather of the crop rows over PCIe -> fused kernel; status word read back"}
             line["cpu_baseline"] = cpu_baseline(host_sets[0])
         others = {}
         for name in WORKLOADS:

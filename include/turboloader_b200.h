@@ -221,6 +221,15 @@ TLB_API int64_t tlb_direct_order(int64_t total, int32_t shuffle, int32_t seed, i
                                  int32_t distributed, int32_t rank, int32_t world, int64_t* out,
                                  int64_t cap);
 
+/* RandomResizedCrop(scale (0.08,1), ratio (3/4,4/3)) + flip sampler of the direct-batch loader
+ * (DirectBatchCore::pick_crop, src/pipeline/direct_batch_loader.hpp:141-178), host only.
+ * sizes_wh = n x (w, h) of the images the rects are drawn on; indices = n sample indices (NULL:
+ * 0..n-1) that seed each sample's generator together with seed and epoch.  Writes n integer
+ * rects (x, y, w, h) and, if flips_out != NULL, n flags.  Returns n, or a negative value for bad
+ * arguments. */
+TLB_API int64_t tlb_pick_crops(int32_t seed, int32_t epoch, const int64_t* indices, const int32_t* sizes_wh,
+                               int64_t n, float hflip_prob, int32_t* boxes_out, uint8_t* flips_out);
+
 #ifdef __cplusplus
 }
 #endif

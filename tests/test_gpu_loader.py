@@ -105,6 +105,44 @@ def test_host_to_device_streaming_entry():
     assert check_bf16(out.view(torch.int16).cpu().numpy().view(np.uint16), expected(wl)) == 0
 
 
+def test_pinned_host_images_are_gathered_by_the_gpu():
+    """Images in page-locked host memory take the GPU-side gather path (no host packing); the
+    result must equal the oracle exactly, for odd widths, any alignment, all output forms."""
+    import torch
+    lib = _capi.load()
+    for seed, dtype, layout, cl in [(41, _capi.TLB_F32, _capi.TLB_NCHW, False), (42, _capi.TLB_BF16, _capi.TLB_NHWC, True)]:
+        wl = S.config2(seed=seed, n=14, lo=33, hi=131, dst=56)
+        wl.dtype, wl.channels_last = ("f32" if dtype == _capi.TLB_F32 else "bf16"), cl
+        pad = 5  # shift the packed images off the 16-byte grid
+        pinned = torch.empty(wl.src.size + pad, dtype=torch.uint8).pin_memory()
+        pinned[pad:] = torch.from_numpy(wl.src)
+        refs = (_capi.ImageRef * wl.n)()
+        crops = (_capi.CropParams * wl.n)()
+        for i in range(wl.n):
+            refs[i].data = pinned.data_ptr() + pad + int(wl.offsets[i])
+            refs[i].w, refs[i].h = int(wl.sizes[i, 0]), int(wl.sizes[i, 1])
+            crops[i].x, crops[i].y, crops[i].w, crops[i].h = (float(v) for v in wl.boxes[i])
+            crops[i].flip = int(wl.flips[i])
+        tdt = torch.float32 if dtype == _capi.TLB_F32 else torch.bfloat16
+        shape = (wl.n, 56, 56, 3) if cl else (wl.n, 3, 56, 56)
+        out = torch.empty(shape, dtype=tdt, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        before = t.launch_count()
+        for _ in range(3):
+            rc = lib.tlb_crop_resize_normalize_to_device(refs, crops, wl.n, 56, 56, _capi.f3(wl.mean), _capi.f3(wl.std), 1,
+                                                         out.data_ptr(), dtype, layout, status.data_ptr(),
+                                                         C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            assert rc == 0, lib.tlb_last_error()
+        torch.cuda.synchronize()
+        assert t.launch_count() - before == 6  # gather + fused transform per call
+        assert int(status.item()) == 0
+        want = expected(wl)
+        if dtype == _capi.TLB_F32:
+            assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+        else:
+            assert check_bf16(out.view(torch.int16).cpu().numpy().view(np.uint16), want) == 0
+
+
 def test_resident_loader_reference_contract():
     import torch
     data = _dataset(50, 20, seed=4)
@@ -181,3 +219,61 @@ def test_resident_loader_explicit_boxes():
         want = O.fused_batch(flat, offsets, sizes, idx.cpu().numpy(), bx[b * 10:(b + 1) * 10], fl[b * 10:(b + 1) * 10], 24, 24,
                              MEAN, STD, True)
         assert np.array_equal(x.cpu().numpy(), want)
+
+
+def test_dataloader_tbl_contract(tmp_path):
+    """DataLoader('x.tbl', output_format='pytorch'): (images, meta) batches, TblRawImageLoader's
+    order and flip rules (turboloader/tbl.py:213-264), state_dict resume, ragged last batch."""
+    import torch
+    from turboloader_b200 import tbl
+    data = _dataset(37, 16, seed=9)
+    path = tmp_path / "d.tbl"
+    tbl.write_raw_tbl(path, data)
+    dl = t.DataLoader(path, batch_size=8, shuffle=True, seed=5, transform=t.ImageNetNormalize(), image_size=16,
+                      hflip_prob=0.5)
+    assert len(dl) == 5
+    order = np.random.default_rng(5).permutation(37)
+    frng = np.random.default_rng((5, 0, 1))
+    got = []
+    for b, (x, meta) in enumerate(dl):
+        idx = order[b * 8:(b + 1) * 8]
+        assert x.is_cuda and x.dtype == torch.float32 and x.shape == (len(idx), 3, 16, 16)
+        assert np.array_equal(meta["indices"], idx) and meta["batch_size"] == len(idx)
+        flips = (frng.random(len(idx)) < 0.5).astype(np.uint8)
+        assert np.array_equal(x.cpu().numpy(), _oracle_uniform(data, sel=idx, flips=flips))
+        got.append(x.cpu().numpy().copy())
+        if b == 1:
+            sd = dl.state_dict()
+    assert sd == {"version": 1, "epoch": 0, "batches_served": 2}
+    # plain [0,1] floats without a transform; sequential order
+    dl2 = t.DataLoader(arrays=data, batch_size=16)
+    x, meta = next(iter(dl2))
+    assert np.array_equal(meta["indices"], np.arange(16))
+    assert np.abs(x.cpu().numpy() - data[:16].transpose(0, 3, 1, 2).astype(np.float32) / 255.0).max() < 1e-6
+    # resume: unflipped loader continues exactly where the state says
+    dl3 = t.DataLoader(path, batch_size=8, shuffle=True, seed=5, transform=t.ImageNetNormalize())
+    ref = [x.cpu().numpy().copy() for x, _ in dl3]
+    dl4 = t.DataLoader(path, batch_size=8, shuffle=True, seed=5, transform=t.ImageNetNormalize())
+    dl4.load_state_dict({"version": 1, "epoch": 0, "batches_served": 3})
+    rest = [x.cpu().numpy().copy() for x, _ in dl4]
+    assert len(rest) == 2 and all(np.array_equal(a, b) for a, b in zip(rest, ref[3:]))
+
+
+def test_resident_loader_train_aug():
+    """train_aug: per-sample RandomResizedCrop + flip drawn for (seed, epoch, sample index),
+    fused with the resize; batches equal the oracle run on the same rects."""
+    data = _dataset(30, 64, seed=12)
+    ld = t.CudaResidentLoader.from_array(data, batch_size=10, shuffle=True, seed=3, train_aug=True, output_size=32,
+                                         return_indices=True, as_tensor=True)
+    flat, offsets, sizes = S.uniform_dataset(data)
+    for epoch in (0, 1):
+        ld.set_epoch(epoch)
+        order = ld.epoch_order()
+        boxes, flips = t.pick_crops(3, epoch, np.tile([[64, 64]], (30, 1)), indices=order)
+        assert flips.sum() not in (0, 30)
+        for b, (x, idx) in enumerate(ld):
+            idx = idx.cpu().numpy()
+            assert np.array_equal(idx, order[b * 10:(b + 1) * 10])
+            want = O.fused_batch(flat, offsets, sizes, idx, boxes[b * 10:(b + 1) * 10], flips[b * 10:(b + 1) * 10], 32, 32,
+                                 MEAN, STD, True)
+            assert np.array_equal(x.cpu().numpy(), want)

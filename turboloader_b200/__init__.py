@@ -10,6 +10,8 @@ from .ops import (IMAGENET_MEAN, IMAGENET_STD, cuda_available, cuda_crop_resize_
                   cuda_normalize_resident, cuda_normalize_resident_gather, cuda_resize_normalize, features,
                   fused_plan, fused_transform, launch_count, make_desc)
 from .cuda_loader import CudaResidentLoader, _CudaArray
+from .dataloader import DataLoader, ImageNetNormalize
+from .augment import pick_crops
 from .sharding import (CONTIGUOUS, HASH_BASED, INTERLEAVED, DistributedSampler, ShardingCoordinator,
                        ShardingStrategy, direct_order, shard_indices)
 
@@ -18,6 +20,7 @@ __all__ = [
     "IMAGENET_MEAN", "IMAGENET_STD", "cuda_available", "cuda_device_name", "cuda_resize_normalize",
     "cuda_crop_resize_normalize", "cuda_normalize_resident", "cuda_normalize_resident_gather",
     "fused_transform", "fused_plan", "make_desc", "features", "launch_count", "CudaResidentLoader", "_CudaArray",
+    "DataLoader", "ImageNetNormalize", "pick_crops",
     "ShardingStrategy", "ShardingCoordinator", "DistributedSampler", "direct_order", "shard_indices",
     "CONTIGUOUS", "INTERLEAVED", "HASH_BASED",
 ]

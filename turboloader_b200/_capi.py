@@ -120,6 +120,9 @@ def load() -> C.CDLL:
     lib.tlb_direct_order.restype = C.c_int64
     lib.tlb_direct_order.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                      i64p, C.c_int64]
+    lib.tlb_pick_crops.restype = C.c_int64
+    lib.tlb_pick_crops.argtypes = [C.c_int32, C.c_int32, i64p, C.POINTER(C.c_int32), C.c_int64, C.c_float,
+                                   C.POINTER(C.c_int32), C.POINTER(C.c_uint8)]
     _lib = lib
     return lib
 

@@ -20,10 +20,12 @@
 
 #include "../../include/turboloader_b200.h"
 #include "fused_params.h"
+#include "host_gather.h"
 
 namespace {
 
 thread_local std::string t_err;
+std::atomic<unsigned long long> g_extra_launches{0};  // kernels other than the fused transform
 
 int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -338,6 +340,105 @@ int host_images_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crop
     DeviceState& st = g_dev[dev];
     std::vector<IntBox> boxes;
     if (int rc = to_int_boxes(imgs, crops, n, boxes)) return rc;
+
+    // ---- pinned sources: let the GPU gather the crop rows itself --------------------------------
+    // When every image lies in page-locked, device-mapped host memory, no host packing is needed:
+    // a small kernel reads exactly the crop rows across PCIe (host_gather.cu) into the device
+    // half of the staging buffer, and the fused kernel follows on the same stream.
+    if (env_int("TLB_HOST_GATHER", 1) != 0) {
+        std::vector<tlb::GatherItem> items(n);
+        bool mapped = true;
+        size_t gpix = 0;
+        unsigned max_rows = 1;
+        int gmax_cw = 1;
+        for (int i = 0; i < n && mapped; ++i) {
+            cudaPointerAttributes attr{};
+            if (cudaPointerGetAttributes(&attr, imgs[i].data) != cudaSuccess) {
+                cudaGetLastError();
+                mapped = false;
+                break;
+            }
+            if ((attr.type != cudaMemoryTypeHost && attr.type != cudaMemoryTypeManaged) || !attr.devicePointer) {
+                mapped = false;
+                break;
+            }
+            const IntBox& b = boxes[i];
+            const unsigned wpad = (static_cast<unsigned>(b.w) + 15u) & ~15u;  // packed row = whole pixels, 16-byte multiple
+            items[i].src = reinterpret_cast<unsigned long long>(attr.devicePointer) +
+                           (static_cast<unsigned long long>(b.y) * imgs[i].w + b.x) * 3ull;
+            items[i].dst_off = gpix;
+            items[i].src_pitch = static_cast<unsigned>(imgs[i].w) * 3u;
+            items[i].row_bytes = static_cast<unsigned>(b.w) * 3u;
+            items[i].rows = static_cast<unsigned>(b.h);
+            items[i].dst_pitch = wpad * 3u;
+            gpix += static_cast<size_t>(wpad) * 3u * b.h;
+            max_rows = std::max(max_rows, static_cast<unsigned>(b.h));
+            gmax_cw = std::max(gmax_cw, b.w);
+        }
+        if (mapped) {
+            // Buffer layout: host half holds [boxes | offsets | sizes | flips | gather items]; the device
+            // half holds the same tables followed by the gathered pixels.
+            const size_t box_tab = 0;
+            const size_t off_tab = box_tab + 16 * size_t(n);
+            const size_t size_tab = off_tab + 8 * size_t(n);
+            const size_t flip_tab = size_tab + 8 * size_t(n);
+            const size_t item_tab = (flip_tab + n + 15) & ~static_cast<size_t>(15);
+            const size_t tab_bytes = item_tab + sizeof(tlb::GatherItem) * size_t(n);
+            const size_t pix_base = (tab_bytes + 255) & ~static_cast<size_t>(255);
+            std::unique_lock<std::mutex> lk(st.mu);
+            Buffer& buf = st.images[st.images_next];
+            st.images_next ^= 1;
+            if (int rc = grow(buf, pix_base + gpix)) return rc;
+            lk.unlock();
+            auto* hb = static_cast<unsigned char*>(buf.host);
+            auto* db = static_cast<unsigned char*>(buf.dev);
+            auto* h_box = reinterpret_cast<int*>(hb + box_tab);
+            auto* h_off = reinterpret_cast<long long*>(hb + off_tab);
+            auto* h_size = reinterpret_cast<int*>(hb + size_tab);
+            for (int i = 0; i < n; ++i) {
+                h_box[4 * i] = 0;
+                h_box[4 * i + 1] = 0;
+                h_box[4 * i + 2] = boxes[i].w;
+                h_box[4 * i + 3] = boxes[i].h;
+                h_off[i] = static_cast<long long>(items[i].dst_off);
+                h_size[2 * i] = static_cast<int>(items[i].dst_pitch / 3u);
+                h_size[2 * i + 1] = boxes[i].h;
+                hb[flip_tab + i] = static_cast<unsigned char>(boxes[i].flip);
+            }
+            std::memcpy(hb + item_tab, items.data(), sizeof(tlb::GatherItem) * size_t(n));
+            TLB_CUDA(cudaMemcpyAsync(db, hb, tab_bytes, cudaMemcpyHostToDevice, stream));
+            cudaError_t ge = static_cast<cudaError_t>(tlb::launch_gather(
+                reinterpret_cast<const tlb::GatherItem*>(db + item_tab), n, max_rows, db + pix_base, stream));
+            if (ge != cudaSuccess) return cuda_fail(ge, "gather_crops_kernel launch");
+            g_extra_launches.fetch_add(1, std::memory_order_relaxed);
+            tlb_transform_desc d{};
+            d.src = db + pix_base;
+            d.src_bytes = gpix;
+            d.n_src = n;
+            d.src_offsets = reinterpret_cast<const int64_t*>(db + off_tab);
+            d.src_sizes = reinterpret_cast<const int32_t*>(db + size_tab);
+            d.n = n;
+            d.boxes = reinterpret_cast<const int32_t*>(db + box_tab);
+            d.flips = db + flip_tab;
+            d.dst_h = dst_h;
+            d.dst_w = dst_w;
+            d.out = out_dev;
+            d.out_dtype = out_dtype;
+            d.out_layout = out_layout;
+            for (int ch = 0; ch < 3; ++ch) {
+                d.mean[ch] = mean[ch];
+                d.std[ch] = std_[ch];
+            }
+            d.normalize_01 = normalize_01;
+            d.max_crop_w = gmax_cw;
+            d.status = status_dev;
+            int rc = check_common(&d);
+            if (rc == TLB_OK) rc = launch_desc(d, gmax_cw, stream);
+            TLB_CUDA(cudaEventRecord(buf.done, stream));
+            buf.pending = true;
+            return rc;
+        }
+    }
 
     std::vector<long long> offs(n);
     size_t pix = 0;
@@ -676,7 +777,7 @@ int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block
     return TLB_OK;
 }
 
-uint64_t tlb_launch_count(void) { return tlb::launch_count(); }
+uint64_t tlb_launch_count(void) { return tlb::launch_count() + g_extra_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"
 

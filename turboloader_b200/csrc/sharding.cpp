@@ -8,6 +8,7 @@
 // The shuffles call the same standard-library engines and algorithms as those sources,
 // so the orders agree element for element when both are built with the same libstdc++.
 #include <algorithm>
+#include <cmath>
 #include <cstdint>
 #include <numeric>
 #include <random>
@@ -100,6 +101,62 @@ int64_t tlb_direct_order(int64_t total, int32_t shuffle, int32_t seed, int32_t e
         e = b + per;
     }
     return emit(b, e, out, cap);
+}
+
+
+// RandomResizedCrop + horizontal-flip sampler of the direct-batch loader
+// (DirectBatchCore::pick_crop, src/pipeline/direct_batch_loader.hpp:141-178): per sample a
+// mt19937_64 seeded with (seed << 32) ^ (epoch << 20) ^ index; up to 10 attempts of
+// area * U(0.08, 1) with a log-uniform aspect ratio in [3/4, 4/3], integer rect accepted when
+// it fits; otherwise the central crop at the clamped aspect ratio; the flip flag is the last
+// draw.  All arithmetic is in float, draws come from uniform_real_distribution<float>(0, 1),
+// in the same order, so with the same libstdc++ the rects agree with that loader's.
+int64_t tlb_pick_crops(int32_t seed, int32_t epoch, const int64_t* indices, const int32_t* sizes_wh, int64_t n,
+                       float hflip_prob, int32_t* boxes_out, uint8_t* flips_out) {
+    if (n < 0 || !sizes_wh || !boxes_out) return -1;
+    const float lo = std::log(3.0f / 4.0f), hi = std::log(4.0f / 3.0f);
+    for (int64_t i = 0; i < n; ++i) {
+        const int w = sizes_wh[2 * i], h = sizes_wh[2 * i + 1];
+        if (w <= 0 || h <= 0) return -(i + 2);
+        const uint64_t idx = static_cast<uint64_t>(indices ? indices[i] : i);
+        std::mt19937_64 rng((static_cast<uint64_t>(seed) << 32) ^ (static_cast<uint64_t>(epoch) << 20) ^ idx);
+        std::uniform_real_distribution<float> uni(0.0f, 1.0f);
+        const float area = static_cast<float>(w) * h;
+        int bx = 0, by = 0, bw = w, bh = h;
+        bool found = false;
+        for (int attempt = 0; attempt < 10 && !found; ++attempt) {
+            const float target = area * (0.08f + uni(rng) * (1.0f - 0.08f));
+            const float ratio = std::exp(lo + uni(rng) * (hi - lo));
+            const int cw = static_cast<int>(std::lround(std::sqrt(target * ratio)));
+            const int ch = static_cast<int>(std::lround(std::sqrt(target / ratio)));
+            if (cw > 0 && ch > 0 && cw <= w && ch <= h) {
+                bw = cw;
+                bh = ch;
+                bx = std::min(static_cast<int>(uni(rng) * (w - cw + 1)), w - cw);
+                by = std::min(static_cast<int>(uni(rng) * (h - ch + 1)), h - ch);
+                found = true;
+            }
+        }
+        if (!found) {
+            const float in_ratio = static_cast<float>(w) / h;
+            if (in_ratio < 3.0f / 4.0f) {
+                bw = w;
+                bh = std::min(h, static_cast<int>(std::lround(w / (3.0f / 4.0f))));
+            } else if (in_ratio > 4.0f / 3.0f) {
+                bh = h;
+                bw = std::min(w, static_cast<int>(std::lround(h * (4.0f / 3.0f))));
+            }
+            bx = (w - bw) / 2;
+            by = (h - bh) / 2;
+        }
+        const bool flip = uni(rng) < hflip_prob;
+        boxes_out[4 * i] = bx;
+        boxes_out[4 * i + 1] = by;
+        boxes_out[4 * i + 2] = bw;
+        boxes_out[4 * i + 3] = bh;
+        if (flips_out) flips_out[i] = flip ? 1 : 0;
+    }
+    return n;
 }
 
 }  // extern "C"

@@ -91,7 +91,7 @@ class CudaResidentLoader:
     def _init_common(self, array, batch_size, *, mean=ops.IMAGENET_MEAN, std=ops.IMAGENET_STD, drop_last=True,
                      shuffle=False, seed=42, return_indices=False, crop_size=None, output_size=None,
                      hflip_prob=0.0, boxes=None, dtype=None, channels_last=False, as_tensor=None, labels=None,
-                     ring=4, device=None):
+                     ring=4, device=None, flips=None, train_aug=False):
         import torch
 
         if not ops.cuda_available():
@@ -110,7 +110,7 @@ class CudaResidentLoader:
             self._gpu = torch.empty((n, H, W, 3), dtype=torch.uint8, device=self._device)
             step = max(1, (64 << 20) // max(1, H * W * 3))
             for s in range(0, n, step):
-                chunk = np.ascontiguousarray(array[s:s + step])
+                chunk = np.array(array[s:s + step])  # a writable copy (memory maps are read-only)
                 self._gpu[s:s + chunk.shape[0]] = torch.from_numpy(chunk)
         self._n, self._H, self._W = int(self._gpu.shape[0]), int(self._gpu.shape[1]), int(self._gpu.shape[2])
         self.batch_size = int(batch_size)
@@ -135,6 +135,14 @@ class CudaResidentLoader:
         else:
             self._oh, self._ow = (output_size, output_size) if np.isscalar(output_size) else tuple(output_size)
         self._boxes_fn = boxes  # callable(epoch, order) -> int32[len(order), 4], or None
+        self._flips_fn = flips  # callable(epoch, n, start_batch) -> uint8[n] per epoch position, or None
+        # train_aug: RandomResizedCrop + flip per sample and epoch, seeded by (seed, epoch, sample index)
+        # like the direct-batch loader's train_aug (src/pipeline/direct_batch_loader.hpp:141-178).
+        self._train_aug = bool(train_aug)
+        if self._train_aug and (boxes is not None or flips is not None):
+            raise ValueError("train_aug draws its own boxes and flips")
+        if self._train_aug and hflip_prob == 0.0:
+            self.hflip_prob = 0.5
         # Plain float32 NCHW batches are handed out as __cuda_array_interface__ objects like the
         # reference's; bf16 has no CAI typestr and channels-last needs strides, so those are tensors.
         plain = self.dtype == torch.float32 and not self.channels_last
@@ -198,13 +206,24 @@ class CudaResidentLoader:
         bs = self.batch_size
         end = (self._n // bs) * bs if self.drop_last else self._n
         order = self.epoch_order()
-        flips = self.epoch_flips()
+        aug_boxes = None
+        if self._train_aug:
+            from .augment import pick_crops
+            sizes = np.tile(np.array([[self._W, self._H]], dtype=np.int32), (self._n, 1))
+            aug_boxes, flips = pick_crops(self.seed, self._epoch, sizes, indices=order, hflip_prob=self.hflip_prob)
+        elif self._flips_fn is not None:
+            flips = np.ascontiguousarray(self._flips_fn(self._epoch, self._n, self._resume_batches), dtype=np.uint8)
+            if flips.shape != (self._n,):
+                raise ValueError("flips callable must return one flag per epoch position")
+        else:
+            flips = self.epoch_flips()
         with torch.cuda.device(self._device):
             d_order = torch.from_numpy(order).to(self._device) if self.shuffle else None
-            d_flips = torch.from_numpy(flips).to(self._device) if self.hflip_prob > 0.0 else None
+            d_flips = torch.from_numpy(flips).to(self._device) if (self.hflip_prob > 0.0 or self._flips_fn is not None) else None
             d_boxes = None
-            if self._boxes_fn is not None:
-                b = np.ascontiguousarray(self._boxes_fn(self._epoch, order), dtype=np.int32).reshape(-1, 4)
+            if self._boxes_fn is not None or aug_boxes is not None:
+                b = aug_boxes if aug_boxes is not None else \
+                    np.ascontiguousarray(self._boxes_fn(self._epoch, order), dtype=np.int32).reshape(-1, 4)
                 if b.shape[0] != self._n:
                     raise ValueError("boxes callable must return one box per epoch position")
                 if (b[:, 2] <= 0).any() or (b[:, 3] <= 0).any() or (b[:, 0] < 0).any() or (b[:, 1] < 0).any() or \
