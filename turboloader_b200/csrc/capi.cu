@@ -140,7 +140,10 @@ int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl) {
     constexpr int kMinRows = 4;
     const int hrow = pl.strips * tlb::kStripRowBytes;
     const int per_row_worst = tlb::kNBuf * pl.pitch + hrow;
-    const int budget = std::clamp(env_int("TLB_SMEM_BUDGET", 56 * 1024), 8 * 1024, 226 * 1024);
+    // Default budget: 8 KB per strip + 8 KB, at most 56 KB (narrow tiles get more CTAs per SM;
+    // measured on 128- and 224-column outputs).
+    const int dflt_budget = std::min(56 * 1024, (pl.strips + 1) * 8 * 1024);
+    const int budget = std::clamp(env_int("TLB_SMEM_BUDGET", dflt_budget), 8 * 1024, 226 * 1024);
     int var = std::max(budget - tlb::kSmemVar, kMinRows * per_row_worst + 2 * hrow);
     var = std::min(var, tlb::kMaxNewRows * per_row_worst + 2 * hrow);
     pl.smem_bytes = tlb::kSmemVar + var;

@@ -51,6 +51,11 @@
 namespace tlb {
 namespace {
 
+#ifndef TLB_H_UNROLL
+#define TLB_H_UNROLL 4
+#endif
+constexpr int kHUnroll = TLB_H_UNROLL;  // source rows in flight per lane in the H step
+
 constexpr unsigned kDevBadIndex = 1u, kDevBadBox = 2u, kDevTooWide = 4u, kDevCopyTimeout = 8u;
 constexpr unsigned kWaitLimit = 1u << 20;  // bounded mbarrier polling (each poll may suspend briefly)
 
@@ -64,14 +69,18 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t mbar, uint32_t by
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes)
                  : "memory");
 }
+// One poll.  The suspend-time hint lets the hardware park the warp until the phase completes
+// (or the hint expires) instead of returning at once: a warp that waits does not burn issue
+// slots re-polling -- with plain polls the waiting planner and compute warps executed more than
+// a quarter of all instructions of the kernel.
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t mbar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(mbar), "r"(parity)
+        : "r"(mbar), "r"(parity), "r"(1000000u)
         : "memory");
     return ok;
 }
@@ -556,7 +565,7 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         if (h_active) {
             const unsigned char* rawb = raw + b * Rr * own_pitch;
             const int2* rowoff = reinterpret_cast<const int2*>(smem + kSmemRowOff) + (i % kSlots) * 32;
-#pragma unroll 2
+#pragma unroll kHUnroll
             for (int j = 0; j < m.y; ++j) {
                 const int2 ro = rowoff[j];  // {raw byte offset of the row, byte offset of its ring slot}
                 const unsigned char* q0 = rawb + off0 + ro.x;
