@@ -267,6 +267,88 @@ def cpu_baseline(wl, budget_s=4.0, min_passes=3):
                       f"host has {os.cpu_count()} logical cores"}
 
 
+def reference_gpu_leg(wl, lib, torch, device, sample=512):
+    """The reference's own CUDA kernels, compiled for this GPU from its tree (oracle/_ref), timed
+    beside the same contract of this library.  (a) host images -> host float32: its
+    crop_resize_normalize_batch against tlb_crop_resize_normalize_batch on the first `sample` images
+    of the batch; (b) resident gather + normalize of 1024 x 160x160 from a 20 000-image device
+    array: its normalize_resident_gather_batch against tlb_normalize_resident_gather_batch (both
+    synchronise before returning).  Returns None when the library was not compiled."""
+    from oracle import oracle as O
+    from turboloader_b200 import _capi
+
+    rlib = O.ref_cuda()
+    if rlib is None or not rlib.tlrefcuda_available():
+        return None
+    n = min(sample, wl.n)
+    images, crops, flips = [], np.zeros((n, 4), np.float32), np.zeros(n, np.int32)
+    refs, cps = (_capi.ImageRef * n)(), (_capi.CropParams * n)()
+    for i in range(n):
+        s_ = int(wl.sel[i]) if wl.sel is not None else i
+        w, h = int(wl.sizes[s_, 0]), int(wl.sizes[s_, 1])
+        off = int(wl.offsets[s_])
+        images.append(wl.src[off:off + w * h * 3].reshape(h, w, 3))
+        crops[i] = wl.boxes[i] if wl.boxes is not None else (0, 0, w, h)
+        flips[i] = int(wl.flips[i]) if wl.flips is not None else 0
+        refs[i].data, refs[i].w, refs[i].h = images[-1].ctypes.data, w, h
+        cps[i].x, cps[i].y, cps[i].w, cps[i].h = [float(v) for v in crops[i]]
+        cps[i].flip = int(flips[i])
+    out = np.empty((n, 3, wl.dst_h, wl.dst_w), np.float32)
+
+    def best(fn, reps=5):
+        fn()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return min(ts)
+
+    t_ref = best(lambda: O.ref_cuda_crop_resize_normalize(images, crops, flips, wl.dst_h, wl.dst_w, wl.mean, wl.std))
+
+    def ours_host():
+        rc = lib.tlb_crop_resize_normalize_batch(refs, cps, n, wl.dst_h, wl.dst_w, _capi.f3(wl.mean), _capi.f3(wl.std),
+                                                 out.ctypes.data)
+        if rc != 0:
+            raise RuntimeError(lib.tlb_last_error().decode())
+
+    t_ours = best(ours_host)
+    res = {"host_to_host": {"sample": f"first {n} images of '{wl.name}', pageable host memory, float32 NCHW to host",
+                            "reference_img_per_s": n / t_ref, "ours_img_per_s": n / t_ours}}
+
+    nsrc, hw, bs = 20000, 160, 1024
+    g = torch.Generator(device=device)
+    g.manual_seed(7)
+    data = torch.randint(0, 256, (nsrc, hw, hw, 3), dtype=torch.uint8, device=device, generator=g)
+    sels = [torch.randperm(nsrc, device=device, generator=g)[:bs].contiguous() for _ in range(8)]
+    mean = np.asarray(wl.mean, np.float32)
+    std = np.asarray(wl.std, np.float32)
+    f32p = C.POINTER(C.c_float)
+
+    def loop(fn, reps=40):
+        for i in range(4):
+            fn(sels[i % 8])
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(reps):
+            if not fn(sels[i % 8]):
+                raise RuntimeError("resident gather call failed")
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / reps
+
+    t_ref = loop(lambda s_: rlib.tlrefcuda_normalize_resident_gather(data.data_ptr(), s_.data_ptr(), bs, hw, hw,
+                                                                     mean.ctypes.data_as(f32p), std.ctypes.data_as(f32p)))
+    t_ours = loop(lambda s_: lib.tlb_normalize_resident_gather_batch(data.data_ptr(), s_.data_ptr(), bs, hw, hw,
+                                                                     _capi.f3(mean), _capi.f3(std)))
+    nbytes = bs * hw * hw * 3 * 5
+    res["resident_gather"] = {"sample": f"{bs} x {hw}x{hw} gathered from {nsrc} resident images, float32 NCHW, "
+                                        "call + stream synchronise, 40 calls",
+                              "reference_img_per_s": bs / t_ref, "ours_img_per_s": bs / t_ours,
+                              "reference_GB_per_s": nbytes / t_ref / 1e9, "ours_GB_per_s": nbytes / t_ours / 1e9}
+    del data
+    return res
+
+
 # ---- main ----------------------------------------------------------------------------------
 
 def run_reference_arm(args):
@@ -459,6 +541,12 @@ def main():
                            "d2h_bytes_per_step": d2h, "steps": e_steps,
                            "path": "tlb_crop_resize_normalize_to_device: pinned host pixels -> GPU-side gather of the crop rows over PCIe -> fused kernel; status word read back"}
             line["cpu_baseline"] = cpu_baseline(host_sets[0])
+            try:
+                rg = reference_gpu_leg(host_sets[0], lib, torch, device)
+            except Exception as e:  # the comparison leg must never take the bench line down
+                rg = {"error": repr(e)}
+            if rg is not None:
+                line["reference_gpu"] = rg
         others = {}
         for name in WORKLOADS:
             if name == args.workload:

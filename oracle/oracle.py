@@ -203,3 +203,62 @@ def ref_direct_order(total, shuffle, seed, epoch, distributed, rank, world):
     k = lib.tlref_direct_order(int(total), int(shuffle), int(seed), int(epoch), int(distributed),
                                int(rank), int(world), _ptr(out, _i64p), out.size)
     return out[:k].copy()
+
+
+# ---- the reference's own CUDA kernels, compiled in place (oracle/_ref/libtl_ref_cuda.so) ---------
+
+REF_CUDA_SO = os.path.join(REF_DIR, "libtl_ref_cuda.so")
+_ref_cuda = None
+
+
+def build_ref_cuda(ref_root: str = "/root/reference") -> bool:
+    if not os.path.isfile(os.path.join(ref_root, "src", "cuda", "cuda_transforms.cu")):
+        return False
+    subprocess.check_call(["make", "-C", HERE, "refcuda", f"REF={ref_root}"], stdout=subprocess.DEVNULL)
+    return True
+
+
+def ref_cuda():
+    """ctypes handle of the reference GPU entry points, or None when the library is absent."""
+    global _ref_cuda
+    if _ref_cuda is None:
+        if not os.path.exists(REF_CUDA_SO):
+            return None
+        lib = C.CDLL(REF_CUDA_SO)
+        lib.tlrefcuda_available.restype = C.c_int
+        lib.tlrefcuda_normalize_resident.restype = C.c_size_t
+        lib.tlrefcuda_normalize_resident.argtypes = [C.c_size_t, C.c_int, C.c_int, C.c_int, _f32p, _f32p]
+        lib.tlrefcuda_normalize_resident_gather.restype = C.c_size_t
+        lib.tlrefcuda_normalize_resident_gather.argtypes = [C.c_size_t, C.c_size_t, C.c_int, C.c_int, C.c_int, _f32p, _f32p]
+        pp = C.POINTER(C.c_void_p)
+        lib.tlrefcuda_resize_normalize.restype = C.c_int
+        lib.tlrefcuda_resize_normalize.argtypes = [pp, _i32p, _i32p, C.c_int, C.c_int, C.c_int, _f32p, _f32p, _f32p]
+        lib.tlrefcuda_crop_resize_normalize.restype = C.c_int
+        lib.tlrefcuda_crop_resize_normalize.argtypes = [pp, _i32p, _i32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int, _f32p,
+                                                        _f32p, _f32p]
+        _ref_cuda = lib
+    return _ref_cuda
+
+
+def ref_cuda_crop_resize_normalize(images, crops_xywh, flips, dst_h, dst_w, mean, std):
+    """The reference's crop_resize_normalize_batch on host images -> host float32 NCHW."""
+    lib = ref_cuda()
+    n = len(images)
+    holds = [np.ascontiguousarray(im, dtype=np.uint8) for im in images]
+    ptrs = (C.c_void_p * n)(*[h.ctypes.data for h in holds])
+    ws = np.array([h.shape[1] for h in holds], dtype=np.int32)
+    hs = np.array([h.shape[0] for h in holds], dtype=np.int32)
+    mean = np.asarray(mean, dtype=np.float32)
+    std = np.asarray(std, dtype=np.float32)
+    out = np.empty((n, 3, dst_h, dst_w), dtype=np.float32)
+    if crops_xywh is None:
+        ok = lib.tlrefcuda_resize_normalize(ptrs, _ptr(ws, _i32p), _ptr(hs, _i32p), n, dst_h, dst_w, _ptr(mean, _f32p),
+                                            _ptr(std, _f32p), _ptr(out, _f32p))
+    else:
+        cr = np.ascontiguousarray(crops_xywh, dtype=np.float32)
+        fl = np.ascontiguousarray(flips, dtype=np.int32)
+        ok = lib.tlrefcuda_crop_resize_normalize(ptrs, _ptr(ws, _i32p), _ptr(hs, _i32p), _ptr(cr, _f32p), _ptr(fl, _i32p), n,
+                                                 dst_h, dst_w, _ptr(mean, _f32p), _ptr(std, _f32p), _ptr(out, _f32p))
+    if not ok:
+        raise RuntimeError("reference CUDA call failed")
+    return out

@@ -1,0 +1,44 @@
+// TEST / BENCHMARK INFRASTRUCTURE ONLY -- C wrappers around the UNMODIFIED reference GPU entry
+// points (turboloader::cuda::*, src/cuda/cuda_transforms.hpp), so that the reference's own CUDA
+// kernels, compiled for this GPU from the reference tree (oracle/Makefile target `refcuda`), can
+// be run beside the sm_100a kernel: (a) as a second statement of the normalize/gather math and
+// (b) as the "reference GPU kernels on the same box" timing.  Nothing in the package links this.
+#include <cstdint>
+#include <vector>
+
+#include "src/cuda/cuda_transforms.hpp"
+
+#define API extern "C" __attribute__((visibility("default")))
+
+API int tlrefcuda_available() { return turboloader::cuda::available() ? 1 : 0; }
+
+// normalize_resident_batch / normalize_resident_gather_batch (cuda_transforms.hpp:49-55):
+// returns the device address of the library-owned (N,3,H,W) float32 result, 0 on error.
+API uintptr_t tlrefcuda_normalize_resident(uintptr_t src_dev, int n, int h, int w, const float* mean,
+                                           const float* std_) {
+    return turboloader::cuda::normalize_resident_batch(src_dev, n, h, w, mean, std_);
+}
+API uintptr_t tlrefcuda_normalize_resident_gather(uintptr_t src_dev, uintptr_t sel_dev, int n, int h, int w,
+                                                  const float* mean, const float* std_) {
+    return turboloader::cuda::normalize_resident_gather_batch(src_dev, sel_dev, n, h, w, mean, std_);
+}
+
+// resize_normalize_batch / crop_resize_normalize_batch (cuda_transforms.hpp:41-42, 117-119): host
+// images in, host float32 NCHW out (allocates, uploads, launches one kernel per image, downloads).
+API int tlrefcuda_resize_normalize(const uint8_t* const* data, const int* ws, const int* hs, int n, int dst_h,
+                                   int dst_w, const float* mean, const float* std_, float* out) {
+    std::vector<turboloader::cuda::ImageRef> imgs(n);
+    for (int i = 0; i < n; ++i) imgs[i] = {data[i], ws[i], hs[i]};
+    return turboloader::cuda::resize_normalize_batch(imgs, dst_h, dst_w, mean, std_, out) ? 1 : 0;
+}
+API int tlrefcuda_crop_resize_normalize(const uint8_t* const* data, const int* ws, const int* hs,
+                                        const float* crops_xywh, const int* flips, int n, int dst_h, int dst_w,
+                                        const float* mean, const float* std_, float* out) {
+    std::vector<turboloader::cuda::ImageRef> imgs(n);
+    std::vector<turboloader::cuda::CropParams> cps(n);
+    for (int i = 0; i < n; ++i) {
+        imgs[i] = {data[i], ws[i], hs[i]};
+        cps[i] = {crops_xywh[4 * i], crops_xywh[4 * i + 1], crops_xywh[4 * i + 2], crops_xywh[4 * i + 3], flips[i]};
+    }
+    return turboloader::cuda::crop_resize_normalize_batch(imgs, cps, dst_h, dst_w, mean, std_, out) ? 1 : 0;
+}

@@ -277,3 +277,36 @@ def test_resident_loader_train_aug():
             want = O.fused_batch(flat, offsets, sizes, idx, boxes[b * 10:(b + 1) * 10], flips[b * 10:(b + 1) * 10], 32, 32,
                                  MEAN, STD, True)
             assert np.array_equal(x.cpu().numpy(), want)
+
+
+@pytest.mark.skipif(O.ref_cuda() is None, reason="reference CUDA kernels were not compiled (oracle/_ref)")
+def test_against_the_reference_gpu_kernels():
+    """The reference's own CUDA kernels (compiled in place for this GPU) as a second statement of the
+    math.  Normalize / gather: they divide by 255 where the CPU path multiplies by 1/255, so the
+    agreement is to rounding, not to the bit (the reference reports 4e-07 against numpy).  Resize:
+    they skip the 8-bit truncation of the CPU path, so they sit within one code step of it."""
+    import torch
+    lib = O.ref_cuda()
+    assert lib.tlrefcuda_available() == 1
+    data = _dataset(64, 32, seed=13)
+    gpu = torch.from_numpy(data).cuda()
+    mean = np.asarray(MEAN, np.float32)
+    std = np.asarray(STD, np.float32)
+    f32p = C.POINTER(C.c_float)
+    sel = torch.from_numpy(np.random.RandomState(1).permutation(64)[:40].astype(np.int64)).cuda()
+    rptr = lib.tlrefcuda_normalize_resident_gather(gpu.data_ptr(), sel.data_ptr(), 40, 32, 32,
+                                                   mean.ctypes.data_as(f32p), std.ctypes.data_as(f32p))
+    assert rptr
+    ref = torch.as_tensor(t._CudaArray(rptr, (40, 3, 32, 32)), device="cuda").cpu().numpy()
+    ours = torch.as_tensor(t._CudaArray(t.cuda_normalize_resident_gather(gpu.data_ptr(), sel.data_ptr(), 40, 32, 32),
+                                        (40, 3, 32, 32)), device="cuda").cpu().numpy()
+    assert np.abs(ours - ref).max() < 1e-6
+    # full-image resize of host images: within one 8-bit code step of the reference GPU kernel
+    rs = np.random.RandomState(2)
+    images = [rs.randint(0, 256, size=(h, w, 3), dtype=np.uint8) for h, w in [(40, 60), (64, 64), (33, 21)]]
+    ref = O.ref_cuda_crop_resize_normalize(images, None, None, 24, 24, MEAN, STD)
+    ours = t.cuda_resize_normalize(images, 24, 24)
+    step = 1.0 / (255.0 * np.asarray(STD, np.float64)).reshape(1, 3, 1, 1)
+    d = np.abs(ours.astype(np.float64) - ref)
+    # 1.001: the two coordinate formulas round differently, which moves a blend by ~2e-4 of a code
+    assert (d <= step * 1.001).all() and d.mean() > 1e-4  # truncation really differs, by < 1 code
