@@ -198,6 +198,21 @@ TLB_API uintptr_t tlb_normalize_resident_gather_batch(uintptr_t src_dev, uintptr
                                                       int32_t h, int32_t w, const float mean[3],
                                                       const float std_[3]);
 
+/* ---- back-to-back launches ----------------------------------------------------------------
+ * No counterpart in the reference (its loaders synchronise after every batch).
+ * With enable != 0 every later tlb_fused_transform launch is made with programmatic stream
+ * serialization: when the work directly before it in its stream is another tlb_fused_transform
+ * launch, it may start while that launch drains its last CTAs, so consecutive batches leave no
+ * SM idle between them (the other entry points are unaffected: they stage their inputs in the
+ * stream themselves and keep full stream order).  The kernel does not wait for its predecessor,
+ * hence the condition the caller accepts by enabling this: a KERNEL placed directly before a
+ * tlb_fused_transform call in the same stream must neither write that call's inputs nor read or
+ * write its outputs (copies, memsets and event waits always keep full stream order, and two
+ * batches of this library never depend on one another).  A stream that carries only this
+ * library's calls -- a loader's own prefetch stream handing batches over by events -- meets it.
+ * Off by default; process-wide; returns the previous setting. */
+TLB_API int tlb_set_launch_overlap(int enable);
+
 /* ---- introspection ---------------------------------------------------------------------
  * Launch geometry the fused kernel would use for `desc` (for tests and the
  * benchmark's launch/byte accounting).  Any out pointer may be NULL. */

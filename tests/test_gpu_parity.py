@@ -127,3 +127,31 @@ def test_invalid_samples_are_zero_filled_and_reported():
     for k in (0, 1, 5):
         assert np.array_equal(res["out"][k], good[k])
     assert np.array_equal(res["indices"], wl.sel)
+
+
+def test_back_to_back_launches_may_overlap():
+    """tlb_set_launch_overlap: consecutive launches into distinct outputs give the same bits as
+    serialized launches; the switch reports its previous setting and defaults to off."""
+    import torch
+
+    import turboloader_b200 as t
+    assert t.set_launch_overlap(True) is False
+    try:
+        wl = S.config2(n=24, seed=5, lo=60, hi=140, dst=64)
+        want = expected(wl)
+        flat = torch.from_numpy(wl.src).cuda()
+        offs = torch.from_numpy(wl.offsets).cuda()
+        sizes = torch.from_numpy(np.ascontiguousarray(wl.sizes)).cuda()
+        boxes = torch.from_numpy(np.ascontiguousarray(wl.boxes)).cuda()
+        flips = torch.from_numpy(wl.flips).cuda()
+        outs = [torch.full((wl.n, 3, 64, 64), -7.0, device="cuda") for _ in range(8)]
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for o in outs:
+            t.fused_transform(flat, n=wl.n, dst_h=64, dst_w=64, out=o, src_offsets=offs, src_sizes=sizes, boxes=boxes,
+                              flips=flips, mean=wl.mean, std=wl.std, max_crop_w=int(wl.boxes[:, 2].max()), status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for o in outs:
+            assert np.array_equal(o.cpu().numpy(), want)
+    finally:
+        assert t.set_launch_overlap(False) is True

@@ -111,6 +111,8 @@ def load() -> C.CDLL:
     lib.tlb_fused_plan.restype = C.c_int
     lib.tlb_fused_plan.argtypes = [C.POINTER(TransformDesc)] + [C.POINTER(C.c_int32)] * 5
     lib.tlb_launch_count.restype = C.c_uint64
+    lib.tlb_set_launch_overlap.restype = C.c_int
+    lib.tlb_set_launch_overlap.argtypes = [C.c_int]
     i64p = C.POINTER(C.c_int64)
     lib.tlb_shard_indices.restype = C.c_int64
     lib.tlb_shard_indices.argtypes = [C.c_int32, C.c_int64, C.c_int64, C.c_int64, i64p, C.c_int64]

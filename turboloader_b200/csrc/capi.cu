@@ -221,14 +221,17 @@ int derive_max_crop_w(const tlb_transform_desc& d) {
     return d.src_w;
 }
 
-int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream) {
+// `may_overlap`: the launch may start before the previous fused launch in the stream has drained
+// (only when the caller enabled it, and only for the entry point whose inputs the library did not
+// itself produce in the stream just before).
+int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool may_overlap = false) {
     int dev;
     if (int rc = current_device(&dev)) return rc;
     if (int rc = ensure_prepared(g_dev[dev])) return rc;
     tlb::FusedParams p{};
     fill_params(d, p);
     if (int rc = make_plan(d, max_crop_w, p.plan)) return rc;
-    cudaError_t e = static_cast<cudaError_t>(tlb::launch_fused(p, d.out_dtype, d.out_layout, stream));
+    cudaError_t e = static_cast<cudaError_t>(tlb::launch_fused(p, d.out_dtype, d.out_layout, stream, may_overlap));
     if (e != cudaSuccess) return cuda_fail(e, "fused_transform_kernel launch");
     return TLB_OK;
 }
@@ -670,7 +673,7 @@ int tlb_fused_transform(const tlb_transform_desc* desc, void* stream) {
     const int mcw = derive_max_crop_w(*desc);
     if (mcw <= 0)
         return fail(TLB_ERR_INVALID_ARG, "max_crop_w is required when sizes and boxes are per-sample device tables");
-    return launch_desc(*desc, mcw, stream);
+    return launch_desc(*desc, mcw, stream, /*may_overlap=*/true);
 }
 
 int tlb_fused_transform_host_params(const tlb_transform_desc* desc, void* stream) {
@@ -779,6 +782,8 @@ int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block
     if (tile_cols) *tile_cols = pl.tile_cols;
     return TLB_OK;
 }
+
+int tlb_set_launch_overlap(int enable) { return tlb::set_launch_overlap(enable); }
 
 uint64_t tlb_launch_count(void) { return tlb::launch_count() + g_extra_launches.load(std::memory_order_relaxed); }
 

@@ -74,9 +74,10 @@ inline __host__ __device__ int raw_rows_for(int var_bytes, int own_pitch, int st
 }
 
 // Implemented in fused_transform.cu.  Returns a cudaError_t as int.
-int launch_fused(const FusedParams& p, int out_dtype, int out_layout, void* stream);
+int launch_fused(const FusedParams& p, int out_dtype, int out_layout, void* stream, bool may_overlap);
 // One-time per-device opt-in to large dynamic shared memory; returns a cudaError_t as int.
 int prepare_device();
 unsigned long long launch_count();
+int set_launch_overlap(int enable);  // returns the previous setting
 
 }  // namespace tlb

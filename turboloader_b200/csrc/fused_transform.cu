@@ -348,6 +348,11 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
     const int warp = tid >> 5;
     const int strips = pl.strips;
 
+    // A batch never reads what the previous launch of this kernel wrote, so the next launch in the
+    // stream may start filling SMs as soon as every CTA of this one has been scheduled.  Only a
+    // launch made with programmatic stream serialization reacts to this; otherwise it is a no-op.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     // ---- which tile of which sample ------------------------------------------------
     unsigned bid = blockIdx.x;
     const int ct = static_cast<int>(bid % static_cast<unsigned>(pl.n_col_tiles));
@@ -646,11 +651,28 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
 }
 
 std::atomic<unsigned long long> g_launches{0};
+std::atomic<int> g_overlap{0};
 
 template <int DTYPE, int LAYOUT>
-int launch_one(const FusedParams& p, cudaStream_t st) {
+int launch_one(const FusedParams& p, cudaStream_t st, bool may_overlap) {
     auto kern = fused_transform_kernel<DTYPE, LAYOUT>;
-    kern<<<static_cast<unsigned>(p.plan.grid), 32 * (p.plan.strips + 1), p.plan.smem_bytes, st>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(p.plan.grid));
+    cfg.blockDim = dim3(32 * (p.plan.strips + 1));
+    cfg.dynamicSmemBytes = static_cast<size_t>(p.plan.smem_bytes);
+    cfg.stream = st;
+    // Programmatic stream serialization: when the work directly before this launch in the stream
+    // is a launch of this same kernel (which signals early, see the top of the kernel), this one
+    // may begin while that one drains its last CTAs; the head and tail of back-to-back batches
+    // then overlap instead of leaving SMs idle.  Behind a copy, a memset or a kernel that does not
+    // signal early the usual stream order holds.  The caller opts in (tlb_set_launch_overlap)
+    // because the kernel does not wait on its predecessor: see the header for the condition.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (may_overlap && g_overlap.load(std::memory_order_relaxed)) ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kern, p);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return static_cast<int>(cudaGetLastError());
 }
@@ -671,11 +693,13 @@ int prepare_device() {
     return e;
 }
 
-int launch_fused(const FusedParams& p, int out_dtype, int out_layout, void* stream) {
+int launch_fused(const FusedParams& p, int out_dtype, int out_layout, void* stream, bool may_overlap) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (out_dtype == 0) return out_layout == 0 ? launch_one<0, 0>(p, st) : launch_one<0, 1>(p, st);
-    return out_layout == 0 ? launch_one<1, 0>(p, st) : launch_one<1, 1>(p, st);
+    if (out_dtype == 0) return out_layout == 0 ? launch_one<0, 0>(p, st, may_overlap) : launch_one<0, 1>(p, st, may_overlap);
+    return out_layout == 0 ? launch_one<1, 0>(p, st, may_overlap) : launch_one<1, 1>(p, st, may_overlap);
 }
+
+int set_launch_overlap(int enable) { return g_overlap.exchange(enable ? 1 : 0, std::memory_order_relaxed); }
 
 unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 

@@ -30,6 +30,14 @@ def cuda_device_name(device: int = 0) -> str:
     return buf.value.decode()
 
 
+def set_launch_overlap(enable: bool) -> bool:
+    """Let consecutive launches of the fused kernel overlap head to tail (``tlb_set_launch_overlap``).
+
+    Enable it only for a stream in which the kernel directly before each launch is another launch
+    of this library (or does not touch the launch's inputs and outputs); returns the old setting."""
+    return bool(_capi.load().tlb_set_launch_overlap(1 if enable else 0))
+
+
 def launch_count() -> int:
     return int(_capi.load().tlb_launch_count())
 
