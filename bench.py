@@ -349,6 +349,80 @@ def reference_gpu_leg(wl, lib, torch, device, sample=512):
     return res
 
 
+def video_leg(torch, device, stream, peak, steps=30):
+    """Fused YUV 4:2:0 clip assembly: 8 clips x 16 NV12 frames of 1280x720 (seeded noise), one crop
+    window + flip per clip (area 35-100 % of the frame), -> (128, 3, 224, 224) float32, one launch
+    per step.  Algorithmic bytes per frame: 1.5 x crop_w x crop_h read + 3 x 224 x 224 x 4 written.
+    Beside it the reference's own clip kernel (one call per clip, as its loader does) on the same
+    frames, when it was compiled."""
+    from oracle import oracle as O
+    from turboloader_b200 import ops
+
+    n_clips, T, W, H, D = 8, 16, 1280, 720, 224
+    n = n_clips * T
+    g = torch.Generator(device=device)
+    g.manual_seed(11)
+    sets = []
+    for _ in range(2):
+        yb = torch.randint(0, 256, (n, H, W), dtype=torch.uint8, device=device, generator=g)
+        uv = torch.randint(0, 256, (n, H // 2, W), dtype=torch.uint8, device=device, generator=g)
+        out = torch.empty((n, 3, D, D), dtype=torch.float32, device=device)
+        sets.append((yb, uv, out))
+    rs = np.random.RandomState(5)
+    crops = np.zeros((n_clips, 4), np.float32)
+    for c in range(n_clips):
+        area = rs.uniform(0.35, 1.0)
+        cw = int(min(W, round(W * np.sqrt(area))))
+        ch = int(min(H, round(H * np.sqrt(area))))
+        crops[c] = (rs.randint(0, W - cw + 1), rs.randint(0, H - ch + 1), cw, ch)
+    flips = rs.randint(0, 2, n_clips).astype(np.int32)
+    rd = float((1.5 * crops[:, 2] * crops[:, 3]).sum() * T)
+    wr = float(n * 3 * D * D * 4)
+
+    def ptrs(yb, uv):
+        yp = [yb.data_ptr() + i * H * W for i in range(n)]
+        cb = [uv.data_ptr() + i * (H // 2) * W for i in range(n)]
+        return yp, cb, [p + 1 for p in cb]
+
+    plist = [ptrs(yb, uv) for yb, uv, _ in sets]
+
+    def step(i):
+        yp, cb, cr = plist[i % 2]
+        ops.video_yuv420(yp, cb, cr, y_stride=W, c_stride=W, c_px_stride=2, src_w=W, src_h=H, out=sets[i % 2][2],
+                         crops=crops, flips=flips, clip_len=T, stream=stream)
+
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for i in range(steps):
+        step(i)
+    stop.record(stream)
+    torch.cuda.synchronize()
+    sec = start.elapsed_time(stop) / 1e3 / steps
+    res = {"workload": f"{n_clips} clips x {T} NV12 frames {W}x{H} -> {D}x{D} f32, per-clip crop window + flip",
+           "frames_per_s": n / sec, "GB_per_s": (rd + wr) / sec / 1e9, "frac_of_peak": (rd + wr) / sec / 1e9 / peak,
+           "algorithmic_bytes_per_launch": rd + wr, "kernel": "yuv420_kernel", "launches_per_step": 1}
+    if O.ref_cuda() is not None:
+        yp, cb, cr = plist[0]
+
+        def ref_step():
+            for c in range(n_clips):
+                sl = slice(c * T, (c + 1) * T)
+                O.ref_cuda_video(yp[sl], cb[sl], cr[sl], W, W, 2, W, H, D, D, (0.485, 0.456, 0.406), (0.229, 0.224, 0.225),
+                                 crop=crops[c], flip=bool(flips[c]))
+
+        ref_step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(5):
+            ref_step()
+        torch.cuda.synchronize()
+        res["reference_gpu_frames_per_s"] = n * 5 / (time.perf_counter() - t0)
+    return res
+
+
 # ---- main ----------------------------------------------------------------------------------
 
 def run_reference_arm(args):
@@ -558,6 +632,10 @@ def main():
                 rg = {"error": repr(e)}
             if rg is not None:
                 line["reference_gpu"] = rg
+            try:
+                line["video_clip"] = video_leg(torch, device, stream, peak)
+            except Exception as e:
+                line["video_clip"] = {"error": repr(e)}
         others = {}
         for name in WORKLOADS:
             if name == args.workload:

@@ -198,6 +198,52 @@ TLB_API uintptr_t tlb_normalize_resident_gather_batch(uintptr_t src_dev, uintptr
                                                       int32_t h, int32_t w, const float mean[3],
                                                       const float std_[3]);
 
+/* ---- YUV 4:2:0 video frames ----------------------------------------------------------------
+ * Replaces turboloader::cuda::video_yuv420_batch and video_clip_yuv420
+ * (src/cuda/cuda_transforms.hpp:65-81; kernels src/cuda/cuda_transforms.cu:143-268): decoded
+ * frames given as DEVICE plane addresses -> YUV->RGB (video range, BT.601 or BT.709), bilinear
+ * resize with MPEG chroma siting, clip to [0,1], normalize, planar (n,3,dst_h,dst_w) output.
+ * c_px_stride 1 = I420 (separate Cb / Cr planes), 2 = NV12 (cr address = cb address + 1 in one
+ * interleaved plane).  Strides are shared by all frames.  One kernel launch per call, whatever n. */
+typedef struct tlb_video_desc {
+    const uintptr_t* y_ptrs;  /* HOST arrays of n device addresses each */
+    const uintptr_t* cb_ptrs;
+    const uintptr_t* cr_ptrs;
+    int32_t n;                /* frames */
+    int32_t y_stride;         /* bytes between luma rows (>= src_w) */
+    int32_t c_stride;         /* bytes between chroma rows */
+    int32_t c_px_stride;      /* 1 or 2 */
+    int32_t src_w, src_h;
+    int32_t dst_h, dst_w;
+    const float* crops;       /* HOST, (x, y, w, h) in source pixels per clip; NULL = whole-frame
+                                 resize (the video_yuv420_batch sampling rule) */
+    const int32_t* flips;     /* HOST, one per clip, or NULL (only read when crops != NULL) */
+    int32_t clip_len;         /* consecutive frames sharing one crops/flips entry; 0 = all n */
+    int32_t bt709;            /* 0: BT.601 matrix, 1: BT.709 */
+    float mean[3];
+    float std[3];             /* (rgb01 - mean) * (1.0f / std) */
+    void* out;                /* DEVICE, caller-allocated (n,3,dst_h,dst_w) */
+    int32_t out_dtype;        /* TLB_F32 / TLB_BF16 */
+} tlb_video_desc;
+
+/* Asynchronous form on the caller's stream: uploads the small address/crop tables through a
+ * pinned ring and launches once; no synchronisation. */
+TLB_API int tlb_video_yuv420(const tlb_video_desc* desc, void* stream);
+/* The reference's two pointer-returning forms, same arguments and lifetime rule: the result is
+ * a library-owned float32 (n,3,dst_h,dst_w) device buffer, double-buffered, valid until the next
+ * call of either function; the call synchronises; returns 0 on error. */
+TLB_API uintptr_t tlb_video_yuv420_batch(const uintptr_t* y_ptrs, const uintptr_t* cb_ptrs,
+                                         const uintptr_t* cr_ptrs, int32_t n, int32_t y_stride,
+                                         int32_t c_stride, int32_t c_px_stride, int32_t src_w,
+                                         int32_t src_h, int32_t dst_h, int32_t dst_w, int32_t bt709,
+                                         const float mean[3], const float std_[3]);
+TLB_API uintptr_t tlb_video_clip_yuv420(const uintptr_t* y_ptrs, const uintptr_t* cb_ptrs,
+                                        const uintptr_t* cr_ptrs, int32_t n, int32_t y_stride,
+                                        int32_t c_stride, int32_t c_px_stride, int32_t src_w,
+                                        int32_t src_h, int32_t dst_h, int32_t dst_w,
+                                        const float crop[4], int32_t flip, int32_t bt709,
+                                        const float mean[3], const float std_[3]);
+
 /* ---- back-to-back launches ----------------------------------------------------------------
  * No counterpart in the reference (its loaders synchronise after every batch).
  * With enable != 0 every later tlb_fused_transform launch is made with programmatic stream

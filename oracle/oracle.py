@@ -34,8 +34,8 @@ _libs: dict[str, C.CDLL] = {}
 
 def build_port(force: bool = False) -> str:
     """Compile the C restatement if it is missing (gcc only, no reference tree needed)."""
-    src = os.path.join(HERE, "fused_ref.c")
-    if force or not os.path.exists(PORT_SO) or os.path.getmtime(PORT_SO) < os.path.getmtime(src):
+    srcs = [os.path.join(HERE, "fused_ref.c"), os.path.join(HERE, "video_ref.c")]
+    if force or not os.path.exists(PORT_SO) or os.path.getmtime(PORT_SO) < max(os.path.getmtime(s) for s in srcs):
         subprocess.check_call(["make", "-C", HERE, "port"], stdout=subprocess.DEVNULL)
     return PORT_SO
 
@@ -83,6 +83,8 @@ def _load(impl: str) -> C.CDLL:
         lib.tlo_f32_to_bf16_array.argtypes = [_f32p, C.POINTER(C.c_uint16), C.c_size_t]
         lib.tlo_nchw_to_nhwc.restype = None
         lib.tlo_nchw_to_nhwc.argtypes = [_f32p, _f32p, C.c_int, C.c_int, C.c_int]
+        lib.tlo_yuv420_frame.restype = None
+        lib.tlo_yuv420_frame.argtypes = [_u8p, _u8p, _u8p] + [C.c_int] * 8 + [_f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p]
     else:
         flavour = impl.split("-", 1)[1] if "-" in impl else "parity"
         if not ref_available(flavour):
@@ -208,7 +210,8 @@ def ref_direct_order(total, shuffle, seed, epoch, distributed, rank, world):
 # ---- the reference's own CUDA kernels, compiled in place (oracle/_ref/libtl_ref_cuda.so) ---------
 
 REF_CUDA_SO = os.path.join(REF_DIR, "libtl_ref_cuda.so")
-_ref_cuda = None
+REF_CUDA_NOFMA_SO = os.path.join(REF_DIR, "libtl_ref_cuda_nofma.so")  # same sources, --fmad=false
+_ref_cuda = {}
 
 
 def build_ref_cuda(ref_root: str = "/root/reference") -> bool:
@@ -218,13 +221,14 @@ def build_ref_cuda(ref_root: str = "/root/reference") -> bool:
     return True
 
 
-def ref_cuda():
-    """ctypes handle of the reference GPU entry points, or None when the library is absent."""
-    global _ref_cuda
-    if _ref_cuda is None:
-        if not os.path.exists(REF_CUDA_SO):
+def ref_cuda(nofma: bool = False):
+    """ctypes handle of the reference GPU entry points, or None when the library is absent.
+    ``nofma`` selects the build without FMA contraction (every fp32 operation rounds separately)."""
+    path = REF_CUDA_NOFMA_SO if nofma else REF_CUDA_SO
+    if path not in _ref_cuda:
+        if not os.path.exists(path):
             return None
-        lib = C.CDLL(REF_CUDA_SO)
+        lib = C.CDLL(path)
         lib.tlrefcuda_available.restype = C.c_int
         lib.tlrefcuda_normalize_resident.restype = C.c_size_t
         lib.tlrefcuda_normalize_resident.argtypes = [C.c_size_t, C.c_int, C.c_int, C.c_int, _f32p, _f32p]
@@ -236,8 +240,54 @@ def ref_cuda():
         lib.tlrefcuda_crop_resize_normalize.restype = C.c_int
         lib.tlrefcuda_crop_resize_normalize.argtypes = [pp, _i32p, _i32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int, _f32p,
                                                         _f32p, _f32p]
-        _ref_cuda = lib
-    return _ref_cuda
+        up = C.POINTER(C.c_size_t)
+        lib.tlrefcuda_video_yuv420_batch.restype = C.c_size_t
+        lib.tlrefcuda_video_yuv420_batch.argtypes = [up, up, up] + [C.c_int] * 9 + [_f32p, _f32p]
+        lib.tlrefcuda_video_clip_yuv420.restype = C.c_size_t
+        lib.tlrefcuda_video_clip_yuv420.argtypes = [up, up, up] + [C.c_int] * 8 + [_f32p, C.c_int, C.c_int, _f32p, _f32p]
+        _ref_cuda[path] = lib
+    return _ref_cuda[path]
+
+
+def ref_cuda_video(y_ptrs, cb_ptrs, cr_ptrs, y_stride, c_stride, c_px_stride, src_w, src_h, dst_h, dst_w, mean, std,
+                   crop=None, flip=False, bt709=False, nofma=False):
+    """The reference's video_yuv420_batch (crop None) / video_clip_yuv420 on device plane addresses;
+    returns the device address of its (n,3,dst_h,dst_w) float32 result (valid until its next call)."""
+    lib = ref_cuda(nofma)
+    n = len(y_ptrs)
+    arrs = [(C.c_size_t * n)(*[int(p) for p in ps]) for ps in (y_ptrs, cb_ptrs, cr_ptrs)]
+    mean = np.asarray(mean, dtype=np.float32)
+    std = np.asarray(std, dtype=np.float32)
+    if crop is None:
+        out = lib.tlrefcuda_video_yuv420_batch(*arrs, n, y_stride, c_stride, c_px_stride, src_w, src_h, dst_h, dst_w,
+                                               int(bool(bt709)), _ptr(mean, _f32p), _ptr(std, _f32p))
+    else:
+        cr = np.asarray(crop, dtype=np.float32)
+        out = lib.tlrefcuda_video_clip_yuv420(*arrs, n, y_stride, c_stride, c_px_stride, src_w, src_h, dst_h, dst_w,
+                                              _ptr(cr, _f32p), int(bool(flip)), int(bool(bt709)), _ptr(mean, _f32p),
+                                              _ptr(std, _f32p))
+    if not out:
+        raise RuntimeError("reference video call failed")
+    return int(out)
+
+
+def yuv420_frame(y, cb, cr, c_px_stride, src_w, src_h, dst_h, dst_w, mean, std, crop=None, flip=False, bt709=False,
+                 y_stride=None, c_stride=None):
+    """CPU restatement (oracle/video_ref.c) of the fused YUV 4:2:0 transform for ONE frame:
+    ``y``, ``cb``, ``cr`` are uint8 arrays holding the planes (for NV12 pass the interleaved plane as
+    ``cb`` and ``cb.reshape(-1)[1:]`` as ``cr``); returns float32 (3, dst_h, dst_w)."""
+    lib = _load("port")
+    y_stride = y.strides[0] if y_stride is None else y_stride
+    c_stride = cb.strides[0] if c_stride is None else c_stride
+    mean = np.asarray(mean, dtype=np.float32)
+    std = np.asarray(std, dtype=np.float32)
+    cw = np.zeros(4, np.float32) if crop is None else np.asarray(crop, dtype=np.float32)
+    out = np.empty((3, dst_h, dst_w), dtype=np.float32)
+    lib.tlo_yuv420_frame(y.ctypes.data_as(_u8p), cb.ctypes.data_as(_u8p), cr.ctypes.data_as(_u8p), int(y_stride),
+                         int(c_stride), int(c_px_stride), src_w, src_h, dst_w, dst_h, 0 if crop is None else 1,
+                         _ptr(cw, _f32p), int(bool(flip)), int(bool(bt709)), _ptr(mean, _f32p), _ptr(std, _f32p),
+                         _ptr(out, _f32p))
+    return out
 
 
 def ref_cuda_crop_resize_normalize(images, crops_xywh, flips, dst_h, dst_w, mean, std):

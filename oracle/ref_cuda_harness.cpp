@@ -42,3 +42,22 @@ API int tlrefcuda_crop_resize_normalize(const uint8_t* const* data, const int* w
     }
     return turboloader::cuda::crop_resize_normalize_batch(imgs, cps, dst_h, dst_w, mean, std_, out) ? 1 : 0;
 }
+
+// video_yuv420_batch / video_clip_yuv420 (cuda_transforms.hpp:65-81): n frames given as device
+// plane addresses; returns the device address of the library-owned (n,3,dst_h,dst_w) float32
+// result (valid until the next call), 0 on error.
+API uintptr_t tlrefcuda_video_yuv420_batch(const uintptr_t* y, const uintptr_t* cb, const uintptr_t* cr, int n,
+                                           int y_stride, int c_stride, int c_px_stride, int src_w, int src_h,
+                                           int dst_h, int dst_w, int bt709, const float* mean, const float* std_) {
+    std::vector<uintptr_t> vy(y, y + n), vcb(cb, cb + n), vcr(cr, cr + n);
+    return turboloader::cuda::video_yuv420_batch(vy, vcb, vcr, y_stride, c_stride, c_px_stride, src_w, src_h, dst_h,
+                                                 dst_w, bt709 != 0, mean, std_);
+}
+API uintptr_t tlrefcuda_video_clip_yuv420(const uintptr_t* y, const uintptr_t* cb, const uintptr_t* cr, int n,
+                                          int y_stride, int c_stride, int c_px_stride, int src_w, int src_h,
+                                          int dst_h, int dst_w, const float* crop, int flip, int bt709,
+                                          const float* mean, const float* std_) {
+    std::vector<uintptr_t> vy(y, y + n), vcb(cb, cb + n), vcr(cr, cr + n);
+    return turboloader::cuda::video_clip_yuv420(vy, vcb, vcr, y_stride, c_stride, c_px_stride, src_w, src_h, dst_h,
+                                                dst_w, crop, flip != 0, bt709 != 0, mean, std_);
+}

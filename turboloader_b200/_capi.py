@@ -51,6 +51,31 @@ class TransformDesc(C.Structure):
     ]
 
 
+class VideoDesc(C.Structure):
+    """``tlb_video_desc`` (field order and types must match the header)."""
+    _fields_ = [
+        ("y_ptrs", C.c_void_p),
+        ("cb_ptrs", C.c_void_p),
+        ("cr_ptrs", C.c_void_p),
+        ("n", C.c_int32),
+        ("y_stride", C.c_int32),
+        ("c_stride", C.c_int32),
+        ("c_px_stride", C.c_int32),
+        ("src_w", C.c_int32),
+        ("src_h", C.c_int32),
+        ("dst_h", C.c_int32),
+        ("dst_w", C.c_int32),
+        ("crops", C.c_void_p),
+        ("flips", C.c_void_p),
+        ("clip_len", C.c_int32),
+        ("bt709", C.c_int32),
+        ("mean", C.c_float * 3),
+        ("std", C.c_float * 3),
+        ("out", C.c_void_p),
+        ("out_dtype", C.c_int32),
+    ]
+
+
 class ImageRef(C.Structure):
     _fields_ = [("data", C.c_void_p), ("w", C.c_int32), ("h", C.c_int32)]
 
@@ -108,6 +133,13 @@ def load() -> C.CDLL:
     lib.tlb_normalize_resident_gather_batch.restype = C.c_size_t
     lib.tlb_normalize_resident_gather_batch.argtypes = [C.c_size_t, C.c_size_t, C.c_int32, C.c_int32, C.c_int32,
                                                         _F3, _F3]
+    up = C.POINTER(C.c_size_t)
+    lib.tlb_video_yuv420.restype = C.c_int
+    lib.tlb_video_yuv420.argtypes = [C.POINTER(VideoDesc), C.c_void_p]
+    lib.tlb_video_yuv420_batch.restype = C.c_size_t
+    lib.tlb_video_yuv420_batch.argtypes = [up, up, up] + [C.c_int32] * 9 + [_F3, _F3]
+    lib.tlb_video_clip_yuv420.restype = C.c_size_t
+    lib.tlb_video_clip_yuv420.argtypes = [up, up, up] + [C.c_int32] * 8 + [C.c_float * 4, C.c_int32, C.c_int32, _F3, _F3]
     lib.tlb_fused_plan.restype = C.c_int
     lib.tlb_fused_plan.argtypes = [C.POINTER(TransformDesc)] + [C.POINTER(C.c_int32)] * 5
     lib.tlb_launch_count.restype = C.c_uint64

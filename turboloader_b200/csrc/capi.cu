@@ -20,6 +20,7 @@
 
 #include "../../include/turboloader_b200.h"
 #include "fused_params.h"
+#include "video_params.h"
 #include "host_gather.h"
 
 namespace {
@@ -75,6 +76,9 @@ struct DeviceState {
     void* out_ring[4] = {nullptr, nullptr, nullptr, nullptr};  // legacy pointer-returning forms
     size_t out_cap[4] = {0, 0, 0, 0};
     int out_next = 0;
+    void* video_out[2] = {nullptr, nullptr};  // pointer-returning video forms: valid until the next call
+    size_t video_cap[2] = {0, 0};
+    int video_next = 0;
     void* sync_out = nullptr;  // device result of the synchronous host-image forms
     size_t sync_out_cap = 0;
     cudaStream_t stream = nullptr;  // private stream of the synchronous forms
@@ -785,7 +789,9 @@ int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block
 
 int tlb_set_launch_overlap(int enable) { return tlb::set_launch_overlap(enable); }
 
-uint64_t tlb_launch_count(void) { return tlb::launch_count() + g_extra_launches.load(std::memory_order_relaxed); }
+uint64_t tlb_launch_count(void) {
+    return tlb::launch_count() + tlb::video_launch_count() + g_extra_launches.load(std::memory_order_relaxed);
+}
 
 }  // extern "C"
 
@@ -924,6 +930,181 @@ int tlb_crop_resize_normalize_to_device_static(const tlb_image_ref* imgs, const 
     d.status = status_dev;
     if (int rc = check_common(&d)) return rc;
     return launch_desc(d, max_cw, stream);
+}
+
+}  // extern "C"
+
+namespace {
+
+// ---- YUV 4:2:0 video ------------------------------------------------------------------------
+int check_video(const tlb_video_desc* d) {
+    if (!d) return fail(TLB_ERR_INVALID_ARG, "video descriptor is NULL");
+    if (d->n < 0) return fail(TLB_ERR_INVALID_ARG, "n < 0");
+    if (d->n == 0) return TLB_OK;
+    if (!d->y_ptrs || !d->cb_ptrs || !d->cr_ptrs || !d->out)
+        return fail(TLB_ERR_INVALID_ARG, "video: a plane address array or the output is NULL");
+    if (d->src_w <= 0 || d->src_h <= 0 || d->dst_w <= 0 || d->dst_h <= 0)
+        return fail(TLB_ERR_INVALID_ARG, "video: non-positive frame or output size");
+    if (d->c_px_stride != 1 && d->c_px_stride != 2)
+        return fail(TLB_ERR_INVALID_ARG, "video: c_px_stride must be 1 (I420) or 2 (NV12)");
+    if (d->y_stride < d->src_w || d->c_stride < ((d->src_w + 1) / 2 - 1) * d->c_px_stride + 1)
+        return fail(TLB_ERR_INVALID_ARG, "video: a row stride is shorter than the row");
+    if (static_cast<long long>(d->y_stride) * d->src_h > 0x7fffffffll)
+        return fail(TLB_ERR_TOO_LARGE, "video: a plane exceeds 2 GiB");
+    if (d->out_dtype != TLB_F32 && d->out_dtype != TLB_BF16) return fail(TLB_ERR_INVALID_ARG, "video: bad out_dtype");
+    if (d->clip_len < 0) return fail(TLB_ERR_INVALID_ARG, "video: clip_len < 0");
+    if (d->n > 65535) return fail(TLB_ERR_TOO_LARGE, "video: at most 65535 frames per call");
+    for (int c = 0; c < 3; ++c)
+        if (!(d->std[c] != 0.0f) || !std::isfinite(d->std[c]) || !std::isfinite(d->mean[c]))
+            return fail(TLB_ERR_INVALID_ARG, "video: std must be finite and non-zero, mean finite");
+    for (int i = 0; i < d->n; ++i)
+        if (!d->y_ptrs[i] || !d->cb_ptrs[i] || !d->cr_ptrs[i])
+            return fail(TLB_ERR_INVALID_ARG, "video: frame %d has a NULL plane address", i);
+    if (d->crops) {
+        const int clips = d->clip_len > 0 ? (d->n + d->clip_len - 1) / d->clip_len : 1;
+        for (int i = 0; i < 4 * clips; ++i)
+            if (!std::isfinite(d->crops[i])) return fail(TLB_ERR_BAD_BOX, "video: a crop window is not finite");
+    }
+    return TLB_OK;
+}
+
+int video_enqueue(const tlb_video_desc& d, void* stream) {
+    int dev;
+    if (int rc = current_device(&dev)) return rc;
+    DeviceState& st = g_dev[dev];
+    const size_t n = static_cast<size_t>(d.n);
+    const size_t clips = d.crops ? (d.clip_len > 0 ? (n + d.clip_len - 1) / d.clip_len : 1) : 0;
+    const size_t off_crop = (3 * n * sizeof(void*) + 15) & ~static_cast<size_t>(15);
+    const size_t off_flip = off_crop + clips * 16;
+    const size_t total = off_flip + clips * 4;
+    std::unique_lock<std::mutex> lk(st.mu);
+    Buffer& buf = st.params[st.params_next];
+    st.params_next = (st.params_next + 1) % 4;
+    if (int rc = grow(buf, total)) return rc;
+    lk.unlock();
+    auto* hb = static_cast<unsigned char*>(buf.host);
+    auto* db = static_cast<unsigned char*>(buf.dev);
+    auto* hp = reinterpret_cast<uintptr_t*>(hb);
+    for (size_t i = 0; i < n; ++i) {
+        hp[i] = d.y_ptrs[i];
+        hp[n + i] = d.cb_ptrs[i];
+        hp[2 * n + i] = d.cr_ptrs[i];
+    }
+    if (clips) {
+        std::memcpy(hb + off_crop, d.crops, clips * 16);
+        auto* hf = reinterpret_cast<int*>(hb + off_flip);
+        for (size_t i = 0; i < clips; ++i) hf[i] = d.flips ? (d.flips[i] != 0) : 0;
+    }
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    TLB_CUDA(cudaMemcpyAsync(buf.dev, buf.host, total, cudaMemcpyHostToDevice, cs));
+    tlb::VideoParams p{};
+    p.planes = reinterpret_cast<const unsigned char* const*>(db);
+    p.crops = clips ? reinterpret_cast<const float4*>(db + off_crop) : nullptr;
+    p.flips = clips ? reinterpret_cast<const int*>(db + off_flip) : nullptr;
+    p.n = d.n;
+    p.clip_len = d.clip_len;
+    p.y_stride = d.y_stride; p.c_stride = d.c_stride; p.c_px_stride = d.c_px_stride;
+    p.src_w = d.src_w; p.src_h = d.src_h; p.dst_w = d.dst_w; p.dst_h = d.dst_h;
+    p.bt709 = d.bt709 ? 1 : 0;
+    for (int c = 0; c < 3; ++c) {
+        p.mean[c] = d.mean[c];
+        p.inv_std[c] = 1.0f / d.std[c];  // cuda_transforms.cu:392 computes the reciprocal on the host, in fp32
+    }
+    p.out = d.out;
+    cudaError_t e = static_cast<cudaError_t>(tlb::launch_video(p, d.out_dtype, stream));
+    TLB_CUDA(cudaEventRecord(buf.done, cs));
+    buf.pending = true;
+    if (e != cudaSuccess) return cuda_fail(e, "yuv420_kernel launch");
+    return TLB_OK;
+}
+
+uintptr_t video_pointer_form(tlb_video_desc d) {
+    d.out = reinterpret_cast<void*>(1);  // placeholder so that validation sees a non-NULL output
+    d.out_dtype = TLB_F32;
+    if (d.n <= 0) {
+        fail(TLB_ERR_INVALID_ARG, "video: no frames");
+        return 0;
+    }
+    if (check_video(&d)) return 0;
+    int dev;
+    if (current_device(&dev)) return 0;
+    DeviceState& st = g_dev[dev];
+    void* out;
+    {
+        std::lock_guard<std::mutex> lk(st.mu);
+        if (!st.stream && cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking) != cudaSuccess) {
+            fail(TLB_ERR_CUDA, "cudaStreamCreate failed");
+            return 0;
+        }
+        const size_t bytes = static_cast<size_t>(d.n) * 3 * d.dst_h * d.dst_w * sizeof(float);
+        st.video_next ^= 1;
+        const int slot = st.video_next;
+        if (bytes > st.video_cap[slot]) {
+            if (st.video_out[slot]) cudaFree(st.video_out[slot]);
+            st.video_out[slot] = nullptr;
+            st.video_cap[slot] = 0;
+            cudaError_t e = cudaMalloc(&st.video_out[slot], bytes);
+            if (e != cudaSuccess) {
+                cuda_fail(e, "cudaMalloc(video output)");
+                return 0;
+            }
+            st.video_cap[slot] = bytes;
+        }
+        out = st.video_out[slot];
+    }
+    d.out = out;
+    if (video_enqueue(d, st.stream)) return 0;
+    cudaError_t e = cudaStreamSynchronize(st.stream);
+    if (e != cudaSuccess) {
+        cuda_fail(e, "cudaStreamSynchronize(video)");
+        return 0;
+    }
+    return reinterpret_cast<uintptr_t>(out);
+}
+
+}  // namespace
+
+extern "C" {
+
+int tlb_video_yuv420(const tlb_video_desc* desc, void* stream) {
+    if (int rc = check_video(desc)) return rc;
+    if (desc->n == 0) return TLB_OK;
+    return video_enqueue(*desc, stream);
+}
+
+uintptr_t tlb_video_yuv420_batch(const uintptr_t* y_ptrs, const uintptr_t* cb_ptrs, const uintptr_t* cr_ptrs,
+                                 int32_t n, int32_t y_stride, int32_t c_stride, int32_t c_px_stride, int32_t src_w,
+                                 int32_t src_h, int32_t dst_h, int32_t dst_w, int32_t bt709, const float mean[3],
+                                 const float std_[3]) {
+    if (!mean || !std_) {
+        fail(TLB_ERR_INVALID_ARG, "video: mean/std is NULL");
+        return 0;
+    }
+    tlb_video_desc d{};
+    d.y_ptrs = y_ptrs; d.cb_ptrs = cb_ptrs; d.cr_ptrs = cr_ptrs; d.n = n;
+    d.y_stride = y_stride; d.c_stride = c_stride; d.c_px_stride = c_px_stride;
+    d.src_w = src_w; d.src_h = src_h; d.dst_h = dst_h; d.dst_w = dst_w; d.bt709 = bt709;
+    for (int c = 0; c < 3; ++c) { d.mean[c] = mean[c]; d.std[c] = std_[c]; }
+    return video_pointer_form(d);
+}
+
+uintptr_t tlb_video_clip_yuv420(const uintptr_t* y_ptrs, const uintptr_t* cb_ptrs, const uintptr_t* cr_ptrs, int32_t n,
+                                int32_t y_stride, int32_t c_stride, int32_t c_px_stride, int32_t src_w, int32_t src_h,
+                                int32_t dst_h, int32_t dst_w, const float crop[4], int32_t flip, int32_t bt709,
+                                const float mean[3], const float std_[3]) {
+    if (!mean || !std_ || !crop) {
+        fail(TLB_ERR_INVALID_ARG, "video: mean/std/crop is NULL");
+        return 0;
+    }
+    tlb_video_desc d{};
+    d.y_ptrs = y_ptrs; d.cb_ptrs = cb_ptrs; d.cr_ptrs = cr_ptrs; d.n = n;
+    d.y_stride = y_stride; d.c_stride = c_stride; d.c_px_stride = c_px_stride;
+    d.src_w = src_w; d.src_h = src_h; d.dst_h = dst_h; d.dst_w = dst_w; d.bt709 = bt709;
+    d.crops = crop;
+    d.flips = &flip;
+    d.clip_len = 0;
+    for (int c = 0; c < 3; ++c) { d.mean[c] = mean[c]; d.std[c] = std_[c]; }
+    return video_pointer_form(d);
 }
 
 }  // extern "C"

@@ -30,6 +30,80 @@ def cuda_device_name(device: int = 0) -> str:
     return buf.value.decode()
 
 
+def _addr_array(ptrs):
+    arr = (C.c_size_t * len(ptrs))(*[int(p) for p in ptrs])
+    return arr
+
+
+def cuda_video_yuv420_batch(y_ptrs, cb_ptrs, cr_ptrs, y_stride, c_stride, c_px_stride, src_w, src_h, dst_h, dst_w,
+                            bt709=False, mean=IMAGENET_MEAN, std=IMAGENET_STD) -> int:
+    """Decoded YUV 4:2:0 frames (lists of device plane addresses) -> device address of a library-owned
+    (n, 3, dst_h, dst_w) float32 batch, valid until the next video call (same name, arguments and
+    lifetime as TurboLoader's binding, src/python/turboloader_bindings.cpp:1686-1709)."""
+    n = len(y_ptrs)
+    if not (len(cb_ptrs) == len(cr_ptrs) == n):
+        raise ValueError("y_ptrs, cb_ptrs and cr_ptrs must have the same length")
+    out = _capi.load().tlb_video_yuv420_batch(_addr_array(y_ptrs), _addr_array(cb_ptrs), _addr_array(cr_ptrs), n,
+                                              int(y_stride), int(c_stride), int(c_px_stride), int(src_w), int(src_h),
+                                              int(dst_h), int(dst_w), int(bool(bt709)), _capi.f3(mean), _capi.f3(std))
+    if not out:
+        raise RuntimeError("cuda_video_yuv420_batch failed: " + _capi.load().tlb_last_error().decode(errors="replace"))
+    return int(out)
+
+
+def cuda_video_clip_yuv420(y_ptrs, cb_ptrs, cr_ptrs, y_stride, c_stride, c_px_stride, src_w, src_h, dst_h, dst_w,
+                           crop, flip=False, bt709=False, mean=IMAGENET_MEAN, std=IMAGENET_STD) -> int:
+    """One (T, 3, dst_h, dst_w) float32 clip from T decoded frames with the SAME crop window
+    (x, y, w, h in source pixels) and flip for every frame (turboloader_bindings.cpp:1711-1734)."""
+    n = len(y_ptrs)
+    if not (len(cb_ptrs) == len(cr_ptrs) == n):
+        raise ValueError("y_ptrs, cb_ptrs and cr_ptrs must have the same length")
+    c4 = (C.c_float * 4)(*[float(v) for v in crop])
+    out = _capi.load().tlb_video_clip_yuv420(_addr_array(y_ptrs), _addr_array(cb_ptrs), _addr_array(cr_ptrs), n,
+                                             int(y_stride), int(c_stride), int(c_px_stride), int(src_w), int(src_h),
+                                             int(dst_h), int(dst_w), c4, int(bool(flip)), int(bool(bt709)),
+                                             _capi.f3(mean), _capi.f3(std))
+    if not out:
+        raise RuntimeError("cuda_video_clip_yuv420 failed: " + _capi.load().tlb_last_error().decode(errors="replace"))
+    return int(out)
+
+
+def video_yuv420(y_ptrs, cb_ptrs, cr_ptrs, *, y_stride, c_stride, c_px_stride, src_w, src_h, out, crops=None,
+                 flips=None, clip_len=0, bt709=False, mean=IMAGENET_MEAN, std=IMAGENET_STD, stream=None):
+    """Asynchronous form (``tlb_video_yuv420``): ``out`` is a caller-allocated CUDA tensor
+    (n, 3, dst_h, dst_w), float32 or bfloat16; ``crops`` an (n_clips, 4) array of windows shared by
+    ``clip_len`` consecutive frames each (None: whole-frame resize)."""
+    import numpy as np
+    import torch
+
+    n = len(y_ptrs)
+    d = _capi.VideoDesc()
+    keep = [_addr_array(y_ptrs), _addr_array(cb_ptrs), _addr_array(cr_ptrs)]
+    d.y_ptrs, d.cb_ptrs, d.cr_ptrs = [C.cast(a, C.c_void_p) for a in keep]
+    d.n = n
+    d.y_stride, d.c_stride, d.c_px_stride = int(y_stride), int(c_stride), int(c_px_stride)
+    d.src_w, d.src_h = int(src_w), int(src_h)
+    if out.dim() != 4 or out.shape[0] != n or out.shape[1] != 3 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous (n, 3, dst_h, dst_w) CUDA tensor")
+    d.dst_h, d.dst_w = int(out.shape[2]), int(out.shape[3])
+    if crops is not None:
+        cr = np.ascontiguousarray(crops, dtype=np.float32).reshape(-1, 4)
+        fl = np.zeros(len(cr), np.int32) if flips is None else np.ascontiguousarray(flips, dtype=np.int32)
+        keep += [cr, fl]
+        d.crops, d.flips = cr.ctypes.data, fl.ctypes.data
+    d.clip_len = int(clip_len)
+    d.bt709 = int(bool(bt709))
+    d.mean, d.std = _capi.f3(mean), _capi.f3(std)
+    d.out = out.data_ptr()
+    d.out_dtype = _capi.TLB_F32 if out.dtype == torch.float32 else _capi.TLB_BF16
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("out must be float32 or bfloat16")
+    st = stream if stream is not None else torch.cuda.current_stream(out.device)
+    with torch.cuda.device(out.device):
+        _capi.check(_capi.load().tlb_video_yuv420(C.byref(d), C.c_void_p(st.cuda_stream)))
+    return out
+
+
 def set_launch_overlap(enable: bool) -> bool:
     """Let consecutive launches of the fused kernel overlap head to tail (``tlb_set_launch_overlap``).
 
