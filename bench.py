@@ -386,10 +386,11 @@ def video_leg(torch, device, stream, peak, steps=30):
 
     plist = [ptrs(yb, uv) for yb, uv, _ in sets]
 
+    descs = [ops.make_video_desc(*plist[i], y_stride=W, c_stride=W, c_px_stride=2, src_w=W, src_h=H, out=sets[i][2],
+                                 crops=crops, flips=flips, clip_len=T) for i in range(2)]
+
     def step(i):
-        yp, cb, cr = plist[i % 2]
-        ops.video_yuv420(yp, cb, cr, y_stride=W, c_stride=W, c_px_stride=2, src_w=W, src_h=H, out=sets[i % 2][2],
-                         crops=crops, flips=flips, clip_len=T, stream=stream)
+        ops.enqueue_video(descs[i % 2], stream.cuda_stream)
 
     for i in range(3):
         step(i)

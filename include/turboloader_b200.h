@@ -224,6 +224,7 @@ typedef struct tlb_video_desc {
     float std[3];             /* (rgb01 - mean) * (1.0f / std) */
     void* out;                /* DEVICE, caller-allocated (n,3,dst_h,dst_w) */
     int32_t out_dtype;        /* TLB_F32 / TLB_BF16 */
+    uint32_t* status;         /* DEVICE word OR-ed with TLB_DEV_COPY_TIMEOUT if a bounded wait gave up; or NULL */
 } tlb_video_desc;
 
 /* Asynchronous form on the caller's stream: uploads the small address/crop tables through a
@@ -243,6 +244,33 @@ TLB_API uintptr_t tlb_video_clip_yuv420(const uintptr_t* y_ptrs, const uintptr_t
                                         int32_t src_h, int32_t dst_h, int32_t dst_w,
                                         const float crop[4], int32_t flip, int32_t bt709,
                                         const float mean[3], const float std_[3]);
+
+/* ---- streaming core: datasets larger than device memory -------------------------------------
+ * Replaces CudaStreamCore (src/cuda/cuda_transforms.cu:629-780; Python turboloader/cuda_loader.py:
+ * 538-674): n uint8 HWC images of one size stay in host memory (pinned, for the copies to overlap)
+ * and are streamed in index order, `slots`-1 batches ahead: per batch one asynchronous copy and one
+ * fused kernel on the slot's own stream.  No worker threads and no host synchronisation when a
+ * consumer stream is given.  crop_box (x,y,w,h; NULL or w<=0: whole image) and out_h/out_w (0: the
+ * crop size) select a centre-crop / resize fused into the same kernel. */
+typedef struct tlb_stream_core tlb_stream_core;
+TLB_API tlb_stream_core* tlb_stream_create(const uint8_t* host_images, int64_t n, int32_t h, int32_t w,
+                                           int32_t batch, const float mean[3], const float std_[3],
+                                           int32_t slots, int32_t drop_last, const int32_t crop_box[4],
+                                           int32_t out_h, int32_t out_w, int32_t out_dtype,
+                                           int32_t out_layout);   /* NULL on error */
+TLB_API void tlb_stream_destroy(tlb_stream_core* core);
+TLB_API int64_t tlb_stream_num_batches(const tlb_stream_core* core);
+/* Starts an epoch: enqueues the first slots-1 batches.  consumer_stream (may be NULL): the stream
+ * on which batches of the previous epoch were used; the slots are reused behind its position. */
+TLB_API int tlb_stream_begin_epoch(tlb_stream_core* core, void* consumer_stream);
+/* Next batch in index order: *out_dev = device address of (n,3,out_h,out_w) [or NHWC], *out_n = n;
+ * *out_n = 0 at the end of the epoch.  With consumer_stream != NULL nothing blocks: that stream is
+ * made to wait for the batch, and slots are refilled only behind the work already enqueued on it.
+ * With NULL the call waits on the host until the batch is complete (the reference's behaviour).
+ * The batch stays valid until the second next call. */
+TLB_API int tlb_stream_next(tlb_stream_core* core, uintptr_t* out_dev, int32_t* out_n, void* consumer_stream);
+/* Drains the slots and returns the OR of the device status bits seen so far. */
+TLB_API int tlb_stream_status(tlb_stream_core* core, uint32_t* out_status);
 
 /* ---- back-to-back launches ----------------------------------------------------------------
  * No counterpart in the reference (its loaders synchronise after every batch).

@@ -68,6 +68,17 @@ class Frames:
         return (self.y_ptrs, self.cb_ptrs, self.cr_ptrs, self.y_stride, self.c_stride, self.c_px, self.w, self.h)
 
 
+@pytest.fixture(params=["direct", "staged"], autouse=True)
+def kernel_choice(request, monkeypatch):
+    """Every test runs against both kernels: the direct-load one (default) and the shared-memory
+    staged one (TLB_VIDEO_STAGED=1)."""
+    if request.param == "staged":
+        monkeypatch.setenv("TLB_VIDEO_STAGED", "1")
+    else:
+        monkeypatch.delenv("TLB_VIDEO_STAGED", raising=False)
+    return request.param
+
+
 def _bits(a):
     return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
 
@@ -89,6 +100,20 @@ def test_clips_share_their_crop_and_flip():
     for i in range(8):
         want = f.oracle(i, 40, 56, crop=tuple(crops[i // 4]), flip=bool(flips[i // 4]))
         assert np.array_equal(_bits(got[i]), _bits(want)), f"frame {i}"
+
+
+def test_upscale_and_windows_touching_the_frame_edges():
+    """Right/bottom edge taps (x1 == x0, y1 == y0), windows partly outside the frame (coordinates
+    clamp), odd frame sizes, an output wider than one block of threads."""
+    f = Frames(3, 37, 53, nv12=True, pad=1, smooth=False, seed=60)
+    got = f.run(80, 300).cpu().numpy()
+    for i in range(3):
+        assert np.array_equal(_bits(got[i]), _bits(f.oracle(i, 80, 300)))
+    crops = np.array([[30.0, 20.0, 40.0, 30.0]], np.float32)  # reaches past the right and bottom edges
+    for flip in (0, 1):
+        got = f.run(33, 47, crops=crops, flips=np.array([flip], np.int32)).cpu().numpy()
+        for i in range(3):
+            assert np.array_equal(_bits(got[i]), _bits(f.oracle(i, 33, 47, crop=tuple(crops[0]), flip=bool(flip))))
 
 
 def test_bf16_output_is_the_rounded_fp32_result():

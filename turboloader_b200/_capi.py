@@ -73,6 +73,7 @@ class VideoDesc(C.Structure):
         ("std", C.c_float * 3),
         ("out", C.c_void_p),
         ("out_dtype", C.c_int32),
+        ("status", C.c_void_p),
     ]
 
 
@@ -140,6 +141,19 @@ def load() -> C.CDLL:
     lib.tlb_video_yuv420_batch.argtypes = [up, up, up] + [C.c_int32] * 9 + [_F3, _F3]
     lib.tlb_video_clip_yuv420.restype = C.c_size_t
     lib.tlb_video_clip_yuv420.argtypes = [up, up, up] + [C.c_int32] * 8 + [C.c_float * 4, C.c_int32, C.c_int32, _F3, _F3]
+    lib.tlb_stream_create.restype = C.c_void_p
+    lib.tlb_stream_create.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, _F3, _F3, C.c_int32,
+                                      C.c_int32, C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_int32, C.c_int32]
+    lib.tlb_stream_destroy.restype = None
+    lib.tlb_stream_destroy.argtypes = [C.c_void_p]
+    lib.tlb_stream_num_batches.restype = C.c_int64
+    lib.tlb_stream_num_batches.argtypes = [C.c_void_p]
+    lib.tlb_stream_begin_epoch.restype = C.c_int
+    lib.tlb_stream_begin_epoch.argtypes = [C.c_void_p, C.c_void_p]
+    lib.tlb_stream_next.restype = C.c_int
+    lib.tlb_stream_next.argtypes = [C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_int32), C.c_void_p]
+    lib.tlb_stream_status.restype = C.c_int
+    lib.tlb_stream_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
     lib.tlb_fused_plan.restype = C.c_int
     lib.tlb_fused_plan.argtypes = [C.POINTER(TransformDesc)] + [C.POINTER(C.c_int32)] * 5
     lib.tlb_launch_count.restype = C.c_uint64

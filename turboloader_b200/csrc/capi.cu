@@ -99,6 +99,7 @@ int ensure_prepared(DeviceState& st) {
     std::lock_guard<std::mutex> lk(st.prep_mu);
     if (st.prepared.load(std::memory_order_acquire)) return TLB_OK;
     cudaError_t e = static_cast<cudaError_t>(tlb::prepare_device());
+    if (e == cudaSuccess) e = static_cast<cudaError_t>(tlb::prepare_video());
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
     st.prepared.store(true, std::memory_order_release);
     return TLB_OK;
@@ -972,6 +973,7 @@ int video_enqueue(const tlb_video_desc& d, void* stream) {
     int dev;
     if (int rc = current_device(&dev)) return rc;
     DeviceState& st = g_dev[dev];
+    if (int rc = ensure_prepared(st)) return rc;
     const size_t n = static_cast<size_t>(d.n);
     const size_t clips = d.crops ? (d.clip_len > 0 ? (n + d.clip_len - 1) / d.clip_len : 1) : 0;
     const size_t off_crop = (3 * n * sizeof(void*) + 15) & ~static_cast<size_t>(15);
@@ -1010,7 +1012,10 @@ int video_enqueue(const tlb_video_desc& d, void* stream) {
         p.mean[c] = d.mean[c];
         p.inv_std[c] = 1.0f / d.std[c];  // cuda_transforms.cu:392 computes the reciprocal on the host, in fp32
     }
+    p.one = 1.0f;
     p.out = d.out;
+    p.status = d.status;
+    p.use_staged = env_int("TLB_VIDEO_STAGED", 0);
     cudaError_t e = static_cast<cudaError_t>(tlb::launch_video(p, d.out_dtype, stream));
     TLB_CUDA(cudaEventRecord(buf.done, cs));
     buf.pending = true;
@@ -1105,6 +1110,199 @@ uintptr_t tlb_video_clip_yuv420(const uintptr_t* y_ptrs, const uintptr_t* cb_ptr
     d.clip_len = 0;
     for (int c = 0; c < 3; ++c) { d.mean[c] = mean[c]; d.std[c] = std_[c]; }
     return video_pointer_form(d);
+}
+
+}  // extern "C"
+
+// ---- streaming core: datasets larger than device memory ------------------------------------
+// Replaces CudaStreamCore (src/cuda/cuda_transforms.cu:629-780): the uint8 dataset stays in
+// (pinned) host memory and is streamed batch by batch.  The reference drives K slots with K worker
+// threads that block on their own streams; here nothing blocks and there are no threads: a slot is
+// a device staging buffer + output buffer + stream, one contiguous asynchronous copy and one fused
+// kernel are enqueued per batch, K-1 batches ahead of the consumer, and a batch is handed over
+// either by an event the consumer's stream waits on (no host synchronisation at all) or, without
+// a consumer stream, by waiting for that event on the host as the reference does.
+struct tlb_stream_core {
+    int dev = 0;
+    const uint8_t* host = nullptr;
+    int64_t n = 0;
+    int h = 0, w = 0, batch = 0, slots = 0;
+    int out_h = 0, out_w = 0;
+    int crop[4] = {0, 0, 0, 0};
+    bool drop_last = true;
+    int out_dtype = TLB_F32, out_layout = TLB_NCHW;
+    float mean[3] = {0, 0, 0}, std_[3] = {1, 1, 1};
+    int64_t n_batches = 0;
+    int64_t enqueued = 0;  // batches enqueued this epoch
+    int64_t returned = 0;  // batches handed to the consumer this epoch
+    std::vector<void*> d_in, d_out;
+    std::vector<cudaStream_t> streams;
+    std::vector<cudaEvent_t> ready;   // slot's kernel finished
+    cudaEvent_t consumed = nullptr;   // consumer stream's position at the latest next() call
+    uint32_t* status = nullptr;       // device word
+};
+
+namespace {
+
+int stream_enqueue(tlb_stream_core* c, void* consumer_stream) {
+    const int64_t b = c->enqueued;
+    const int slot = static_cast<int>(b % c->slots);
+    const int64_t first = b * c->batch;
+    const int nb = static_cast<int>(std::min<int64_t>(c->batch, c->n - first));
+    cudaStream_t st = c->streams[slot];
+    // The slot's previous output may still be in use by work the consumer enqueued before this
+    // call: order this slot's stream behind the consumer stream's current position.
+    if (consumer_stream) {
+        TLB_CUDA(cudaEventRecord(c->consumed, static_cast<cudaStream_t>(consumer_stream)));
+        TLB_CUDA(cudaStreamWaitEvent(st, c->consumed, 0));
+    }
+    const size_t img = static_cast<size_t>(c->h) * c->w * 3;
+    TLB_CUDA(cudaMemcpyAsync(c->d_in[slot], c->host + first * img, nb * img, cudaMemcpyHostToDevice, st));
+    tlb_transform_desc d{};
+    d.src = static_cast<const uint8_t*>(c->d_in[slot]);
+    d.src_bytes = nb * img;
+    d.n_src = nb;
+    d.src_w = c->w;
+    d.src_h = c->h;
+    d.n = nb;
+    for (int i = 0; i < 4; ++i) d.uniform_box[i] = c->crop[i];
+    d.dst_h = c->out_h;
+    d.dst_w = c->out_w;
+    d.out = c->d_out[slot];
+    d.out_dtype = c->out_dtype;
+    d.out_layout = c->out_layout;
+    for (int i = 0; i < 3; ++i) {
+        d.mean[i] = c->mean[i];
+        d.std[i] = c->std_[i];
+    }
+    d.normalize_01 = 1;
+    d.status = c->status;
+    if (int rc = tlb_fused_transform(&d, st)) return rc;
+    TLB_CUDA(cudaEventRecord(c->ready[slot], st));
+    c->enqueued = b + 1;
+    return TLB_OK;
+}
+
+void stream_free(tlb_stream_core* c) {
+    if (!c) return;
+    for (void* p : c->d_in) if (p) cudaFree(p);
+    for (void* p : c->d_out) if (p) cudaFree(p);
+    for (cudaEvent_t e : c->ready) if (e) cudaEventDestroy(e);
+    for (cudaStream_t s : c->streams) if (s) cudaStreamDestroy(s);
+    if (c->consumed) cudaEventDestroy(c->consumed);
+    if (c->status) cudaFree(c->status);
+    delete c;
+}
+
+}  // namespace
+
+extern "C" {
+
+tlb_stream_core* tlb_stream_create(const uint8_t* host_images, int64_t n, int32_t h, int32_t w, int32_t batch,
+                                   const float mean[3], const float std_[3], int32_t slots, int32_t drop_last,
+                                   const int32_t crop_box[4], int32_t out_h, int32_t out_w, int32_t out_dtype,
+                                   int32_t out_layout) {
+    if (!host_images || n <= 0 || h <= 0 || w <= 0 || batch <= 0 || !mean || !std_) {
+        fail(TLB_ERR_INVALID_ARG, "stream: NULL pointer or non-positive size");
+        return nullptr;
+    }
+    if ((out_dtype != TLB_F32 && out_dtype != TLB_BF16) || (out_layout != TLB_NCHW && out_layout != TLB_NHWC)) {
+        fail(TLB_ERR_INVALID_ARG, "stream: unknown output dtype or layout");
+        return nullptr;
+    }
+    int dev;
+    if (current_device(&dev)) return nullptr;
+    auto* c = new tlb_stream_core;
+    c->dev = dev;
+    c->host = host_images;
+    c->n = n; c->h = h; c->w = w; c->batch = batch;
+    c->slots = std::clamp(static_cast<int>(slots), 2, 16);
+    c->drop_last = drop_last != 0;
+    c->out_dtype = out_dtype; c->out_layout = out_layout;
+    if (crop_box && crop_box[2] > 0) {
+        for (int i = 0; i < 4; ++i) c->crop[i] = crop_box[i];
+        if (crop_box[0] < 0 || crop_box[1] < 0 || crop_box[3] <= 0 || crop_box[0] > w - crop_box[2] ||
+            crop_box[1] > h - crop_box[3]) {
+            fail(TLB_ERR_BAD_BOX, "stream: crop box leaves the %dx%d images", w, h);
+            delete c;
+            return nullptr;
+        }
+    }
+    const int cw = c->crop[2] > 0 ? c->crop[2] : w, chh = c->crop[2] > 0 ? c->crop[3] : h;
+    c->out_h = out_h > 0 ? out_h : chh;
+    c->out_w = out_w > 0 ? out_w : cw;
+    for (int i = 0; i < 3; ++i) { c->mean[i] = mean[i]; c->std_[i] = std_[i]; }
+    c->n_batches = c->drop_last ? n / batch : (n + batch - 1) / batch;
+    const size_t in_bytes = static_cast<size_t>(batch) * h * w * 3;
+    const size_t out_bytes = static_cast<size_t>(batch) * 3 * c->out_h * c->out_w * (out_dtype == TLB_F32 ? 4 : 2);
+    c->d_in.assign(c->slots, nullptr);
+    c->d_out.assign(c->slots, nullptr);
+    c->streams.assign(c->slots, nullptr);
+    c->ready.assign(c->slots, nullptr);
+    bool ok = cudaMalloc(reinterpret_cast<void**>(&c->status), 4) == cudaSuccess && cudaMemset(c->status, 0, 4) == cudaSuccess &&
+              cudaEventCreateWithFlags(&c->consumed, cudaEventDisableTiming) == cudaSuccess;
+    for (int s = 0; ok && s < c->slots; ++s) {
+        ok = cudaMalloc(&c->d_in[s], in_bytes) == cudaSuccess && cudaMalloc(&c->d_out[s], out_bytes) == cudaSuccess &&
+             cudaStreamCreateWithFlags(&c->streams[s], cudaStreamNonBlocking) == cudaSuccess &&
+             cudaEventCreateWithFlags(&c->ready[s], cudaEventDisableTiming) == cudaSuccess;
+    }
+    if (!ok) {
+        cuda_fail(cudaGetLastError(), "stream: allocating the slots");
+        stream_free(c);
+        return nullptr;
+    }
+    return c;
+}
+
+void tlb_stream_destroy(tlb_stream_core* core) {
+    if (!core) return;
+    cudaSetDevice(core->dev);
+    for (cudaStream_t s : core->streams) if (s) cudaStreamSynchronize(s);
+    stream_free(core);
+}
+
+int64_t tlb_stream_num_batches(const tlb_stream_core* core) { return core ? core->n_batches : -1; }
+
+int tlb_stream_begin_epoch(tlb_stream_core* core, void* consumer_stream) {
+    if (!core) return fail(TLB_ERR_INVALID_ARG, "stream: core is NULL");
+    TLB_CUDA(cudaSetDevice(core->dev));
+    // Batches of an abandoned epoch may still be in flight; their slots are reused in stream order.
+    core->enqueued = 0;
+    core->returned = 0;
+    const int64_t ahead = std::min<int64_t>(core->slots - 1, core->n_batches);
+    for (int64_t i = 0; i < ahead; ++i)
+        if (int rc = stream_enqueue(core, consumer_stream)) return rc;
+    return TLB_OK;
+}
+
+int tlb_stream_next(tlb_stream_core* core, uintptr_t* out_dev, int32_t* out_n, void* consumer_stream) {
+    if (!core || !out_dev || !out_n) return fail(TLB_ERR_INVALID_ARG, "stream: NULL argument");
+    *out_dev = 0;
+    *out_n = 0;
+    if (core->returned >= core->n_batches) return TLB_OK;  // end of epoch
+    TLB_CUDA(cudaSetDevice(core->dev));
+    // Keep slots-1 batches enqueued beyond the ones already handed out.  The slot refilled here is
+    // the one handed out two calls ago: a batch stays valid until the second next call.
+    if (core->enqueued < core->n_batches && core->enqueued - core->returned < core->slots - 1)
+        if (int rc = stream_enqueue(core, consumer_stream)) return rc;
+    const int64_t b = core->returned;
+    const int slot = static_cast<int>(b % core->slots);
+    if (consumer_stream)
+        TLB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(consumer_stream), core->ready[slot], 0));
+    else
+        TLB_CUDA(cudaEventSynchronize(core->ready[slot]));
+    *out_dev = reinterpret_cast<uintptr_t>(core->d_out[slot]);
+    *out_n = static_cast<int32_t>(std::min<int64_t>(core->batch, core->n - b * core->batch));
+    core->returned = b + 1;
+    return TLB_OK;
+}
+
+int tlb_stream_status(tlb_stream_core* core, uint32_t* out_status) {
+    if (!core || !out_status) return fail(TLB_ERR_INVALID_ARG, "stream: NULL argument");
+    TLB_CUDA(cudaSetDevice(core->dev));
+    for (cudaStream_t s : core->streams) TLB_CUDA(cudaStreamSynchronize(s));
+    TLB_CUDA(cudaMemcpy(out_status, core->status, 4, cudaMemcpyDeviceToHost));
+    return TLB_OK;
 }
 
 }  // extern "C"

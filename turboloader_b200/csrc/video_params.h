@@ -15,10 +15,17 @@ struct VideoParams {
     int y_stride, c_stride, c_px_stride; // bytes; c_px_stride 1 = I420 planes, 2 = NV12 interleaved
     int src_w, src_h, dst_w, dst_h, bt709;
     float mean[3], inv_std[3];
+    float one;                           // 1.0f, passed at run time (see add_prod in video_yuv420.cu)
     void* out;                           // (n, 3, dst_h, dst_w)
+    unsigned* status;                    // optional device word, OR-ed with 8 if a staging copy never completed
+    int stage_rows;                      // set by launch_video: output rows per CTA of the staged kernel
+    int use_staged;                      // non-zero: use the shared-memory staged kernel when the frame fits
 };
 
-int launch_video(const VideoParams& p, int out_dtype, void* stream);  // returns a cudaError_t value
+constexpr int kVideoStageMaxBytes = 200 * 1024;  // most dynamic shared memory the staged kernel may ask for
+
+int prepare_video();                                           // once per device: shared-memory opt-in
+int launch_video(VideoParams p, int out_dtype, void* stream);  // returns a cudaError_t value
 unsigned long long video_launch_count();
 
 }  // namespace tlb

@@ -7,14 +7,24 @@
 //   turboloader::cuda::video_clip_yuv420    src/cuda/cuda_transforms.cu:207-268, 416-473
 //
 // Arithmetic: the kernels replaced are the only statement of this math; it is followed operation
-// by operation with every multiply, add and divide rounded to fp32 separately (this library is
-// built without FMA contraction), which is what the CPU oracle restates.  Bytes become floats
-// without an integer conversion: fma(2^23 + b, w, -2^23 * w) is exactly RN(b * w).
+// by operation with every multiply, add and divide rounded to fp32 separately, which is what the
+// CPU oracle restates.  Two output rows ride in the two lanes of the packed fp32 instructions;
+// bytes become floats without an integer conversion (fma(2^23 + b, w, -2^23 * w) == RN(b * w));
+// the division by 255 is a three-operation sequence that equals the IEEE quotient.
 //
-// Work split: a CTA owns kVideoRows output rows of one frame; a thread owns one output column
-// (columns beyond the block width wrap) and walks down the rows, so the horizontal taps and
-// weights (luma and chroma) are worked out once per thread and the vertical ones once per CTA
-// (a small table in shared memory).  A warp's stores are 32 consecutive outputs of one row.
+// Two kernels share that arithmetic:
+//  * yuv420_direct_kernel (the default): per-thread byte loads of the taps straight from global
+//    memory through L1, with the next row pair's lines prefetched.  A bilinear downscale taps only
+//    part of the source, and this kernel reads only the sectors it taps.
+//  * yuv420_staged_kernel (opt-in): a CTA owns a few output rows of one frame; one warp issues a
+//    bulk asynchronous copy (cp.async.bulk, completion on an mbarrier) for every source row
+//    segment the CTA needs -- two luma and two chroma rows per output row, clipped to the columns
+//    the CTA's outputs tap -- and everybody then reads taps from shared memory.  Measured on the
+//    benchmark's clip workload it is the slower of the two (one copy-then-compute phase per CTA,
+//    no overlap inside the CTA), so it is not the default; it moves whole row segments, which
+//    pays when nearly every source byte is tapped (resize factors near 1).
+// A thread owns one output column and walks down the CTA's rows, so the horizontal taps and
+// weights are worked out once per thread and the vertical ones once per CTA.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -27,17 +37,54 @@
 namespace tlb {
 namespace {
 
-constexpr int kVideoRows = 8;  // output rows per CTA
+constexpr int kDirectRows = 8;     // output rows per CTA of the direct kernel (processed as pairs)
+constexpr int kStageMaxRows = 16;  // most output rows per CTA of the staged kernel
+constexpr unsigned kVideoCopyTimeout = 8u;  // status bit: a bounded wait on the staging copies gave up
 
-struct RowTaps {
-    int y0, y1;    // byte offsets of the two luma rows
-    int c0, c1;    // byte offsets of the two chroma rows
-    float dy, cdy;
-    float idy, icdy;  // 1 - dy, 1 - cdy
-};
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 
-__device__ __forceinline__ float byte_times(unsigned b, float w, float nw) {
-    return __fmaf_rn(__uint_as_float(b | 0x4B000000u), w, nw);  // == RN(b * w); nw = -2^23 * w
+// Packed two-lane fp32 operations of sm_100; each lane rounds like the scalar instruction.
+#define TLB_V2(name, op)                                                                              \
+    __device__ __forceinline__ float2 name(float2 a, float2 b) {                                      \
+        float2 d;                                                                                     \
+        asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t" op      \
+            " rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"                                              \
+            : "=f"(d.x), "=f"(d.y)                                                                    \
+            : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));                                                \
+        return d;                                                                                     \
+    }
+TLB_V2(mul2, "mul.rn.f32x2")
+TLB_V2(add2, "add.rn.f32x2")
+#undef TLB_V2
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+// (RN(b0 * w.x), RN(b1 * w.y)) for two bytes without an integer conversion: OR-ing a byte into
+// the mantissa of 2^23 gives the float 2^23 + b; with nw = -2^23 * w (exact),
+// fma(2^23 + b, w, nw) evaluates b * w exactly and rounds once.
+__device__ __forceinline__ float2 bytes_times(unsigned b0, unsigned b1, float2 w, float2 nw) {
+    return fma2(f2(__uint_as_float(b0 | 0x4B000000u), __uint_as_float(b1 | 0x4B000000u)), w, nw);
+}
+// a + b where a is a product: issued as fma(a, one, b).  The assembler fuses a packed multiply
+// that feeds a packed add into one FMA (observed even with contraction disabled), which would
+// drop the product's own rounding; an FMA whose multiplicand is the finished product and whose
+// multiplier is a 1.0f it cannot see through (a kernel parameter) cannot be fused any further.
+// sign_one = +1 adds the product, -1 subtracts it (a * -1 is exact).
+__device__ __forceinline__ float2 add_prod(float2 prod, float2 sign_one, float2 b) { return fma2(prod, sign_one, b); }
+
+// x / 255 correctly rounded in three operations (q = x * r; e = x - q * 255 exactly, by FMA;
+// q + e * r): equal to the IEEE quotient for every float with 2^-40 <= |x| <= 2^12 and for zero
+// (checked exhaustively on the CPU against the division); channel values lie within +-1000.
+__device__ __forceinline__ float2 div255(float2 x) {
+    const float r = 1.0f / 255.0f;
+    const float2 q = mul2(x, f2(r, r));
+    const float2 e = fma2(q, f2(-255.0f, -255.0f), x);
+    return fma2(e, f2(r, r), q);
 }
 
 template <int DTYPE>
@@ -48,12 +95,126 @@ __device__ __forceinline__ void put(void* out, long long idx, float v) {
         static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
 }
 
+// The 24 taps of a pair of output rows (index [h]: row r + h): luma upper/lower row (a, b),
+// Cb and Cr upper/lower row (ua, ub, va, vb), left/right tap (0, 1).
+struct Taps {
+    unsigned a0[2], a1[2], b0[2], b1[2], ua0[2], ua1[2], ub0[2], ub1[2], va0[2], va1[2], vb0[2], vb1[2];
+};
+// Vertical weights of the pair, (row r, row r+1) in the two lanes.
+struct PairWeights {
+    float2 dy, idy, cdy, icdy;
+};
+// Per-column weights (both lanes equal) and launch constants, packed.
+struct ColWeights {
+    float2 wx, iwx, nwx, niwx, wc, iwc, nwc, niwc;
+};
+struct Consts {
+    float2 kY, kRV, kGU, kGV, kBU, one, mone, m16, m128, nm0, nm1, nm2, is0, is1, is2;
+};
+
+__device__ __forceinline__ Consts make_consts(const VideoParams& p) {
+    Consts c;
+    const float ky = 255.0f / 219.0f;
+    const float rv = p.bt709 ? 1.792741f : 1.596027f, gu = p.bt709 ? 0.213249f : 0.391762f;
+    const float gv = p.bt709 ? 0.532909f : 0.812968f, bu = p.bt709 ? 2.112402f : 2.017232f;
+    c.kY = f2(ky, ky); c.kRV = f2(rv, rv); c.kGU = f2(gu, gu); c.kGV = f2(gv, gv); c.kBU = f2(bu, bu);
+    c.one = f2(p.one, p.one); c.mone = f2(-p.one, -p.one);
+    c.m16 = f2(-16.0f, -16.0f); c.m128 = f2(-128.0f, -128.0f);
+    c.nm0 = f2(-p.mean[0], -p.mean[0]); c.nm1 = f2(-p.mean[1], -p.mean[1]); c.nm2 = f2(-p.mean[2], -p.mean[2]);
+    c.is0 = f2(p.inv_std[0], p.inv_std[0]); c.is1 = f2(p.inv_std[1], p.inv_std[1]); c.is2 = f2(p.inv_std[2], p.inv_std[2]);
+    return c;
+}
+
+__device__ __forceinline__ ColWeights make_col(float dx, float cdx) {
+    ColWeights w;
+    const float idx = 1.0f - dx, icdx = 1.0f - cdx;
+    w.wx = f2(dx, dx); w.iwx = f2(idx, idx);
+    w.nwx = f2(-8388608.0f * dx, -8388608.0f * dx); w.niwx = f2(-8388608.0f * idx, -8388608.0f * idx);
+    w.wc = f2(cdx, cdx); w.iwc = f2(icdx, icdx);
+    w.nwc = f2(-8388608.0f * cdx, -8388608.0f * cdx); w.niwc = f2(-8388608.0f * icdx, -8388608.0f * icdx);
+    return w;
+}
+
+// Output-row coordinates (cuda_transforms.cu:150-152 whole frame; :219-223 crop window).
+__device__ __forceinline__ float src_y(const VideoParams& p, bool use_crop, float4 crop, int y) {
+    if (use_crop) {
+        const float sy = crop.y + __fdiv_rn(static_cast<float>(y) + 0.5f, static_cast<float>(p.dst_h)) * crop.w - 0.5f;
+        return fminf(fmaxf(sy, 0.0f), static_cast<float>(p.src_h - 1));
+    }
+    return fmaxf(0.0f, __fdiv_rn((static_cast<float>(y) + 0.5f) * static_cast<float>(p.src_h),
+                                 static_cast<float>(p.dst_h)) - 0.5f);
+}
+__device__ __forceinline__ float src_x(const VideoParams& p, bool use_crop, float4 crop, bool flip, int x) {
+    if (use_crop) {
+        const int ox = flip ? (p.dst_w - 1 - x) : x;
+        const float sx = crop.x + __fdiv_rn(static_cast<float>(ox) + 0.5f, static_cast<float>(p.dst_w)) * crop.z - 0.5f;
+        return fminf(fmaxf(sx, 0.0f), static_cast<float>(p.src_w - 1));
+    }
+    return fmaxf(0.0f, __fdiv_rn((static_cast<float>(x) + 0.5f) * static_cast<float>(p.src_w),
+                                 static_cast<float>(p.dst_w)) - 0.5f);
+}
+
+// Blend, colour conversion, clip and normalize of one row pair; stores up to two rows.
 template <int DTYPE>
-__global__ void __launch_bounds__(256) yuv420_kernel(const __grid_constant__ VideoParams p) {
-    __shared__ RowTaps taps[kVideoRows];
-    const int t = blockIdx.y;                    // frame
-    const int r0 = blockIdx.x * kVideoRows;      // first output row of this CTA
-    const int rows = min(kVideoRows, p.dst_h - r0);
+__device__ __forceinline__ void convert_store(const Taps& k, const PairWeights& pw, const ColWeights& w, const Consts& c,
+                                              void* out, long long o, long long plane, int W, bool second) {
+    const float2 ytop = add2(bytes_times(k.a0[0], k.a0[1], w.iwx, w.niwx), bytes_times(k.a1[0], k.a1[1], w.wx, w.nwx));
+    const float2 ybot = add2(bytes_times(k.b0[0], k.b0[1], w.iwx, w.niwx), bytes_times(k.b1[0], k.b1[1], w.wx, w.nwx));
+    const float2 yv0 = add_prod(mul2(ytop, pw.idy), c.one, mul2(ybot, pw.dy));
+    const float2 utop = add2(bytes_times(k.ua0[0], k.ua0[1], w.iwc, w.niwc), bytes_times(k.ua1[0], k.ua1[1], w.wc, w.nwc));
+    const float2 ubot = add2(bytes_times(k.ub0[0], k.ub0[1], w.iwc, w.niwc), bytes_times(k.ub1[0], k.ub1[1], w.wc, w.nwc));
+    const float2 cbv = add_prod(mul2(utop, pw.icdy), c.one, mul2(ubot, pw.cdy));
+    const float2 vtop = add2(bytes_times(k.va0[0], k.va0[1], w.iwc, w.niwc), bytes_times(k.va1[0], k.va1[1], w.wc, w.nwc));
+    const float2 vbot = add2(bytes_times(k.vb0[0], k.vb0[1], w.iwc, w.niwc), bytes_times(k.vb1[0], k.vb1[1], w.wc, w.nwc));
+    const float2 crv = add_prod(mul2(vtop, pw.icdy), c.one, mul2(vbot, pw.cdy));
+
+    const float2 yv = mul2(add2(yv0, c.m16), c.kY);
+    const float2 cb = add2(cbv, c.m128), cr = add2(crv, c.m128);
+    const float2 R = add_prod(mul2(c.kRV, cr), c.one, yv);                                        // yv + kRV*cr
+    const float2 G = add_prod(mul2(c.kGV, cr), c.mone, add_prod(mul2(c.kGU, cb), c.mone, yv));  // (yv - kGU*cb) - kGV*cr
+    const float2 B = add_prod(mul2(c.kBU, cb), c.one, yv);                                        // yv + kBU*cb
+    float2 r01 = div255(R), g01 = div255(G), b01 = div255(B);
+    r01 = f2(fminf(fmaxf(r01.x, 0.0f), 1.0f), fminf(fmaxf(r01.y, 0.0f), 1.0f));
+    g01 = f2(fminf(fmaxf(g01.x, 0.0f), 1.0f), fminf(fmaxf(g01.y, 0.0f), 1.0f));
+    b01 = f2(fminf(fmaxf(b01.x, 0.0f), 1.0f), fminf(fmaxf(b01.y, 0.0f), 1.0f));
+    const float2 ro = mul2(add2(r01, c.nm0), c.is0);
+    const float2 go = mul2(add2(g01, c.nm1), c.is1);
+    const float2 bo = mul2(add2(b01, c.nm2), c.is2);
+    put<DTYPE>(out, o, ro.x);
+    put<DTYPE>(out, o + plane, go.x);
+    put<DTYPE>(out, o + 2 * plane, bo.x);
+    if (second) {
+        put<DTYPE>(out, o + W, ro.y);
+        put<DTYPE>(out, o + plane + W, go.y);
+        put<DTYPE>(out, o + 2 * plane + W, bo.y);
+    }
+}
+
+// ================= direct kernel: taps loaded from global memory ==========================
+struct __align__(16) DirectPair {
+    int ya[2], yb[2];  // byte offsets of the upper / lower luma row, for row r and row r+1
+    int ca[2], cb[2];  // same for the chroma rows
+    PairWeights w;
+};
+
+// Two horizontally adjacent taps of a row.  The right tap is the left one again at the right
+// edge; its load is skipped there so that nothing beyond the row is touched.
+__device__ __forceinline__ void taps_global(const unsigned char* p, int step, bool edge, unsigned& t0, unsigned& t1) {
+    t0 = __ldg(p);
+    t1 = t0;
+    if (!edge) t1 = __ldg(p + step);
+}
+
+// Asks for the line of the next row pair's taps while the current pair is being converted: costs
+// no register and no wait, and turns most of the next iteration's misses into hits (+6 %).
+__device__ __forceinline__ void prefetch_line(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+
+template <int DTYPE>
+__global__ void __launch_bounds__(256) yuv420_direct_kernel(const __grid_constant__ VideoParams p) {
+    __shared__ DirectPair pairs[kDirectRows / 2];
+    const int t = blockIdx.y;                     // frame
+    const int r0 = blockIdx.x * kDirectRows;      // first output row of this CTA
+    const int rows = min(kDirectRows, p.dst_h - r0);
     const int W = p.dst_w, H = p.dst_h;
     const int cw = (p.src_w + 1) / 2, ch = (p.src_h + 1) / 2;
     const bool use_crop = p.crops != nullptr;
@@ -64,120 +225,351 @@ __global__ void __launch_bounds__(256) yuv420_kernel(const __grid_constant__ Vid
         crop = p.crops[clip];
         flip = p.flips ? p.flips[clip] != 0 : false;
     }
-
-    if (threadIdx.x < rows) {
-        const int y = r0 + threadIdx.x;
-        float sy;
-        if (use_crop) {
-            sy = crop.y + __fdiv_rn(static_cast<float>(y) + 0.5f, static_cast<float>(H)) * crop.w - 0.5f;
-            sy = fminf(fmaxf(sy, 0.0f), static_cast<float>(p.src_h - 1));
-        } else {
-            sy = fmaxf(0.0f, __fdiv_rn((static_cast<float>(y) + 0.5f) * static_cast<float>(p.src_h),
-                                       static_cast<float>(H)) - 0.5f);
-        }
+    if (threadIdx.x < kDirectRows) {
+        // Rows past the end of the frame repeat the last row (their results are never stored).
+        const int y = min(r0 + static_cast<int>(threadIdx.x), H - 1);
+        const float sy = src_y(p, use_crop, crop, y);
         const int y0 = static_cast<int>(sy);
         const int y1 = min(y0 + 1, p.src_h - 1);
         const float cyf = fminf(fmaxf(sy * 0.5f - 0.25f, 0.0f), static_cast<float>(ch - 1));
         const int cy0 = static_cast<int>(cyf);
         const int cy1 = min(cy0 + 1, ch - 1);
-        RowTaps rt;
-        rt.y0 = y0 * p.y_stride;
-        rt.y1 = y1 * p.y_stride;
-        rt.c0 = cy0 * p.c_stride;
-        rt.c1 = cy1 * p.c_stride;
-        rt.dy = sy - static_cast<float>(y0);
-        rt.cdy = cyf - static_cast<float>(cy0);
-        rt.idy = 1.0f - rt.dy;
-        rt.icdy = 1.0f - rt.cdy;
-        taps[threadIdx.x] = rt;
+        const float dy = sy - static_cast<float>(y0), cdy = cyf - static_cast<float>(cy0);
+        DirectPair& pt = pairs[threadIdx.x >> 1];
+        const int h = threadIdx.x & 1;
+        pt.ya[h] = y0 * p.y_stride;
+        pt.yb[h] = y1 * p.y_stride;
+        pt.ca[h] = cy0 * p.c_stride;
+        pt.cb[h] = cy1 * p.c_stride;
+        (&pt.w.dy.x)[h] = dy;
+        (&pt.w.idy.x)[h] = 1.0f - dy;
+        (&pt.w.cdy.x)[h] = cdy;
+        (&pt.w.icdy.x)[h] = 1.0f - cdy;
     }
     const unsigned char* __restrict__ yp = p.planes[t];
     const unsigned char* __restrict__ cbp = p.planes[p.n + t];
     const unsigned char* __restrict__ crp = p.planes[2 * p.n + t];
     __syncthreads();
 
-    const float kY = 255.0f / 219.0f;
-    const float kRV = p.bt709 ? 1.792741f : 1.596027f;
-    const float kGU = p.bt709 ? 0.213249f : 0.391762f;
-    const float kGV = p.bt709 ? 0.532909f : 0.812968f;
-    const float kBU = p.bt709 ? 2.112402f : 2.017232f;
-    const float nm0 = p.mean[0], nm1 = p.mean[1], nm2 = p.mean[2];
-    const float is0 = p.inv_std[0], is1 = p.inv_std[1], is2 = p.inv_std[2];
+    const Consts c = make_consts(p);
     const long long plane = static_cast<long long>(H) * W;
     const long long frame_base = static_cast<long long>(t) * 3 * plane;
-
+    const int cstep = p.c_px_stride;
     for (int x = threadIdx.x; x < W; x += blockDim.x) {
-        float sx;
-        if (use_crop) {
-            const int ox = flip ? (W - 1 - x) : x;
-            sx = crop.x + __fdiv_rn(static_cast<float>(ox) + 0.5f, static_cast<float>(W)) * crop.z - 0.5f;
-            sx = fminf(fmaxf(sx, 0.0f), static_cast<float>(p.src_w - 1));
-        } else {
-            sx = fmaxf(0.0f, __fdiv_rn((static_cast<float>(x) + 0.5f) * static_cast<float>(p.src_w),
-                                       static_cast<float>(W)) - 0.5f);
-        }
+        const float sx = src_x(p, use_crop, crop, flip, x);
         const int x0 = static_cast<int>(sx);
-        const int x1 = min(x0 + 1, p.src_w - 1);
-        const float dx = sx - static_cast<float>(x0);
-        const float idx_ = 1.0f - dx;
-        const float ndx = -8388608.0f * dx, nidx = -8388608.0f * idx_;
+        const bool yedge = x0 + 1 > p.src_w - 1;
         const float cxf = fminf(fmaxf(sx * 0.5f, 0.0f), static_cast<float>(cw - 1));
         const int cx0 = static_cast<int>(cxf);
-        const int cx1 = min(cx0 + 1, cw - 1);
-        const float cdx = cxf - static_cast<float>(cx0);
-        const float icdx = 1.0f - cdx;
-        const float ncdx = -8388608.0f * cdx, nicdx = -8388608.0f * icdx;
-        const int i0 = cx0 * p.c_px_stride, i1 = cx1 * p.c_px_stride;
+        const bool cedge = cx0 + 1 > cw - 1;
+        const ColWeights w = make_col(sx - static_cast<float>(x0), cxf - static_cast<float>(cx0));
+        const unsigned char* ycol = yp + x0;
+        const unsigned char* ucol = cbp + cx0 * cstep;
+        const unsigned char* vcol = crp + cx0 * cstep;
         long long o = frame_base + static_cast<long long>(r0) * W + x;
+        for (int r = 0; r < rows; r += 2, o += 2 * W) {
+            const DirectPair& q = pairs[r >> 1];
+            if (r + 2 < rows) {
+                const DirectPair& nx = pairs[(r >> 1) + 1];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    prefetch_line(ycol + nx.ya[h]);
+                    prefetch_line(ycol + nx.yb[h]);
+                    prefetch_line(ucol + nx.ca[h]);
+                    prefetch_line(ucol + nx.cb[h]);
+                    prefetch_line(vcol + nx.ca[h]);
+                    prefetch_line(vcol + nx.cb[h]);
+                }
+            }
+            Taps k;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                taps_global(ycol + q.ya[h], 1, yedge, k.a0[h], k.a1[h]);
+                taps_global(ycol + q.yb[h], 1, yedge, k.b0[h], k.b1[h]);
+                taps_global(ucol + q.ca[h], cstep, cedge, k.ua0[h], k.ua1[h]);
+                taps_global(ucol + q.cb[h], cstep, cedge, k.ub0[h], k.ub1[h]);
+                taps_global(vcol + q.ca[h], cstep, cedge, k.va0[h], k.va1[h]);
+                taps_global(vcol + q.cb[h], cstep, cedge, k.vb0[h], k.vb1[h]);
+            }
+            convert_store<DTYPE>(k, q.w, w, c, p.out, o, plane, W, r + 1 < rows);
+        }
+    }
+}
 
-#pragma unroll 2
-        for (int r = 0; r < rows; ++r, o += W) {
-            const RowTaps rt = taps[r];
-            const unsigned char* ya = yp + rt.y0;
-            const unsigned char* yb = yp + rt.y1;
-            const unsigned a0 = __ldg(ya + x0), a1 = __ldg(ya + x1), b0 = __ldg(yb + x0), b1 = __ldg(yb + x1);
-            const unsigned char* ua = cbp + rt.c0;
-            const unsigned char* ub = cbp + rt.c1;
-            const unsigned char* va = crp + rt.c0;
-            const unsigned char* vb = crp + rt.c1;
-            const unsigned u00 = __ldg(ua + i0), u01 = __ldg(ua + i1), u10 = __ldg(ub + i0), u11 = __ldg(ub + i1);
-            const unsigned v00 = __ldg(va + i0), v01 = __ldg(va + i1), v10 = __ldg(vb + i0), v11 = __ldg(vb + i1);
+// ================= staged kernel: source row segments copied to shared memory first =======
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(mbar), "r"(parity), "r"(1000000u)
+        : "memory");
+    return ok != 0;
+}
+// Bounded (about one second on the global timer): returns false if the copies never landed.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity) {
+    if (mbar_try_wait(mbar, parity)) return true;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (unsigned it = 0; it < (1u << 20); ++it) {
+        if (mbar_try_wait(mbar, parity)) return true;
+        if ((it & 15u) == 15u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (now - t0 > 1000000000ull) return false;
+        }
+    }
+    return false;
+}
 
-            const float ytop = byte_times(a0, idx_, nidx) + byte_times(a1, dx, ndx);
-            const float ybot = byte_times(b0, idx_, nidx) + byte_times(b1, dx, ndx);
-            const float yv0 = ytop * rt.idy + ybot * rt.dy;
-            const float cbv = (byte_times(u00, icdx, nicdx) + byte_times(u01, cdx, ncdx)) * rt.icdy +
-                              (byte_times(u10, icdx, nicdx) + byte_times(u11, cdx, ncdx)) * rt.cdy;
-            const float crv = (byte_times(v00, icdx, nicdx) + byte_times(v01, cdx, ncdx)) * rt.icdy +
-                              (byte_times(v10, icdx, nicdx) + byte_times(v11, cdx, ncdx)) * rt.cdy;
+// Shared-memory layout of the staged kernel: header (mbarrier, row table), then one slot per
+// staged row segment.  A slot keeps the segment at the same offset modulo 16 as in global
+// memory, so that the aligned middle of it can be moved by one bulk copy (16-byte granularity
+// on both sides) and only its ragged first and last bytes by plain loads.
+struct __align__(16) StageRow {
+    int ya, yb;          // shared-memory byte offsets of the first luma tap column in the upper / lower row
+    int ua, ub, va, vb;  // same for Cb and Cr
+    float dy, idy, cdy, icdy;
+    int pad[2];
+};
+constexpr int kStageHeader = 16 + kStageMaxRows * static_cast<int>(sizeof(StageRow));
 
-            const float yv = (yv0 - 16.0f) * kY;
-            const float cb = cbv - 128.0f, cr = crv - 128.0f;
-            const float R = yv + kRV * cr;
-            const float G = yv - kGU * cb - kGV * cr;
-            const float B = yv + kBU * cb;
-            const float r01 = fminf(fmaxf(__fdiv_rn(R, 255.0f), 0.0f), 1.0f);
-            const float g01 = fminf(fmaxf(__fdiv_rn(G, 255.0f), 0.0f), 1.0f);
-            const float b01 = fminf(fmaxf(__fdiv_rn(B, 255.0f), 0.0f), 1.0f);
-            put<DTYPE>(p.out, o, (r01 - nm0) * is0);
-            put<DTYPE>(p.out, o + plane, (g01 - nm1) * is1);
-            put<DTYPE>(p.out, o + 2 * plane, (b01 - nm2) * is2);
+template <int DTYPE>
+__global__ void __launch_bounds__(256, 5) yuv420_staged_kernel(const __grid_constant__ VideoParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    StageRow* const table = reinterpret_cast<StageRow*>(smem + 16);
+    const uint32_t mbar = smem_addr(smem);
+    const int R = p.stage_rows;                   // output rows per CTA (even)
+    const int t = blockIdx.y;                     // frame
+    const int r0 = blockIdx.x * R;                // first output row of this CTA
+    const int rows = min(R, p.dst_h - r0);
+    const int W = p.dst_w, H = p.dst_h;
+    const int cw = (p.src_w + 1) / 2, ch = (p.src_h + 1) / 2;
+    const int cstep = p.c_px_stride;
+    const bool use_crop = p.crops != nullptr;
+    float4 crop = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool flip = false;
+    if (use_crop) {
+        const int clip = p.clip_len > 0 ? t / p.clip_len : 0;
+        crop = p.crops[clip];
+        flip = p.flips ? p.flips[clip] != 0 : false;
+    }
+    // Columns the CTA's outputs tap: sx is monotonic in the (possibly mirrored) output column.
+    const float sx_a = src_x(p, use_crop, crop, flip, flip ? W - 1 : 0);
+    const float sx_b = src_x(p, use_crop, crop, flip, flip ? 0 : W - 1);
+    const int fx_lo = static_cast<int>(sx_a);
+    const int fx_hi = min(static_cast<int>(sx_b) + 1, p.src_w - 1);
+    const int cfx_lo = static_cast<int>(fminf(fmaxf(sx_a * 0.5f, 0.0f), static_cast<float>(cw - 1)));
+    const int cfx_hi = min(static_cast<int>(fminf(fmaxf(sx_b * 0.5f, 0.0f), static_cast<float>(cw - 1))) + 1, cw - 1);
+    const int ylen = fx_hi - fx_lo + 1;                       // bytes of a luma segment
+    const int clen = (cfx_hi - cfx_lo) * cstep + 1;           // bytes of a chroma segment of ONE plane
+    const unsigned char* const yp = p.planes[t];
+    const unsigned char* const cbp = p.planes[p.n + t];
+    const unsigned char* const crp = p.planes[2 * p.n + t];
+    // NV12 / NV21: both chroma planes live interleaved in one buffer; stage it once.
+    const bool shared_uv = cstep == 2 && (crp == cbp + 1 || cbp == crp + 1);
+    const unsigned char* const uvp = crp < cbp ? crp : cbp;   // lower of the two addresses (shared_uv only)
+    const int uvlen = clen + 1;
+    const int ypitch = (ylen + 15 + 15) & ~15;
+    const int cpitch = ((shared_uv ? uvlen : clen) + 15 + 15) & ~15;
+    const int cslots = shared_uv ? 2 : 4;                     // chroma slots per output row
+    const int row_bytes = 2 * ypitch + cslots * cpitch;
+    unsigned char* const slots = smem + kStageHeader;
+
+    if (threadIdx.x < 32) {
+        if (threadIdx.x == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(1u) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+        // ---- one lane per staged segment: row table entry + copy ------------------------------
+        const int nseg = rows * (2 + cslots);
+        unsigned total = 0;
+        for (int sgi = threadIdx.x; sgi < ((nseg + 31) & ~31); sgi += 32) {
+            unsigned bytes = 0;
+            unsigned long long lo = 0;
+            uint32_t dst = 0;
+            if (sgi < nseg) {
+                const int j = sgi / (2 + cslots), kind = sgi % (2 + cslots);
+                const int y = r0 + j;
+                const float sy = src_y(p, use_crop, crop, y);
+                const int y0 = static_cast<int>(sy);
+                const int y1 = min(y0 + 1, p.src_h - 1);
+                const float cyf = fminf(fmaxf(sy * 0.5f - 0.25f, 0.0f), static_cast<float>(ch - 1));
+                const int cy0 = static_cast<int>(cyf);
+                const int cy1 = min(cy0 + 1, ch - 1);
+                unsigned long long a0, reg_lo, reg_hi;  // segment start; readable bytes of its plane
+                int len, slot_off;
+                if (kind < 2) {
+                    reg_lo = reinterpret_cast<unsigned long long>(yp);
+                    reg_hi = reg_lo + static_cast<unsigned long long>(p.src_h - 1) * p.y_stride + p.src_w;
+                    a0 = reg_lo + static_cast<unsigned long long>(kind ? y1 : y0) * p.y_stride + fx_lo;
+                    len = ylen;
+                    slot_off = j * row_bytes + kind * ypitch;
+                } else {
+                    const int ck = kind - 2;                  // shared: 0 upper, 1 lower; else 0 Ua 1 Ub 2 Va 3 Vb
+                    const int crow = (shared_uv ? ck : (ck & 1)) ? cy1 : cy0;
+                    const unsigned char* base = shared_uv ? uvp : (ck < 2 ? cbp : crp);
+                    reg_lo = reinterpret_cast<unsigned long long>(base);
+                    reg_hi = reg_lo + static_cast<unsigned long long>(ch - 1) * p.c_stride + (cw - 1) * cstep + 1 +
+                             (shared_uv ? 1 : 0);
+                    a0 = reg_lo + static_cast<unsigned long long>(crow) * p.c_stride + cfx_lo * cstep;
+                    len = shared_uv ? uvlen : clen;
+                    slot_off = j * row_bytes + 2 * ypitch + ck * cpitch;
+                }
+                const unsigned long long a1 = a0 + len;
+                const int phase = static_cast<int>(a0 & 15ull);
+                unsigned char* slot = slots + slot_off;      // holds global bytes [a0 - phase, ...)
+                // Copy whole 16-byte chunks around the segment, but never beyond the plane: only the
+                // first and the last row of a plane can have a ragged edge, moved by plain loads.
+                lo = a0 & ~15ull;
+                if (lo < reg_lo) lo += 16;
+                unsigned long long hi = (a1 + 15ull) & ~15ull;
+                if (hi > reg_hi) hi = a1 & ~15ull;
+                bytes = hi > lo ? static_cast<unsigned>(hi - lo) : 0u;
+                dst = smem_addr(slot) + static_cast<uint32_t>(lo - (a0 - phase));
+                const unsigned long long head_end = bytes ? (lo < a1 ? lo : a1) : a1;
+                for (unsigned long long a = a0; a < head_end; ++a)
+                    slot[phase + (a - a0)] = *reinterpret_cast<const unsigned char*>(a);
+                if (bytes)
+                    for (unsigned long long a = (hi > a0 ? hi : a0); a < a1; ++a)
+                        slot[phase + (a - a0)] = *reinterpret_cast<const unsigned char*>(a);
+                // table entry: the lane that stages a row's first segment also writes its weights
+                StageRow& e = table[j];
+                const int first = slot_off + phase + kStageHeader;
+                if (kind == 0) {
+                    e.ya = first;
+                    e.dy = sy - static_cast<float>(y0);
+                    e.idy = 1.0f - e.dy;
+                    e.cdy = cyf - static_cast<float>(cy0);
+                    e.icdy = 1.0f - e.cdy;
+                } else if (kind == 1) {
+                    e.yb = first;
+                } else if (shared_uv) {
+                    const int uo = first + (cbp > crp ? 1 : 0), vo = first + (crp > cbp ? 1 : 0);
+                    if (kind == 2) { e.ua = uo; e.va = vo; } else { e.ub = uo; e.vb = vo; }
+                } else {
+                    (kind == 2 ? e.ua : kind == 3 ? e.ub : kind == 4 ? e.va : e.vb) = first;
+                }
+            }
+            unsigned sum = bytes;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            total += sum;
+            __syncwarp();
+            if (bytes)
+                asm volatile(
+                    "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                    "l"(lo), "r"(bytes), "r"(mbar)
+                    : "memory");
+        }
+        // The expected byte count is posted after the copies were issued: the phase cannot
+        // complete before this arrival, whatever has landed by then.
+        __syncwarp();
+        if (threadIdx.x == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(total) : "memory");
+    }
+    // Per-column setup overlaps the copies.
+    const Consts c = make_consts(p);
+    const long long plane = static_cast<long long>(H) * W;
+    const long long frame_base = static_cast<long long>(t) * 3 * plane;
+    __syncthreads();  // row table and ragged bytes written by warp 0 are visible
+    if (!mbar_wait_bounded(mbar, 0u)) {
+        if (threadIdx.x == 0 && p.status) atomicOr(p.status, kVideoCopyTimeout);
+        return;
+    }
+
+    for (int x = threadIdx.x; x < W; x += blockDim.x) {
+        const float sx = src_x(p, use_crop, crop, flip, x);
+        const int x0 = static_cast<int>(sx);
+        const bool yedge = x0 + 1 > p.src_w - 1;
+        const float cxf = fminf(fmaxf(sx * 0.5f, 0.0f), static_cast<float>(cw - 1));
+        const int cx0 = static_cast<int>(cxf);
+        const bool cedge = cx0 + 1 > cw - 1;
+        const ColWeights w = make_col(sx - static_cast<float>(x0), cxf - static_cast<float>(cx0));
+        const unsigned char* const ycol = smem + (x0 - fx_lo);
+        const unsigned char* const ccol = smem + (cx0 - cfx_lo) * cstep;
+        const int ystep = yedge ? 0 : 1, ccstep = cedge ? 0 : cstep;
+        long long o = frame_base + static_cast<long long>(r0) * W + x;
+        for (int r = 0; r < rows; r += 2, o += 2 * W) {
+            Taps k;
+            PairWeights pw;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const StageRow& e = table[min(r + h, rows - 1)];
+                k.a0[h] = ycol[e.ya]; k.a1[h] = ycol[e.ya + ystep];
+                k.b0[h] = ycol[e.yb]; k.b1[h] = ycol[e.yb + ystep];
+                k.ua0[h] = ccol[e.ua]; k.ua1[h] = ccol[e.ua + ccstep];
+                k.ub0[h] = ccol[e.ub]; k.ub1[h] = ccol[e.ub + ccstep];
+                k.va0[h] = ccol[e.va]; k.va1[h] = ccol[e.va + ccstep];
+                k.vb0[h] = ccol[e.vb]; k.vb1[h] = ccol[e.vb + ccstep];
+                (&pw.dy.x)[h] = e.dy; (&pw.idy.x)[h] = e.idy; (&pw.cdy.x)[h] = e.cdy; (&pw.icdy.x)[h] = e.icdy;
+            }
+            convert_store<DTYPE>(k, pw, w, c, p.out, o, plane, W, r + 1 < rows);
         }
     }
 }
 
 std::atomic<unsigned long long> g_video_launches{0};
 
+template <int DTYPE>
+int opt_in() {
+    return static_cast<int>(cudaFuncSetAttribute(yuv420_staged_kernel<DTYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 kVideoStageMaxBytes));
+}
+
 }  // namespace
 
-int launch_video(const VideoParams& p, int out_dtype, void* stream) {
+// Shared memory the staged kernel needs for `rows` output rows per CTA (an upper bound over all
+// alignments: every segment is padded to a 16-byte multiple plus 16).
+int video_stage_bytes(const VideoParams& p, int rows) {
+    const int cw = (p.src_w + 1) / 2;
+    const int ypitch = (p.src_w + 30) & ~15;
+    const int cpitch_shared = ((cw - 1) * 2 + 2 + 30) & ~15, cpitch_split = ((cw - 1) * p.c_px_stride + 1 + 30) & ~15;
+    const int chroma = std::max(2 * cpitch_shared, 4 * cpitch_split);
+    return kStageHeader + rows * (2 * ypitch + chroma);
+}
+
+int prepare_video() {
+    int e = opt_in<0>();
+    if (!e) e = opt_in<1>();
+    return e;
+}
+
+int launch_video(VideoParams p, int out_dtype, void* stream) {
     const int threads = std::min(256, ((p.dst_w + 31) / 32) * 32);
-    const dim3 grid(static_cast<unsigned>((p.dst_h + kVideoRows - 1) / kVideoRows), static_cast<unsigned>(p.n));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (out_dtype == 0)
-        yuv420_kernel<0><<<grid, threads, 0, st>>>(p);
-    else
-        yuv420_kernel<1><<<grid, threads, 0, st>>>(p);
+    // Rows per CTA of the staged kernel: as many (even, at most kStageMaxRows) as keep the staging
+    // buffer near 40 KB, so that several CTAs share an SM and overlap copy with arithmetic.
+    int rows = 0;
+    if (p.use_staged) {
+        for (int r = kStageMaxRows; r >= 2; r -= 2) {
+            if (video_stage_bytes(p, r) <= (r == 2 ? kVideoStageMaxBytes : 40 * 1024)) {
+                rows = r;
+                break;
+            }
+        }
+    }
+    if (rows) {
+        p.stage_rows = rows;
+        const int smem = video_stage_bytes(p, rows);
+        const dim3 grid(static_cast<unsigned>((p.dst_h + rows - 1) / rows), static_cast<unsigned>(p.n));
+        if (out_dtype == 0)
+            yuv420_staged_kernel<0><<<grid, threads, smem, st>>>(p);
+        else
+            yuv420_staged_kernel<1><<<grid, threads, smem, st>>>(p);
+    } else {
+        const dim3 grid(static_cast<unsigned>((p.dst_h + kDirectRows - 1) / kDirectRows), static_cast<unsigned>(p.n));
+        if (out_dtype == 0)
+            yuv420_direct_kernel<0><<<grid, threads, 0, st>>>(p);
+        else
+            yuv420_direct_kernel<1><<<grid, threads, 0, st>>>(p);
+    }
     g_video_launches.fetch_add(1, std::memory_order_relaxed);
     return static_cast<int>(cudaGetLastError());
 }

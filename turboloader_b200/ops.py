@@ -68,15 +68,16 @@ def cuda_video_clip_yuv420(y_ptrs, cb_ptrs, cr_ptrs, y_stride, c_stride, c_px_st
     return int(out)
 
 
-def video_yuv420(y_ptrs, cb_ptrs, cr_ptrs, *, y_stride, c_stride, c_px_stride, src_w, src_h, out, crops=None,
-                 flips=None, clip_len=0, bt709=False, mean=IMAGENET_MEAN, std=IMAGENET_STD, stream=None):
-    """Asynchronous form (``tlb_video_yuv420``): ``out`` is a caller-allocated CUDA tensor
-    (n, 3, dst_h, dst_w), float32 or bfloat16; ``crops`` an (n_clips, 4) array of windows shared by
-    ``clip_len`` consecutive frames each (None: whole-frame resize)."""
+def make_video_desc(y_ptrs, cb_ptrs, cr_ptrs, *, y_stride, c_stride, c_px_stride, src_w, src_h, out, crops=None,
+                    flips=None, clip_len=0, bt709=False, mean=IMAGENET_MEAN, std=IMAGENET_STD, status=None):
+    """Fill a ``tlb_video_desc``; the returned struct keeps its host arrays alive (``_keep``) and can
+    be enqueued any number of times with ``enqueue_video``."""
     import numpy as np
     import torch
 
     n = len(y_ptrs)
+    if not (len(cb_ptrs) == len(cr_ptrs) == n):
+        raise ValueError("y_ptrs, cb_ptrs and cr_ptrs must have the same length")
     d = _capi.VideoDesc()
     keep = [_addr_array(y_ptrs), _addr_array(cb_ptrs), _addr_array(cr_ptrs)]
     d.y_ptrs, d.cb_ptrs, d.cr_ptrs = [C.cast(a, C.c_void_p) for a in keep]
@@ -85,6 +86,8 @@ def video_yuv420(y_ptrs, cb_ptrs, cr_ptrs, *, y_stride, c_stride, c_px_stride, s
     d.src_w, d.src_h = int(src_w), int(src_h)
     if out.dim() != 4 or out.shape[0] != n or out.shape[1] != 3 or not out.is_contiguous():
         raise ValueError("out must be a contiguous (n, 3, dst_h, dst_w) CUDA tensor")
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("out must be float32 or bfloat16")
     d.dst_h, d.dst_w = int(out.shape[2]), int(out.shape[3])
     if crops is not None:
         cr = np.ascontiguousarray(crops, dtype=np.float32).reshape(-1, 4)
@@ -96,11 +99,28 @@ def video_yuv420(y_ptrs, cb_ptrs, cr_ptrs, *, y_stride, c_stride, c_px_stride, s
     d.mean, d.std = _capi.f3(mean), _capi.f3(std)
     d.out = out.data_ptr()
     d.out_dtype = _capi.TLB_F32 if out.dtype == torch.float32 else _capi.TLB_BF16
-    if out.dtype not in (torch.float32, torch.bfloat16):
-        raise TypeError("out must be float32 or bfloat16")
+    if status is not None:
+        d.status = _dev_ptr(status, torch.int32, "status")
+    d._keep = keep + [out, status]
+    return d
+
+
+def enqueue_video(desc, stream_ptr) -> None:
+    """``tlb_video_yuv420`` on a raw stream handle (int)."""
+    _capi.check(_capi.load().tlb_video_yuv420(C.byref(desc), C.c_void_p(stream_ptr)))
+
+
+def video_yuv420(y_ptrs, cb_ptrs, cr_ptrs, *, out, stream=None, **kw):
+    """Asynchronous form (``tlb_video_yuv420``): ``out`` is a caller-allocated CUDA tensor
+    (n, 3, dst_h, dst_w), float32 or bfloat16; ``crops`` an (n_clips, 4) array of windows shared by
+    ``clip_len`` consecutive frames each (None: whole-frame resize).  Keyword arguments as
+    ``make_video_desc``."""
+    import torch
+
+    d = make_video_desc(y_ptrs, cb_ptrs, cr_ptrs, out=out, **kw)
     st = stream if stream is not None else torch.cuda.current_stream(out.device)
     with torch.cuda.device(out.device):
-        _capi.check(_capi.load().tlb_video_yuv420(C.byref(d), C.c_void_p(st.cuda_stream)))
+        enqueue_video(d, st.cuda_stream)
     return out
 
 
