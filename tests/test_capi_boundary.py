@@ -117,3 +117,48 @@ def test_no_gpu_means_unavailable_not_fallback():
     assert ops.features()["cpu_fallback"] is False
     with pytest.raises(RuntimeError):
         ops.cuda_resize_normalize([np.zeros((4, 4, 3), np.uint8)], 2, 2)
+
+
+def test_video_descriptor_is_validated_on_the_host():
+    lib = _capi.load()
+    ptrs = (C.c_size_t * 2)(4096, 8192)
+    out = np.zeros(16, np.float32)
+
+    def vd(**kw):
+        d = _capi.VideoDesc()
+        d.y_ptrs = d.cb_ptrs = d.cr_ptrs = C.cast(ptrs, C.c_void_p)
+        d.n, d.y_stride, d.c_stride, d.c_px_stride = 2, 32, 16, 1
+        d.src_w, d.src_h, d.dst_h, d.dst_w = 32, 32, 8, 8
+        d.mean, d.std = _capi.f3((0, 0, 0)), _capi.f3((1, 1, 1))
+        d.out = out.ctypes.data
+        for k, v in kw.items():
+            setattr(d, k, v)
+        return d
+
+    assert lib.tlb_video_yuv420(None, None) == 1
+    assert lib.tlb_video_yuv420(C.byref(vd(n=0)), None) == 0  # empty batch: nothing to do
+    for kw in (dict(y_stride=31), dict(c_px_stride=3), dict(c_stride=15), dict(dst_w=0), dict(out=None),
+               dict(out_dtype=5), dict(clip_len=-1), dict(std=_capi.f3((1, 0, 1)))):
+        assert lib.tlb_video_yuv420(C.byref(vd(**kw)), None) == 1, kw
+        assert lib.tlb_last_error()
+    assert lib.tlb_video_yuv420(C.byref(vd(n=70000)), None) == 7
+    bad_crop = np.array([0, 0, np.inf, 4], np.float32)
+    assert lib.tlb_video_yuv420(C.byref(vd(crops=bad_crop.ctypes.data)), None) == 2
+    null_plane = (C.c_size_t * 2)(4096, 0)
+    assert lib.tlb_video_yuv420(C.byref(vd(cb_ptrs=C.cast(null_plane, C.c_void_p))), None) == 1
+    assert b"frame 1" in lib.tlb_last_error()
+    m, s = _capi.f3((0, 0, 0)), _capi.f3((1, 1, 1))
+    assert lib.tlb_video_yuv420_batch(ptrs, ptrs, ptrs, 0, 32, 16, 1, 32, 32, 8, 8, 0, m, s) == 0
+
+
+def test_stream_core_arguments_are_validated_on_the_host():
+    lib = _capi.load()
+    img = np.zeros((4, 8, 8, 3), np.uint8)
+    m, s = _capi.f3((0, 0, 0)), _capi.f3((1, 1, 1))
+    assert not lib.tlb_stream_create(None, 4, 8, 8, 2, m, s, 3, 1, None, 0, 0, 0, 0)
+    assert not lib.tlb_stream_create(img.ctypes.data, 0, 8, 8, 2, m, s, 3, 1, None, 0, 0, 0, 0)
+    assert not lib.tlb_stream_create(img.ctypes.data, 4, 8, 8, 2, m, s, 3, 1, None, 0, 0, 9, 0)
+    assert lib.tlb_last_error()
+    assert lib.tlb_stream_num_batches(None) == -1
+    assert lib.tlb_stream_begin_epoch(None, None) == 1
+    lib.tlb_stream_destroy(None)  # a no-op
