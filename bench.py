@@ -346,6 +346,51 @@ def reference_gpu_leg(wl, lib, torch, device, sample=512):
                               "reference_img_per_s": bs / t_ref, "ours_img_per_s": bs / t_ours,
                               "reference_GB_per_s": nbytes / t_ref / 1e9, "ours_GB_per_s": nbytes / t_ours / 1e9}
     del data
+
+    # (c) streaming from pinned host memory (dataset larger than device memory): one epoch of 20 000
+    # 160x160 images in batches of 1024, 3 slots: its CudaStreamCore (3 worker threads, blocking
+    # hand-over) against tlb_stream_* (no threads, blocking hand-over here too for a like-for-like loop).
+    ns, bs_s = 20000, 1024
+    host = torch.empty((ns, hw, hw, 3), dtype=torch.uint8).pin_memory()
+    host.numpy()[...] = np.random.RandomState(3).randint(0, 256, size=(64, hw, hw, 3), dtype=np.uint8)[np.arange(ns) % 64]
+    core = rlib.tlrefcuda_stream_create(host.data_ptr(), ns, hw, hw, bs_s, mean.ctypes.data_as(f32p),
+                                        std.ctypes.data_as(f32p), 3, 1)
+    nn = C.c_int(0)
+
+    def ref_epoch():
+        rlib.tlrefcuda_stream_begin_epoch(core)
+        got = 0
+        while rlib.tlrefcuda_stream_next(core, C.byref(nn)):
+            got += nn.value
+        return got
+
+    ref_epoch()
+    t0 = time.perf_counter()
+    got = ref_epoch()
+    t_ref = time.perf_counter() - t0
+    rlib.tlrefcuda_stream_destroy(core)
+    ours = lib.tlb_stream_create(host.data_ptr(), ns, hw, hw, bs_s, _capi.f3(mean), _capi.f3(std), 3, 1, None, 0, 0, 0, 0)
+    ptr = C.c_size_t(0)
+    n32 = C.c_int32(0)
+
+    def our_epoch():
+        lib.tlb_stream_begin_epoch(ours, None)
+        tot = 0
+        while True:
+            lib.tlb_stream_next(ours, C.byref(ptr), C.byref(n32), None)
+            if n32.value == 0:
+                return tot
+            tot += n32.value
+
+    our_epoch()
+    t0 = time.perf_counter()
+    got2 = our_epoch()
+    t_ours = time.perf_counter() - t0
+    lib.tlb_stream_destroy(ours)
+    res["streaming"] = {"sample": f"one epoch of {ns} x {hw}x{hw} uint8 images from pinned host memory, batch {bs_s}, 3 slots, "
+                                  "float32 NCHW on the device, host waits for every batch",
+                        "reference_img_per_s": got / t_ref, "ours_img_per_s": got2 / t_ours,
+                        "ours_h2d_GB_per_s": got2 * hw * hw * 3 / t_ours / 1e9}
     return res
 
 

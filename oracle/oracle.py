@@ -245,6 +245,16 @@ def ref_cuda(nofma: bool = False):
         lib.tlrefcuda_video_yuv420_batch.argtypes = [up, up, up] + [C.c_int] * 9 + [_f32p, _f32p]
         lib.tlrefcuda_video_clip_yuv420.restype = C.c_size_t
         lib.tlrefcuda_video_clip_yuv420.argtypes = [up, up, up] + [C.c_int] * 8 + [_f32p, C.c_int, C.c_int, _f32p, _f32p]
+        lib.tlrefcuda_stream_create.restype = C.c_void_p
+        lib.tlrefcuda_stream_create.argtypes = [C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int, _f32p, _f32p, C.c_int, C.c_int]
+        lib.tlrefcuda_stream_destroy.restype = None
+        lib.tlrefcuda_stream_destroy.argtypes = [C.c_void_p]
+        lib.tlrefcuda_stream_num_batches.restype = C.c_int
+        lib.tlrefcuda_stream_num_batches.argtypes = [C.c_void_p]
+        lib.tlrefcuda_stream_begin_epoch.restype = None
+        lib.tlrefcuda_stream_begin_epoch.argtypes = [C.c_void_p]
+        lib.tlrefcuda_stream_next.restype = C.c_size_t
+        lib.tlrefcuda_stream_next.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
         _ref_cuda[path] = lib
     return _ref_cuda[path]
 

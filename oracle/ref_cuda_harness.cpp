@@ -61,3 +61,18 @@ API uintptr_t tlrefcuda_video_clip_yuv420(const uintptr_t* y, const uintptr_t* c
     return turboloader::cuda::video_clip_yuv420(vy, vcb, vcr, y_stride, c_stride, c_px_stride, src_w, src_h, dst_h,
                                                 dst_w, crop, flip != 0, bt709 != 0, mean, std_);
 }
+
+// CudaStreamCore (cuda_transforms.hpp:100-112): dataset in pinned host memory streamed by K worker
+// threads.  next returns the device address of the next ready (n,3,h,w) float32 batch, 0 at the end.
+API void* tlrefcuda_stream_create(uintptr_t host_ptr, int n, int h, int w, int batch, const float* mean,
+                                  const float* std_, int num_slots, int drop_last) {
+    return new turboloader::cuda::CudaStreamCore(host_ptr, n, h, w, batch, mean, std_, num_slots, drop_last != 0);
+}
+API void tlrefcuda_stream_destroy(void* core) { delete static_cast<turboloader::cuda::CudaStreamCore*>(core); }
+API int tlrefcuda_stream_num_batches(void* core) {
+    return static_cast<turboloader::cuda::CudaStreamCore*>(core)->num_batches();
+}
+API void tlrefcuda_stream_begin_epoch(void* core) { static_cast<turboloader::cuda::CudaStreamCore*>(core)->begin_epoch(); }
+API uintptr_t tlrefcuda_stream_next(void* core, int* out_n) {
+    return static_cast<turboloader::cuda::CudaStreamCore*>(core)->next_batch(out_n);
+}

@@ -566,7 +566,6 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         const int4 m = meta[i % kSlots];  // {output rows, new source rows, last?, first output row}
 
         // ---- H step: new source rows -> horizontally interpolated fp32 in the strip's ring ----
-#ifndef TLB_EXP_SKIP_H
         if (h_active) {
             const unsigned char* rawb = raw + b * Rr * own_pitch;
             const int2* rowoff = reinterpret_cast<const int2*>(smem + kSmemRowOff) + (i % kSlots) * 32;
@@ -590,12 +589,10 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
                 }
             }
         }
-#endif
         __syncwarp();  // the strip's new h rows are visible to the whole warp; raw reads are done
         if (lane == 0) mbar_arrive(smem_addr(smem + kSmemEmpty + 8 * b));  // this warp is done with raw buffer b
 
         // ---- V step: blend, truncate, normalize, store --------------------------------------
-#ifndef TLB_EXP_SKIP_V
         if (v_active) {
             const float4* rowp = rowp_tile + (m.w - ty0);
             if (v_full) {
@@ -644,7 +641,6 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
                 }
             }
         }
-#endif
         if (m.z) break;
         __syncwarp();  // every lane has consumed pass i before the ring slots are rewritten
     }

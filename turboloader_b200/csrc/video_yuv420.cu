@@ -337,12 +337,13 @@ struct __align__(16) StageRow {
     float dy, idy, cdy, icdy;
     int pad[2];
 };
-constexpr int kStageHeader = 16 + kStageMaxRows * static_cast<int>(sizeof(StageRow));
+constexpr int kStageBars = 8 * (kStageMaxRows / 2);  // one 8-byte mbarrier per pair of output rows
+constexpr int kStageHeader = kStageBars + kStageMaxRows * static_cast<int>(sizeof(StageRow));
 
 template <int DTYPE>
 __global__ void __launch_bounds__(256, 5) yuv420_staged_kernel(const __grid_constant__ VideoParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    StageRow* const table = reinterpret_cast<StageRow*>(smem + 16);
+    StageRow* const table = reinterpret_cast<StageRow*>(smem + kStageBars);
     const uint32_t mbar = smem_addr(smem);
     const int R = p.stage_rows;                   // output rows per CTA (even)
     const int t = blockIdx.y;                     // frame
@@ -381,20 +382,24 @@ __global__ void __launch_bounds__(256, 5) yuv420_staged_kernel(const __grid_cons
     const int row_bytes = 2 * ypitch + cslots * cpitch;
     unsigned char* const slots = smem + kStageHeader;
 
-    if (threadIdx.x < 32) {
-        if (threadIdx.x == 0) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(1u) : "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        }
-        __syncwarp();
-        // ---- one lane per staged segment: row table entry + copy ------------------------------
+    // One mbarrier per PAIR of output rows: the pairs' copies are all issued up front and the
+    // arithmetic on pair i starts as soon as its own rows have landed, while later pairs are
+    // still in flight.
+    const int npairs = (rows + 1) >> 1;
+    if (threadIdx.x < npairs) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar + 8 * threadIdx.x), "r"(1u) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    {
+        // ---- one thread per staged segment: row table entry + copy ---------------------------
         const int nseg = rows * (2 + cslots);
-        unsigned total = 0;
-        for (int sgi = threadIdx.x; sgi < ((nseg + 31) & ~31); sgi += 32) {
+        for (int sgi = threadIdx.x; sgi < nseg; sgi += blockDim.x) {
             unsigned bytes = 0;
             unsigned long long lo = 0;
             uint32_t dst = 0;
-            if (sgi < nseg) {
+            const uint32_t pbar = mbar + 8 * ((sgi / (2 + cslots)) >> 1);
+            {
                 const int j = sgi / (2 + cslots), kind = sgi % (2 + cslots);
                 const int y = r0 + j;
                 const float sy = src_y(p, use_crop, crop, y);
@@ -457,32 +462,28 @@ __global__ void __launch_bounds__(256, 5) yuv420_staged_kernel(const __grid_cons
                     (kind == 2 ? e.ua : kind == 3 ? e.ub : kind == 4 ? e.va : e.vb) = first;
                 }
             }
-            unsigned sum = bytes;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            total += sum;
-            __syncwarp();
-            if (bytes)
+            if (bytes) {
+                // The byte count is added to the pair's barrier before the copy is issued; the
+                // barrier's single arrival comes after every thread has done so (below).
+                asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(pbar), "r"(bytes) : "memory");
                 asm volatile(
                     "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                    "l"(lo), "r"(bytes), "r"(mbar)
+                    "l"(lo), "r"(bytes), "r"(pbar)
                     : "memory");
+            }
         }
-        // The expected byte count is posted after the copies were issued: the phase cannot
-        // complete before this arrival, whatever has landed by then.
-        __syncwarp();
-        if (threadIdx.x == 0)
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(total) : "memory");
     }
     // Per-column setup overlaps the copies.
     const Consts c = make_consts(p);
     const long long plane = static_cast<long long>(H) * W;
     const long long frame_base = static_cast<long long>(t) * 3 * plane;
-    __syncthreads();  // row table and ragged bytes written by warp 0 are visible
-    if (!mbar_wait_bounded(mbar, 0u)) {
-        if (threadIdx.x == 0 && p.status) atomicOr(p.status, kVideoCopyTimeout);
-        return;
-    }
+    __syncthreads();  // row table, ragged bytes and every expected byte count are in place
+    if (threadIdx.x < npairs)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar + 8 * threadIdx.x) : "memory");
+    // Each warp waits for a pair's rows once (the wait is uniform across the warp) and keeps a
+    // bit per pair, since the column loop below may visit the pairs more than once.
+    unsigned landed = 0;
+    bool gave_up = false;
 
     for (int x = threadIdx.x; x < W; x += blockDim.x) {
         const float sx = src_x(p, use_crop, crop, flip, x);
@@ -497,6 +498,13 @@ __global__ void __launch_bounds__(256, 5) yuv420_staged_kernel(const __grid_cons
         const int ystep = yedge ? 0 : 1, ccstep = cedge ? 0 : cstep;
         long long o = frame_base + static_cast<long long>(r0) * W + x;
         for (int r = 0; r < rows; r += 2, o += 2 * W) {
+            if (!((landed >> (r >> 1)) & 1u)) {
+                if (!mbar_wait_bounded(mbar + 8 * (r >> 1), 0u)) {
+                    gave_up = true;
+                    break;
+                }
+                landed |= 1u << (r >> 1);
+            }
             Taps k;
             PairWeights pw;
 #pragma unroll
@@ -512,6 +520,13 @@ __global__ void __launch_bounds__(256, 5) yuv420_staged_kernel(const __grid_cons
             }
             convert_store<DTYPE>(k, pw, w, c, p.out, o, plane, W, r + 1 < rows);
         }
+        if (gave_up) break;
+    }
+    if (gave_up) {
+        // A copy did not land within the limit: report it, then give every copy of this CTA one
+        // more bounded chance to finish before the shared memory it targets is released.
+        if (p.status) atomicOr(p.status, kVideoCopyTimeout);
+        for (int i = 0; i < npairs; ++i) mbar_wait_bounded(mbar + 8 * i, 0u);
     }
 }
 
