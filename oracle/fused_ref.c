@@ -22,6 +22,7 @@
  *   src/pipeline/direct_batch_loader.hpp:219-257  crop copy -> resize -> flip -> normalize
  *   src/pipeline/direct_batch_loader.hpp:55-59    inv_std = 1.0f / std
  *   src/python/turboloader_bindings.cpp:1198-1258 normalize_u8_gather (index gather)
+ *   src/transforms/simd_utils.hpp:1939-2014  resize_triangle_antialias (opt-in quality resize)
  */
 #include <math.h>
 #include <stdint.h>
@@ -111,6 +112,85 @@ TLO_API uint16_t tlo_f32_to_bf16(float f) {
  * target size), flip the RESIZED u8 image, then normalize into three planes.
  * `scratch` must hold cw*ch*3 + dw*dh*3 bytes.
  */
+/*
+ * One axis of the antialiased triangle filter (simd_utils.hpp:1945-1975): for every output
+ * index the first source tap, the tap count and the normalized weights.  `weights` has
+ * dst_dim * max_taps entries.  Returns max_taps.
+ */
+static int tlo_aa_taps(int src_dim, int dst_dim, int* left, int* count, float* weights) {
+    const float scale = tlo_scale(src_dim, dst_dim);
+    const float support = scale > 1.0f ? scale : 1.0f;
+    const int max_taps = (int)ceilf(support * 2.0f) + 2;
+    if (!weights) return max_taps;
+    for (int i = 0; i < dst_dim; ++i) {
+        float* w = weights + (size_t)i * max_taps;
+        const float center = ((float)i + 0.5f) * scale;
+        int lo = (int)floorf(center - support);
+        int hi = (int)ceilf(center + support);
+        if (lo < 0) lo = 0;
+        if (hi > src_dim) hi = src_dim;
+        float wsum = 0.0f;
+        int n = 0;
+        for (int j = lo; j < hi && n < max_taps; ++j, ++n) {
+            const float t = ((float)j + 0.5f - center) / support;
+            float v = 1.0f - fabsf(t);
+            if (v < 0.0f) v = 0.0f;
+            w[n] = v;
+            wsum += v;
+        }
+        if (wsum > 0.0f)
+            for (int k = 0; k < n; ++k) w[k] /= wsum;
+        left[i] = lo;
+        count[i] = n;
+    }
+    return max_taps;
+}
+
+/*
+ * Antialiased (triangle filter) resize u8 HWC -> u8 HWC (simd_utils.hpp:1939-2014): horizontal
+ * pass into a float image, vertical pass, result rounded half up after a [0,255] clamp.  Every
+ * accumulation is a sequential fp32 sum of separately rounded products, first tap first.
+ */
+TLO_API void tlo_resize_antialias_u8(const uint8_t* src, uint8_t* dst, int sw, int sh, int dw, int dh) {
+    const int xt = tlo_aa_taps(sw, dw, NULL, NULL, NULL), yt = tlo_aa_taps(sh, dh, NULL, NULL, NULL);
+    int* xl = (int*)malloc(sizeof(int) * 2 * ((size_t)dw + dh));
+    int *xc = xl + dw, *yl = xc + dw, *yc = yl + dh;
+    float* xw = (float*)calloc((size_t)dw * xt + (size_t)dh * yt, sizeof(float));
+    float* yw = xw + (size_t)dw * xt;
+    float* tmp = (float*)malloc(sizeof(float) * (size_t)sh * dw * 3);
+    tlo_aa_taps(sw, dw, xl, xc, xw);
+    tlo_aa_taps(sh, dh, yl, yc, yw);
+    for (int y = 0; y < sh; ++y) {
+        const uint8_t* srow = src + (size_t)y * sw * 3;
+        float* trow = tmp + (size_t)y * dw * 3;
+        for (int x = 0; x < dw; ++x) {
+            const float* w = xw + (size_t)x * xt;
+            for (int c = 0; c < 3; ++c) {
+                float acc = 0.0f;
+                for (int k = 0; k < xc[x]; ++k) acc += w[k] * (float)srow[(xl[x] + k) * 3 + c];
+                trow[x * 3 + c] = acc;
+            }
+        }
+    }
+    for (int y = 0; y < dh; ++y) {
+        const float* w = yw + (size_t)y * yt;
+        for (int x = 0; x < dw; ++x)
+            for (int c = 0; c < 3; ++c) {
+                float acc = 0.0f;
+                for (int k = 0; k < yc[y]; ++k) acc += w[k] * tmp[((size_t)(yl[y] + k) * dw + x) * 3 + c];
+                float v = acc + 0.5f;
+                v = v > 255.0f ? 255.0f : v;
+                v = v < 0.0f ? 0.0f : v;
+                dst[((size_t)y * dw + x) * 3 + c] = (uint8_t)v;
+            }
+    }
+    free(tmp);
+    free(xw);
+    free(xl);
+}
+
+static int g_antialias = 0; /* set per call by tlo_fused_batch_aa; the oracle is single-threaded */
+
 static void tlo_one_sample(const uint8_t* img, int iw, int ih, int cx, int cy, int cw, int ch,
                            int flip, int dw, int dh, int normalize_01, const float* mean,
                            const float* inv_std, float* out_chw, uint8_t* scratch) {
@@ -122,6 +202,8 @@ static void tlo_one_sample(const uint8_t* img, int iw, int ih, int cx, int cy, i
                (size_t)cw * 3);
     if (cw == dw && ch == dh)
         memcpy(resized, cropped, (size_t)dw * dh * 3);
+    else if (g_antialias)
+        tlo_resize_antialias_u8(cropped, resized, cw, ch, dw, dh);
     else
         tlo_resize_bilinear_u8(cropped, resized, cw, ch, dw, dh);
     if (flip) {
@@ -175,6 +257,18 @@ TLO_API int tlo_fused_batch(const uint8_t* src, const int64_t* offsets, const in
     }
     free(scratch);
     return 0;
+}
+
+/* Same, with the resize of direct_batch_loader.hpp:229-231 selected by `antialias`. */
+TLO_API int tlo_fused_batch_aa(const uint8_t* src, const int64_t* offsets, const int32_t* sizes,
+                               int64_t n_src, const int64_t* sel, const int32_t* boxes,
+                               const uint8_t* flips, int n, int dh, int dw, const float* mean,
+                               const float* std_, int normalize_01, float* out, int antialias) {
+    g_antialias = antialias != 0;
+    const int rc = tlo_fused_batch(src, offsets, sizes, n_src, sel, boxes, flips, n, dh, dw, mean, std_,
+                                   normalize_01, out);
+    g_antialias = 0;
+    return rc;
 }
 
 /* NCHW f32 -> NHWC f32 (same values, permuted). */

@@ -77,6 +77,8 @@ def _load(impl: str) -> C.CDLL:
         lib.tlo_fused_batch.restype = C.c_int
         lib.tlo_fused_batch.argtypes = [_u8p, _i64p, _i32p, C.c_int64, _i64p, _i32p, _u8p, C.c_int,
                                         C.c_int, C.c_int, _f32p, _f32p, C.c_int, _f32p]
+        lib.tlo_fused_batch_aa.restype = C.c_int
+        lib.tlo_fused_batch_aa.argtypes = lib.tlo_fused_batch.argtypes + [C.c_int]
         lib.tlo_resize_bilinear_u8.restype = None
         lib.tlo_resize_bilinear_u8.argtypes = [_u8p, _u8p, C.c_int, C.c_int, C.c_int, C.c_int]
         lib.tlo_f32_to_bf16_array.restype = None
@@ -93,6 +95,8 @@ def _load(impl: str) -> C.CDLL:
         lib.tlref_fused_batch.restype = C.c_int
         lib.tlref_fused_batch.argtypes = [_u8p, _i64p, _i32p, C.c_int64, _i64p, _i32p, _u8p, C.c_int,
                                           C.c_int, C.c_int, _f32p, _f32p, C.c_int, _f32p, C.c_int]
+        lib.tlref_fused_batch_aa.restype = C.c_int
+        lib.tlref_fused_batch_aa.argtypes = lib.tlref_fused_batch.argtypes + [C.c_int]
         lib.tlref_resize_bilinear.restype = None
         lib.tlref_resize_bilinear.argtypes = [_u8p, _u8p, C.c_int, C.c_int, C.c_int, C.c_int]
         lib.tlref_threads.restype = C.c_int
@@ -114,7 +118,7 @@ def _ptr(a, ty):
 
 
 def fused_batch(src, offsets, sizes, sel, boxes, flips, dst_h, dst_w, mean, std, normalize_01=True,
-                impl="port", threads=1, out=None):
+                impl="port", threads=1, out=None, antialias=False):
     """fp32 NCHW result of crop -> bilinear(u8, truncating) -> flip -> normalize.
 
     ``src`` packed uint8, ``offsets`` int64[n_src], ``sizes`` int32[n_src,2] as (w,h),
@@ -137,7 +141,11 @@ def fused_batch(src, offsets, sizes, sel, boxes, flips, dst_h, dst_w, mean, std,
     args = [_ptr(src, _u8p), _ptr(offsets, _i64p), _ptr(sizes, _i32p), n_src, _ptr(sel, _i64p),
             _ptr(boxes, _i32p), _ptr(flips, _u8p), n, dst_h, dst_w, _ptr(mean, _f32p),
             _ptr(std, _f32p), int(bool(normalize_01)), _ptr(out, _f32p)]
-    rc = lib.tlo_fused_batch(*args) if impl == "port" else lib.tlref_fused_batch(*args, int(threads))
+    if antialias:
+        rc = (lib.tlo_fused_batch_aa(*args, 1) if impl == "port"
+              else lib.tlref_fused_batch_aa(*args, int(threads), 1))
+    else:
+        rc = lib.tlo_fused_batch(*args) if impl == "port" else lib.tlref_fused_batch(*args, int(threads))
     if rc != 0:
         raise IndexError(f"sample {-rc - 1}: index or crop box out of range")
     return out

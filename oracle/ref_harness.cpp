@@ -49,10 +49,10 @@ __attribute__((visibility("default"))) void tlref_resize_bilinear(const uint8_t*
 // runs the samples on the calling thread; otherwise the reference pool
 // (hardware_concurrency threads) is used, as fill_batch does
 // (direct_batch_loader.hpp:106-113).
-__attribute__((visibility("default"))) int tlref_fused_batch(
+static int fused_batch_impl(
     const uint8_t* src, const int64_t* offsets, const int32_t* sizes, int64_t n_src,
     const int64_t* sel, const int32_t* boxes, const uint8_t* flips, int n, int dh, int dw,
-    const float* mean, const float* std_, int normalize_01, float* out, int threads) {
+    const float* mean, const float* std_, int normalize_01, float* out, int threads, bool antialias) {
     const float inv_std[3] = {1.0f / std_[0], 1.0f / std_[1], 1.0f / std_[2]};
     for (int i = 0; i < n; ++i) {
         int64_t s = sel ? sel[i] : i;
@@ -77,6 +77,8 @@ __attribute__((visibility("default"))) int tlref_fused_batch(
         resized.resize(npix * 3);
         if (cw == dw && ch == dh)
             std::memcpy(resized.data(), cropped.data(), resized.size());
+        else if (antialias)  // direct_batch_loader.hpp:229-231
+            tsimd::resize_triangle_antialias(cropped.data(), resized.data(), cw, ch, dw, dh, 3);
         else
             tsimd::resize_bilinear_simd(cropped.data(), resized.data(), cw, ch, dw, dh, 3);
         if (flips && flips[i]) {
@@ -96,6 +98,23 @@ __attribute__((visibility("default"))) int tlref_fused_batch(
         turboloader::parallel_for((size_t)n, one);
     }
     return 0;
+}
+
+__attribute__((visibility("default"))) int tlref_fused_batch(
+    const uint8_t* src, const int64_t* offsets, const int32_t* sizes, int64_t n_src,
+    const int64_t* sel, const int32_t* boxes, const uint8_t* flips, int n, int dh, int dw,
+    const float* mean, const float* std_, int normalize_01, float* out, int threads) {
+    return fused_batch_impl(src, offsets, sizes, n_src, sel, boxes, flips, n, dh, dw, mean, std_, normalize_01, out,
+                            threads, false);
+}
+
+// The same pipeline with DirectBatchCore's `antialias` option on.
+__attribute__((visibility("default"))) int tlref_fused_batch_aa(
+    const uint8_t* src, const int64_t* offsets, const int32_t* sizes, int64_t n_src,
+    const int64_t* sel, const int32_t* boxes, const uint8_t* flips, int n, int dh, int dw,
+    const float* mean, const float* std_, int normalize_01, float* out, int threads, int antialias) {
+    return fused_batch_impl(src, offsets, sizes, n_src, sel, boxes, flips, n, dh, dw, mean, std_, normalize_01, out,
+                            threads, antialias != 0);
 }
 
 }  // extern "C"
