@@ -91,6 +91,14 @@ typedef struct tlb_transform_desc {
                                /*   (uniform box width, else src_w, which must then be set */
                                /*   to the widest image)                                   */
     uint32_t* status;          /* device word OR-ed with TLB_DEV_* bits, or NULL           */
+
+    /* -- resize filter ---------------------------------------------------------------- */
+    int32_t antialias;         /* 0: bilinear (above).  1: the reference's opt-in triangle  */
+                               /*   filter whose support widens on downscale, rounded half  */
+                               /*   up (DirectBatchCore antialias=true,                     */
+                               /*   src/transforms/simd_utils.hpp:1939-2014)                */
+    int32_t max_crop_h;        /* antialias only: upper bound of any crop height; 0 = derive */
+                               /*   (uniform box height, else src_h = the tallest image)    */
 } tlb_transform_desc;
 
 /* ---- capability ----------------------------------------------------------------------

@@ -13,6 +13,8 @@ Files written:
   fused_small.npz     full fp32 outputs of the fused crop/flip/resize/normalize replay
                       (direct_batch_loader.hpp:219-243) on small ragged inputs
   fused_hashes.json   sha256 of fused outputs at config-like shapes
+  antialias_hashes.json  the same pipeline with DirectBatchCore's antialias option
+                      (resize_triangle_antialias) on
   sharding.json       index lists of the reference sharding rules, sampler and epoch order
 """
 import hashlib
@@ -65,9 +67,9 @@ def fused_case(seed, n, lo, hi, dst_h, dst_w, with_sel):
     return dict(src=src, offsets=offsets, sizes=sizes, sel=sel, boxes=boxes, flips=flips, dst_h=dst_h, dst_w=dst_w)
 
 
-def run_ref(c, mean=MEAN, std=STD, n01=True):
+def run_ref(c, mean=MEAN, std=STD, n01=True, antialias=False):
     return O.fused_batch(c["src"], c["offsets"], c["sizes"], c["sel"], c["boxes"], c["flips"], c["dst_h"], c["dst_w"],
-                         mean, std, n01, impl="ref-parity")
+                         mean, std, n01, impl="ref-parity", antialias=antialias)
 
 
 FUSED_SMALL = [dict(seed=101, n=5, lo=9, hi=40, dst_h=12, dst_w=20, with_sel=False),
@@ -76,6 +78,11 @@ FUSED_SMALL = [dict(seed=101, n=5, lo=9, hi=40, dst_h=12, dst_w=20, with_sel=Fal
 FUSED_HASHED = [dict(seed=201, n=6, lo=200, hi=500, dst_h=224, dst_w=224, with_sel=False),
                 dict(seed=202, n=8, lo=160, hi=160, dst_h=128, dst_w=128, with_sel=True),
                 dict(seed=203, n=2, lo=512, hi=512, dst_h=384, dst_w=384, with_sel=False)]
+
+
+ANTIALIAS_HASHED = [dict(seed=301, n=5, lo=60, hi=260, dst_h=48, dst_w=64, with_sel=False),
+                    dict(seed=302, n=4, lo=300, hi=420, dst_h=24, dst_w=24, with_sel=True),
+                    dict(seed=303, n=4, lo=20, hi=40, dst_h=56, dst_w=40, with_sel=False)]
 
 
 def main():
@@ -102,6 +109,13 @@ def main():
         c = fused_case(**spec)
         hashes[json.dumps(spec, sort_keys=True)] = hashlib.sha256(run_ref(c).tobytes()).hexdigest()
     with open(os.path.join(HERE, "fused_hashes.json"), "w") as f:
+        json.dump(hashes, f, indent=1)
+
+    hashes = {}
+    for spec in ANTIALIAS_HASHED:
+        c = fused_case(**spec)
+        hashes[json.dumps(spec, sort_keys=True)] = hashlib.sha256(run_ref(c, antialias=True).tobytes()).hexdigest()
+    with open(os.path.join(HERE, "antialias_hashes.json"), "w") as f:
         json.dump(hashes, f, indent=1)
 
     sh = {"shard": [], "sampler": [], "order": []}

@@ -17,6 +17,12 @@ def oracle_f32(wl: Workload, impl="port") -> np.ndarray:
                          wl.std, wl.normalize_01, impl=impl)
 
 
+def expected_antialias(wl):
+    """Oracle result with the reference's opt-in antialiased resize (NCHW fp32)."""
+    return O.fused_batch(wl.src, wl.offsets, wl.sizes, wl.sel, wl.boxes, wl.flips, wl.dst_h, wl.dst_w, wl.mean, wl.std,
+                         wl.normalize_01, antialias=True)
+
+
 def expected(wl: Workload, impl="port") -> np.ndarray:
     """Oracle result in the workload's layout; bf16 as uint16 bit patterns."""
     ref = oracle_f32(wl, impl)

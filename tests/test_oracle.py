@@ -9,7 +9,7 @@ import pytest
 
 from oracle import oracle as O
 
-from golden.make_golden import FUSED_HASHED, FUSED_SMALL, MEAN, RESIZE_CASES, STD, fused_case, rs_image
+from golden.make_golden import ANTIALIAS_HASHED, FUSED_HASHED, FUSED_SMALL, MEAN, RESIZE_CASES, STD, fused_case, rs_image
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -105,3 +105,28 @@ def test_port_equals_compiled_reference():
     for i, (sw, sh, dw, dh) in enumerate(RESIZE_CASES):
         img = rs_image(77 + i, sh, sw)
         assert np.array_equal(O.resize_bilinear_u8(img, dh, dw, "port"), O.resize_bilinear_u8(img, dh, dw, "ref-parity"))
+
+
+@pytest.mark.skipif(not O.ref_available("parity"), reason="compiled reference harness (oracle/_ref) not present")
+@pytest.mark.parametrize("lo,hi,dst", [(60, 260, 48), (300, 420, 24), (30, 50, 64), (48, 48, 48)])
+def test_antialias_restatement_equals_the_reference(lo, hi, dst):
+    """resize_triangle_antialias (simd_utils.hpp:1939-2014) through the replayed DirectBatchCore
+    pipeline with antialias=true: the C restatement is bit-identical to the compiled reference."""
+    from turboloader_b200 import synthetic as S
+    wl = S.config2(n=6, seed=lo + dst, lo=lo, hi=hi, dst=dst)
+    a = O.fused_batch(wl.src, wl.offsets, wl.sizes, wl.sel, wl.boxes, wl.flips, dst, dst, wl.mean, wl.std, True,
+                      antialias=True)
+    b = O.fused_batch(wl.src, wl.offsets, wl.sizes, wl.sel, wl.boxes, wl.flips, dst, dst, wl.mean, wl.std, True,
+                      antialias=True, impl="ref-parity")
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_antialias_golden_hashes():
+    """Hashes of antialiased outputs produced by the compiled reference (tests/golden/make_golden.py)."""
+    gold = json.load(open(os.path.join(GOLD, "antialias_hashes.json")))
+    assert len(gold) >= 3
+    for spec in ANTIALIAS_HASHED:
+        c = fused_case(**spec)
+        got = O.fused_batch(c["src"], c["offsets"], c["sizes"], c["sel"], c["boxes"], c["flips"], c["dst_h"], c["dst_w"],
+                            MEAN, STD, True, antialias=True)
+        assert hashlib.sha256(got.tobytes()).hexdigest() == gold[json.dumps(spec, sort_keys=True)]

@@ -48,6 +48,8 @@ class TransformDesc(C.Structure):
         ("normalize_01", C.c_int32),
         ("max_crop_w", C.c_int32),
         ("status", C.c_void_p),
+        ("antialias", C.c_int32),
+        ("max_crop_h", C.c_int32),
     ]
 
 

@@ -21,6 +21,7 @@
 #include "../../include/turboloader_b200.h"
 #include "fused_params.h"
 #include "video_params.h"
+#include "antialias_params.h"
 #include "host_gather.h"
 
 namespace {
@@ -100,6 +101,7 @@ int ensure_prepared(DeviceState& st) {
     if (st.prepared.load(std::memory_order_acquire)) return TLB_OK;
     cudaError_t e = static_cast<cudaError_t>(tlb::prepare_device());
     if (e == cudaSuccess) e = static_cast<cudaError_t>(tlb::prepare_video());
+    if (e == cudaSuccess) e = static_cast<cudaError_t>(tlb::prepare_antialias());
     if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(max dynamic shared memory)");
     st.prepared.store(true, std::memory_order_release);
     return TLB_OK;
@@ -235,6 +237,27 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
     if (int rc = ensure_prepared(g_dev[dev])) return rc;
     tlb::FusedParams p{};
     fill_params(d, p);
+    if (d.antialias) {
+        // Opt-in triangle filter: its own kernel; tap tables are sized from the largest crop.
+        int max_crop_h = d.max_crop_h;
+        if (max_crop_h <= 0) max_crop_h = (!d.boxes && d.uniform_box[2] > 0) ? d.uniform_box[3] : d.src_h;
+        if (max_crop_h <= 0) return fail(TLB_ERR_INVALID_ARG, "antialias: max_crop_h (or src_h) is required");
+        tlb::AAPlan a{};
+        a.xt = tlb::aa_max_taps(max_crop_w, d.dst_w);
+        a.yt = tlb::aa_max_taps(max_crop_h, d.dst_h);
+        a.tile_cols = std::min(256, round_up(d.dst_w, 32));
+        a.n_col_tiles = (d.dst_w + a.tile_cols - 1) / a.tile_cols;
+        a.tile_rows = std::min(32, d.dst_h);
+        a.n_row_tiles = (d.dst_h + a.tile_rows - 1) / a.tile_rows;
+        a.smem_bytes = 4 * (a.xt * a.tile_cols + a.tile_rows * a.yt + 2 * a.tile_rows + a.yt * 3 * a.tile_cols);
+        if (a.smem_bytes > tlb::kAAMaxSmem)
+            return fail(TLB_ERR_TOO_LARGE, "antialias: a %d-tap filter does not fit the shared-memory tables", std::max(a.xt, a.yt));
+        a.grid = static_cast<long long>(d.n) * a.n_row_tiles * a.n_col_tiles;
+        if (a.grid > 0x7fffffffll) return fail(TLB_ERR_TOO_LARGE, "antialias: too many tiles for one launch");
+        cudaError_t e = static_cast<cudaError_t>(tlb::launch_antialias(p, a, d.out_dtype, d.out_layout, stream));
+        if (e != cudaSuccess) return cuda_fail(e, "antialias_kernel launch");
+        return TLB_OK;
+    }
     if (int rc = make_plan(d, max_crop_w, p.plan)) return rc;
     cudaError_t e = static_cast<cudaError_t>(tlb::launch_fused(p, d.out_dtype, d.out_layout, stream, may_overlap));
     if (e != cudaSuccess) return cuda_fail(e, "fused_transform_kernel launch");
@@ -791,7 +814,8 @@ int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block
 int tlb_set_launch_overlap(int enable) { return tlb::set_launch_overlap(enable); }
 
 uint64_t tlb_launch_count(void) {
-    return tlb::launch_count() + tlb::video_launch_count() + g_extra_launches.load(std::memory_order_relaxed);
+    return tlb::launch_count() + tlb::video_launch_count() + tlb::antialias_launch_count() +
+           g_extra_launches.load(std::memory_order_relaxed);
 }
 
 }  // extern "C"

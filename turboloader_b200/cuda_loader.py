@@ -91,7 +91,7 @@ class CudaResidentLoader:
     def _init_common(self, array, batch_size, *, mean=ops.IMAGENET_MEAN, std=ops.IMAGENET_STD, drop_last=True,
                      shuffle=False, seed=42, return_indices=False, crop_size=None, output_size=None,
                      hflip_prob=0.0, boxes=None, dtype=None, channels_last=False, as_tensor=None, labels=None,
-                     ring=4, device=None, flips=None, train_aug=False):
+                     ring=4, device=None, flips=None, train_aug=False, antialias=False):
         import torch
 
         if not ops.cuda_available():
@@ -119,6 +119,7 @@ class CudaResidentLoader:
         self.return_indices = bool(return_indices)
         self.hflip_prob = float(hflip_prob)
         self.channels_last = bool(channels_last)
+        self.antialias = bool(antialias)  # DirectBatchCore's antialias option: triangle filter on downscale
         self.dtype = torch.float32 if dtype is None else dtype
         if self.dtype not in (torch.float32, torch.bfloat16):
             raise ValueError("dtype must be torch.float32 or torch.bfloat16")
@@ -279,6 +280,7 @@ class CudaResidentLoader:
                 d.std = _capi.f3(self.std)
                 d.normalize_01 = 1
                 d.max_crop_w = max_cw
+                d.antialias = int(self.antialias)
                 d.status = self._status.data_ptr()
                 stream = torch.cuda.current_stream(self._device)
                 _capi.check(lib.tlb_fused_transform(C.byref(d), C.c_void_p(stream.cuda_stream)))

@@ -236,7 +236,7 @@ def _dev_ptr(t, dtype, what):
 def make_desc(src, *, n, dst_h, dst_w, out, src_w=0, src_h=0, n_src=None, src_offsets=None, src_sizes=None,
               sel=None, boxes=None, uniform_box=None, flips=None, mean=IMAGENET_MEAN, std=IMAGENET_STD,
               normalize_01=True, channels_last=False, out_indices=None, labels_in=None, labels_out=None,
-              max_crop_w=0, status=None):
+              max_crop_w=0, status=None, antialias=False, max_crop_h=0):
     """Fill a ``tlb_transform_desc`` from CUDA tensors (all tables on the device)."""
     import torch
 
@@ -275,6 +275,8 @@ def make_desc(src, *, n, dst_h, dst_w, out, src_w=0, src_h=0, n_src=None, src_of
     d.std = _capi.f3(std)
     d.normalize_01 = int(bool(normalize_01))
     d.max_crop_w = int(max_crop_w)
+    d.antialias = int(bool(antialias))  # the reference's opt-in triangle-filter resize
+    d.max_crop_h = int(max_crop_h)
     d.status = _dev_ptr(status, torch.int32, "status")
     return d
 
