@@ -584,6 +584,8 @@ def main():
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--sets", type=int, default=2, help="distinct input/output sets cycled through")
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, CPU baseline and the other workloads")
+    ap.add_argument("--video-only", action="store_true",
+                    help="run only the YUV 4:2:0 clip leg and print its JSON (used for profiling that kernel)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -612,6 +614,10 @@ def main():
 
     if not ops.cuda_available():
         raise SystemExit("bench.py: the C-ABI library did not find an sm_100 device (no fallback exists)")
+    if args.video_only:
+        peak, _ = measured_peak_gbs()
+        print(json.dumps(video_leg(torch, device, torch.cuda.current_stream(), peak, steps=max(3, min(args.steps, 30)))))
+        return
     lib = _capi.load()
     # The timed stream carries nothing but this library's launches, one batch after another, which
     # is the condition under which consecutive launches may overlap head to tail.
@@ -701,6 +707,18 @@ def main():
                             "frac_of_peak": (r + w) / (s / 50) / 1e9 / peak, "batch": batches[0].wl.n,
                             "frac_of_peak_serialized": (r + w) / (s1 / 50) / 1e9 / peak}
         line["other_workloads"] = others
+        # The opt-in antialiased (triangle filter) resize on the default workload: same inputs, the
+        # descriptor's antialias flag set.  Quality path: 3-4x the arithmetic of the bilinear kernel.
+        try:
+            torch.cuda.empty_cache()
+            batches = make_device_batches(args.workload, seed, device, 2)
+            for b in batches:
+                b.desc.antialias = 1
+            s = time_steps(batches, lib, stream, 20, 3, torch, barrier)
+            line["antialias"] = {"workload": args.workload, "img_per_s": 20 * batches[0].wl.n / s,
+                                 "kernel": "antialias_kernel"}
+        except Exception as e:
+            line["antialias"] = {"error": repr(e)}
     elif world > 1:
         # Multi-GPU: e2e at N GPUs = every rank feeding its own GPU from its own pinned host shard.
         if args.workload in ("variable_rrc", "fixed_resize", "highres_nhwc") and not args.no_extras:
