@@ -130,7 +130,7 @@ class DeviceBatch:
             raise RuntimeError(lib.tlb_last_error().decode())
 
 
-def make_device_batches(name, seed, device, sets):
+def make_device_batches(name, seed, device, sets, resident_images=100_000):
     """Device-resident batches of the named workload (distinct data per set)."""
     import torch
 
@@ -143,7 +143,7 @@ def make_device_batches(name, seed, device, sets):
     if name == "resident_epoch":
         # 100,000 x 160x160x3 uniform-noise images resident in HBM (7.68 GB); batches of 1024
         # gathered through default_rng(seed).permutation; centre crop 144 -> 128, bf16 NCHW + indices.
-        n_ds, src, batch = 100_000, 160, 1024
+        n_ds, src, batch = int(resident_images), 160, 1024
         data = torch.randint(0, 256, (n_ds, src, src, 3), dtype=torch.uint8, device=device, generator=g)
         perm = np.random.default_rng(seed).permutation(n_ds).astype(np.int64)
         flips = (np.random.default_rng([seed, 0, 7]).random(n_ds) < 0.5).astype(np.uint8)
@@ -584,6 +584,8 @@ def main():
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--sets", type=int, default=2, help="distinct input/output sets cycled through")
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, CPU baseline and the other workloads")
+    ap.add_argument("--resident-images", type=int, default=100_000,
+                    help="dataset size of the resident_epoch workload (smaller for profiler captures)")
     ap.add_argument("--video-only", action="store_true",
                     help="run only the YUV 4:2:0 clip leg and print its JSON (used for profiling that kernel)")
     args = ap.parse_args()
@@ -628,7 +630,7 @@ def main():
 
     # Every rank owns a disjoint shard: its data are generated from a rank-specific seed.
     seed = args.seed + 100_003 * rank
-    batches = make_device_batches(args.workload, seed, device, args.sets)
+    batches = make_device_batches(args.workload, seed, device, args.sets, args.resident_images)
     wl = batches[0].wl
     launches0 = ops.launch_count()
     sampler.sample()

@@ -162,3 +162,22 @@ def test_stream_core_arguments_are_validated_on_the_host():
     assert lib.tlb_stream_num_batches(None) == -1
     assert lib.tlb_stream_begin_epoch(None, None) == 1
     lib.tlb_stream_destroy(None)  # a no-op
+
+
+def test_video_descriptor_from_python_and_no_device_error():
+    import torch
+    out = torch.empty((2, 3, 8, 8), dtype=torch.float32)
+    d = ops.make_video_desc([4096, 8192], [4096, 8192], [4100, 8200], y_stride=32, c_stride=16, c_px_stride=1, src_w=32,
+                            src_h=32, out=out, crops=[[0, 0, 16, 16]], flips=[1], clip_len=0, bt709=True)
+    assert (d.n, d.dst_h, d.dst_w, d.bt709, d.out_dtype) == (2, 8, 8, 1, _capi.TLB_F32)
+    assert d.crops and d.flips and d.out == out.data_ptr()
+    with pytest.raises(ValueError):
+        ops.make_video_desc([1], [1, 2], [1], y_stride=8, c_stride=4, c_px_stride=1, src_w=8, src_h=8, out=out)
+    with pytest.raises(TypeError):
+        ops.make_video_desc([1, 2], [1, 2], [1, 2], y_stride=8, c_stride=4, c_px_stride=1, src_w=8, src_h=8,
+                            out=out.to(torch.float16))
+    if torch.cuda.is_available():
+        pytest.skip("GPU present: the enqueue would run")
+    with pytest.raises(_capi.TurboLoaderB200Error) as e:
+        ops.enqueue_video(d, 0)
+    assert e.value.code == 6  # TLB_ERR_NO_DEVICE: there is no CPU fallback
