@@ -170,31 +170,61 @@ __global__ void __launch_bounds__(256) antialias_kernel(const __grid_constant__ 
     const float m0 = p.mean[0], m1 = p.mean[1], m2 = p.mean[2];
     const float i0 = p.inv_std[0], i1 = p.inv_std[1], i2 = p.inv_std[2];
 
-    int next_src = yl[0];  // next source row to filter horizontally
+    // Ring slots advance with the source rows (slot = source row modulo RR, kept incrementally:
+    // an integer modulo per tap was a third of the instructions of the first version).
+    int next_src = yl[0];      // next source row to filter horizontally
+    int next_slot = 0;         // ring slot of next_src
+    int lo_prev = yl[0], lo_slot = 0;  // first tap row of the previous output row and its slot
     for (int r = 0; r < ty1 - ty0; ++r) {
         const int lo = yl[r], n = yc[r];
+        lo_slot += lo - lo_prev;  // lo never decreases
+        lo_prev = lo;
+        while (lo_slot >= RR) lo_slot -= RR;
         // ---- horizontal pass for the source rows this output row adds ---------------------
+        if (next_src < lo) {  // rows no output row of this tile taps
+            next_slot += lo - next_src;
+            next_src = lo;
+            while (next_slot >= RR) next_slot -= RR;
+        }
         for (; next_src < lo + n; ++next_src) {
-            if (next_src < lo) continue;  // rows no output row of this tile taps
             const unsigned char* sp = col + next_src * row_pitch;
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f;
-            for (int q = 0; q < xn; ++q) {
-                const float w = xw[q * TC + tid];
-                a0 = __fadd_rn(a0, __fmul_rn(w, static_cast<float>(__ldg(sp + 3 * q))));
-                a1 = __fadd_rn(a1, __fmul_rn(w, static_cast<float>(__ldg(sp + 3 * q + 1))));
-                a2 = __fadd_rn(a2, __fmul_rn(w, static_cast<float>(__ldg(sp + 3 * q + 2))));
+            // w * (float)byte without an integer conversion: fma(2^23 + b, w, -2^23 * w) is exactly
+            // RN(b * w), the product the reference forms.  Four taps per trip keep 12 loads in flight.
+            for (int q0 = 0; q0 < xn; q0 += 4) {
+                unsigned b[4][3];
+                float w[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const bool on = q0 + u < xn;
+                    w[u] = on ? xw[(q0 + u) * TC + tid] : 0.0f;
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) b[u][c] = on ? static_cast<unsigned>(__ldg(sp + 3 * (q0 + u) + c)) : 0u;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (q0 + u < xn) {
+                        const float nw = __fmul_rn(-8388608.0f, w[u]);
+                        a0 = __fadd_rn(a0, __fmaf_rn(__uint_as_float(b[u][0] | 0x4B000000u), w[u], nw));
+                        a1 = __fadd_rn(a1, __fmaf_rn(__uint_as_float(b[u][1] | 0x4B000000u), w[u], nw));
+                        a2 = __fadd_rn(a2, __fmaf_rn(__uint_as_float(b[u][2] | 0x4B000000u), w[u], nw));
+                    }
+                }
             }
-            float* slot = myring + (next_src % RR) * 3 * TC;
+            float* slot = myring + next_slot * 3 * TC;
             slot[0] = a0;
             slot[TC] = a1;
             slot[2 * TC] = a2;
+            if (++next_slot == RR) next_slot = 0;
         }
         // ---- vertical pass, rounding, normalize, store --------------------------------------
         float v0 = 0.0f, v1 = 0.0f, v2 = 0.0f;
         const float* wr = yw + r * a.yt;
+        int vs = lo_slot;
         for (int q = 0; q < n; ++q) {
             const float w = wr[q];
-            const float* slot = myring + ((lo + q) % RR) * 3 * TC;
+            const float* slot = myring + vs * 3 * TC;
+            if (++vs == RR) vs = 0;
             v0 = __fadd_rn(v0, __fmul_rn(w, slot[0]));
             v1 = __fadd_rn(v1, __fmul_rn(w, slot[TC]));
             v2 = __fadd_rn(v2, __fmul_rn(w, slot[2 * TC]));
