@@ -86,3 +86,56 @@ def test_config3_resident_epoch_full():
     small = t.CudaResidentLoader.from_array(data, hflip_prob=0.0, **{**kw, "batch_size": 256})
     xs, idxs = next(iter(small))
     assert torch.equal(idxs, idx0[:256]) and torch.equal(xs, x0[:256])
+
+
+def test_config2_full_antialias():
+    """The opt-in triangle-filter resize on the full variable-size batch (512 images), bit-exact."""
+    from helpers import expected_antialias
+
+    def aa(d):
+        d.antialias = 1
+
+    wl = S.config2(seed=0, n=512)
+    res = run_gpu(wl, mutate=aa)
+    assert res["status"] == 0
+    want = expected_antialias(wl)
+    assert int((res["out"].view(np.uint32) != want.view(np.uint32)).sum()) == 0
+
+
+def test_video_clip_batch_full():
+    """The benchmark's clip workload shape: 8 clips x 16 NV12 frames of 1280x720, per-clip window and
+    flip, one launch; every 8th frame checked against the CPU oracle bit for bit, and the frames of
+    a clip are consistent with their shared window (re-running one clip alone gives the same bits)."""
+    import torch
+    n_clips, T, W, H, D = 8, 16, 1280, 720, 224
+    n = n_clips * T
+    g = torch.Generator(device="cuda")
+    g.manual_seed(11)
+    yb = torch.randint(0, 256, (n, H, W), dtype=torch.uint8, device="cuda", generator=g)
+    uv = torch.randint(0, 256, (n, H // 2, W), dtype=torch.uint8, device="cuda", generator=g)
+    rs = np.random.RandomState(5)
+    crops = np.zeros((n_clips, 4), np.float32)
+    for c in range(n_clips):
+        area = rs.uniform(0.35, 1.0)
+        cw, ch = int(min(W, round(W * np.sqrt(area)))), int(min(H, round(H * np.sqrt(area))))
+        crops[c] = (rs.randint(0, W - cw + 1), rs.randint(0, H - ch + 1), cw, ch)
+    flips = rs.randint(0, 2, n_clips).astype(np.int32)
+    yp = [yb.data_ptr() + i * H * W for i in range(n)]
+    cb = [uv.data_ptr() + i * (H // 2) * W for i in range(n)]
+    cr = [p + 1 for p in cb]
+    out = torch.empty((n, 3, D, D), dtype=torch.float32, device="cuda")
+    t.video_yuv420(yp, cb, cr, y_stride=W, c_stride=W, c_px_stride=2, src_w=W, src_h=H, out=out, crops=crops,
+                   flips=flips, clip_len=T)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    for i in range(0, n, 8):
+        y_h = yb[i].cpu().numpy()
+        uv_h = uv[i].cpu().numpy()
+        want = O.yuv420_frame(y_h, uv_h, uv_h.reshape(-1)[1:], 2, W, H, D, D, t.IMAGENET_MEAN, t.IMAGENET_STD,
+                              crop=tuple(crops[i // T]), flip=bool(flips[i // T]), c_stride=W)
+        assert np.array_equal(got[i].view(np.uint32), want.view(np.uint32)), f"frame {i}"
+    one = torch.empty((T, 3, D, D), dtype=torch.float32, device="cuda")
+    t.video_yuv420(yp[3 * T:4 * T], cb[3 * T:4 * T], cr[3 * T:4 * T], y_stride=W, c_stride=W, c_px_stride=2, src_w=W,
+                   src_h=H, out=one, crops=crops[3:4], flips=flips[3:4], clip_len=0)
+    torch.cuda.synchronize()
+    assert torch.equal(one, out[3 * T:4 * T])
