@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.environ.get("TLB_LIB") or os.path.join(HERE, "libturboloader_b200.so")
-SOURCES = ["fused_transform.cu", "host_gather.cu", "video_yuv420.cu", "antialias.cu", "capi.cu", "sharding.cpp"]
+SOURCES = ["fused_transform.cu", "host_gather.cu", "video_yuv420.cu", "antialias.cu", "normalize_copy.cu", "capi.cu", "sharding.cpp"]
 HEADERS = ["fused_params.h", "host_gather.h", "video_params.h", "antialias_params.h", os.path.join("..", "..", "include", "turboloader_b200.h")]
 
 NVCC_FLAGS = [

@@ -259,6 +259,15 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
         return TLB_OK;
     }
     if (int rc = make_plan(d, max_crop_w, p.plan)) return rc;
+    // Identity size (no resampling) on a uniform dataset: a plain streaming kernel does the job.
+    const bool uniform = !d.boxes && !d.src_sizes && !d.src_offsets;
+    const int cw = d.uniform_box[2] > 0 ? d.uniform_box[2] : d.src_w;
+    const int ch = d.uniform_box[2] > 0 ? d.uniform_box[3] : d.src_h;
+    if (uniform && cw == d.dst_w && ch == d.dst_h && env_int("TLB_IDENTITY_FAST", 1) != 0) {
+        cudaError_t ce = static_cast<cudaError_t>(tlb::launch_normalize_copy(p, d.out_dtype, d.out_layout, stream));
+        if (ce != cudaSuccess) return cuda_fail(ce, "normalize_copy_kernel launch");
+        return TLB_OK;
+    }
     cudaError_t e = static_cast<cudaError_t>(tlb::launch_fused(p, d.out_dtype, d.out_layout, stream, may_overlap));
     if (e != cudaSuccess) return cuda_fail(e, "fused_transform_kernel launch");
     return TLB_OK;
@@ -814,7 +823,7 @@ int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block
 int tlb_set_launch_overlap(int enable) { return tlb::set_launch_overlap(enable); }
 
 uint64_t tlb_launch_count(void) {
-    return tlb::launch_count() + tlb::video_launch_count() + tlb::antialias_launch_count() +
+    return tlb::launch_count() + tlb::video_launch_count() + tlb::antialias_launch_count() + tlb::normalize_copy_launch_count() +
            g_extra_launches.load(std::memory_order_relaxed);
 }
 

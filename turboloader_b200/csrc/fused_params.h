@@ -80,4 +80,9 @@ int prepare_device();
 unsigned long long launch_count();
 int set_launch_overlap(int enable);  // returns the previous setting
 
+// Implemented in normalize_copy.cu: the identity-size case (crop size == output size, uniform
+// dataset, no per-sample boxes).  Uses p.plan.vec_ok only.  Returns a cudaError_t as int.
+int launch_normalize_copy(const FusedParams& p, int out_dtype, int out_layout, void* stream);
+unsigned long long normalize_copy_launch_count();
+
 }  // namespace tlb
