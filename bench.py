@@ -11,10 +11,12 @@ fp32 NCHW 224x224).  Under torchrun every rank transforms batches of its own dis
 shard with no collective ("weak" scaling: per-rank work is fixed).
 
 Prints ONE JSON line (rank 0).  ``value`` is images/s over all ranks with inputs resident
-in HBM; ``e2e`` is the same metric through the host-image C-ABI entry point (pinned host
-pixels -> crop rows pulled across PCIe -> kernel -> device batch, status word read back every step); ``roofline``
-compares the kernel's algorithmic bytes per second with the measured HBM copy bandwidth;
-``cpu_baseline`` times the reference's own CPU fused path on this box's host cores.
+in HBM (median of several repeats of the K-step loop); ``e2e`` is the same metric through the
+host-image C-ABI entry point (pinned host pixels -> crop rows pulled across PCIe -> kernel ->
+device batch, status word read back every step); ``roofline`` compares the kernel's algorithmic
+bytes per second with the measured HBM copy bandwidth; ``cpu_baseline`` times the reference's own
+CPU fused path on this box's host cores; ``sharded_scaling`` (at every N) runs the 8-GPU scaling
+configuration -- 32,768 images split over the ranks by the package's own sharding functions.
 """
 from __future__ import annotations
 
@@ -123,6 +125,11 @@ class DeviceBatch:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         d.status = self.status.data_ptr()
         self.desc = d
+
+    def set_overlap(self, on):
+        """Per-call launch flag: back-to-back launches of a stream that carries only this library's
+        kernels may overlap head to tail (TLB_FLAG_LAUNCH_OVERLAP)."""
+        self.desc.flags = 1 if on else 0
 
     def launch(self, lib, stream_ptr):
         rc = lib.tlb_fused_transform(C.byref(self.desc), stream_ptr)
@@ -262,9 +269,21 @@ def cpu_baseline(wl, budget_s=4.0, min_passes=3):
     med = statistics.median(times)
     build = {"avx2fma": "-O3 -mavx2 -mfma -funroll-loops (hand-written AVX2 branch)",
              "parity": "-O2 -mavx2 -ffp-contract=off", "port": "C restatement, -O2, scalar"}[flavour]
-    return {"value": wl.n / med, "unit": UNIT, "cores": threads, "kind": kind,
-            "sample": f"{len(times)} passes over the {wl.n}-image batch of '{wl.name}' (median), build {build}, "
-                      f"host has {os.cpu_count()} logical cores"}
+    res = {"value": wl.n / med, "unit": UNIT, "cores": threads, "kind": kind,
+           "sample": f"{len(times)} passes over the {wl.n}-image batch of '{wl.name}' (median), build {build}, "
+                     f"host has {os.cpu_count()} logical cores"}
+    # The reference's own build flags (-march=native, setup.py:678) on an AVX-512 host select the
+    # header's scalar resize branch: reported beside the hand-written AVX2 branch above.
+    if kind == "reference" and flavour != "avx512" and O.ref_available("avx512"):
+        try:
+            cpu_reference_pass(wl, "avx512", threads)
+            ts = [cpu_reference_pass(wl, "avx512", threads) for _ in range(max(3, min(len(times), 10)))]
+            res["march_native"] = {"value": wl.n / statistics.median(ts), "unit": UNIT,
+                                   "build": "-O3 -mavx2 -mfma -mavx512f/bw/vl/dq -funroll-loops",
+                                   "branch": O.ref_branch("avx512")}
+        except Exception as e:  # the extra figure must never take the baseline down
+            res["march_native"] = {"error": repr(e)}
+    return res
 
 
 def reference_gpu_leg(wl, lib, torch, device, sample=512):
@@ -471,6 +490,13 @@ def video_leg(torch, device, stream, peak, steps=30):
 
 # ---- main ----------------------------------------------------------------------------------
 
+def bench_config(wl, seed):
+    """The ``config`` object: identical for both arms, so that their lines describe one workload."""
+    return {"workload": wl.name, "batch_per_gpu": wl.n, "dst": [wl.dst_h, wl.dst_w],
+            "out": f"{wl.dtype} {'NHWC' if wl.channels_last else 'NCHW'}", "seed": int(seed),
+            "sharding": "disjoint shard per rank, no collective"}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -492,9 +518,9 @@ def run_reference_arm(args):
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
             "warmup": args.warmup, "ms_per_step": 1e3 * dt / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl.name, "batch": wl.n, "dst": [wl.dst_h, wl.dst_w],
-                       "note": "reference CPU fused path (resize_bilinear_simd + deinterleave_hwc_to_chw_f32 on its "
-                               "own parallel_for), one host, rank 0 only"},
+            "config": bench_config(wl, args.seed),
+            "note": "reference CPU fused path (resize_bilinear_simd + deinterleave_hwc_to_chw_f32 on its own "
+                    "parallel_for), one host, rank 0 only",
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": kind,
                              "sample": f"each step = one pass over the {wl.n}-image batch, flavour {flavour}"},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -516,6 +542,174 @@ def time_steps(batches, lib, stream, steps, warmup, torch, barrier):
     torch.cuda.synchronize()
     barrier()
     return start.elapsed_time(stop) / 1e3
+
+
+def time_steps_repeated(batches, lib, stream, steps, warmup, torch, barrier, repeats=5):
+    """The K-step loop `repeats` times (a step stays one batch); returns the list of seconds."""
+    out = [time_steps(batches, lib, stream, steps, warmup, torch, barrier)]
+    for _ in range(repeats - 1):
+        out.append(time_steps(batches, lib, stream, steps, 0, torch, barrier))
+    return out
+
+
+def rank_cores(rank, world):
+    """A disjoint set of host cores for this rank (the allowed cores split into `world` blocks)."""
+    cores = sorted(os.sched_getaffinity(0))
+    per = max(1, len(cores) // world)
+    mine = cores[rank * per:(rank + 1) * per] or cores
+    return mine
+
+
+def sharded_scaling_leg(args, lib, torch, device, stream, rank, world, dist, barrier, peak, epochs=7):
+    """The 8-GPU sharded scaling configuration at this world size: a global set of 32,768 uint8
+    256x256x3 images (uniform noise) split into contiguous per-rank shards by the package's own
+    sharding functions, batches of 1024, RandomResizedCrop boxes (scale (0.08, 1)) and flips keyed by
+    the GLOBAL index, -> 224x224 bf16 NCHW.  Each rank keeps only its shard in HBM and transforms
+    it batch by batch with no collective; the epoch is timed on the device, max over ranks.  Pixels
+    of global image g come from a generator seeded with (seed, g // 1024), so a sample's bytes do
+    not depend on the world size.  After the timed region one rank-local batch is compared with the
+    CPU oracle, bit for bit."""
+    import turboloader_b200 as t
+    from turboloader_b200 import synthetic as S
+
+    total, batch, src, dst = 32768, 1024, 256, 224
+    shard = t.shard_indices("contiguous", total, world, rank)
+    order = t.direct_order(total, False, args.seed, 0, world > 1, rank, world)
+    if not np.array_equal(shard, order):
+        raise SystemExit("bench.py: shard_indices and direct_order disagree")
+    boxes_all, flips_all = S.config5_params(args.seed, total, src)
+    blocks = shard.reshape(-1, batch)
+    sizes = np.tile(np.array([[src, src]], np.int32), (batch, 1))
+    outs = [torch.empty((batch, 3, dst, dst), dtype=torch.bfloat16, device=device) for _ in range(3)]
+    batches = []
+    for i, glob in enumerate(blocks):
+        g = torch.Generator(device=device)
+        g.manual_seed(int(args.seed) * 1_000_003 + int(glob[0]) // batch)
+        data = torch.randint(0, 256, (batch, src, src, 3), dtype=torch.uint8, device=device, generator=g)
+        wl = S.Workload("sharded_scaling", np.empty(0, np.uint8), np.empty(0, np.int64), sizes, batch, dst, dst,
+                        boxes=boxes_all[glob].copy(), flips=flips_all[glob].copy(), dtype="bf16", uniform_hw=(src, src),
+                        notes={"global_indices": glob})
+        b = DeviceBatch(wl, device, src=data.view(-1))
+        b.out = outs[i % 3]
+        b.desc.out = b.out.data_ptr()
+        b.set_overlap(True)
+        batches.append(b)
+    sp = C.c_void_p(stream.cuda_stream)
+    secs = []
+    for e in range(epochs + 1):  # the first epoch is the warm-up
+        torch.cuda.synchronize()
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for b in batches:
+            b.launch(lib, sp)
+        stop.record(stream)
+        torch.cuda.synchronize()
+        tt = torch.tensor([start.elapsed_time(stop) / 1e3], dtype=torch.float64, device=device)
+        if dist is not None:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        if e > 0:
+            secs.append(float(tt.item()))
+    for b in batches:
+        if int(b.status.item()) != 0:
+            raise SystemExit("bench.py: device status word is non-zero (sharded_scaling)")
+    # parity, outside the timing: this rank's batch `pick` against the CPU oracle
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import expected
+    pick = rank % len(batches)
+    b = batches[pick]
+    b.set_overlap(False)
+    b.launch(lib, sp)
+    torch.cuda.synchronize()
+    wl = b.wl
+    wl.src = b.src.cpu().numpy()
+    wl.offsets = np.arange(batch, dtype=np.int64) * (src * src * 3)
+    got = b.out.view(torch.int16).cpu().numpy().view(np.uint16)
+    exact = bool(np.array_equal(got, expected(wl)))
+    flag = torch.tensor([1 if exact else 0], dtype=torch.int32, device=device)
+    if dist is not None:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag.item()) != 1:
+        raise SystemExit("bench.py: sharded_scaling output differs from the CPU oracle")
+    med = statistics.median(secs)
+    r, w = wl.algorithmic_bytes()
+    per_rank_gbs = (r + w) * len(batches) / med / 1e9
+    return {"workload": "32,768 x 256x256x3 uint8 split by tlb_shard_indices(contiguous) == tlb_direct_order, batch 1024, "
+                        "RRC(0.08,1) boxes + flips keyed by the global index, -> 224x224 bf16 NCHW",
+            "img_per_s": total / med, "epoch_ms_median": 1e3 * med, "epoch_ms_min": 1e3 * min(secs),
+            "epoch_ms_max": 1e3 * max(secs), "epochs_timed": len(secs), "batches_per_rank": len(batches),
+            "per_rank_GB_per_s": per_rank_gbs, "per_rank_frac_of_peak": per_rank_gbs / peak,
+            "timing": "CUDA events around each rank's epoch, max over ranks, median over epochs",
+            "parity": f"bit-exact against the CPU oracle on every rank (rank r checked its batch r % {len(batches)})"}
+
+
+def loader_epoch_leg(args, torch, device, peak, n_images):
+    """The product API on the resident-epoch configuration: CudaResidentLoader iterated over one
+    whole epoch (batches of 1024 gathered through the shuffled order, centre crop 144 -> 128, flips,
+    bf16 NCHW + indices), CUDA events around the epoch on the consumer's stream."""
+    import turboloader_b200 as t
+
+    g = torch.Generator(device=device)
+    g.manual_seed(args.seed + 3)
+    data = torch.randint(0, 256, (n_images, 160, 160, 3), dtype=torch.uint8, device=device, generator=g)
+    ld = t.CudaResidentLoader.from_array(data, batch_size=1024, shuffle=True, seed=args.seed, return_indices=True,
+                                         crop_size=144, output_size=128, hflip_prob=0.5, dtype=torch.bfloat16,
+                                         drop_last=True)
+    stream = torch.cuda.current_stream()
+    times = []
+    for ep in range(4):
+        ld.set_epoch(ep)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record(stream)
+        nb = 0
+        for x, idx in ld:
+            nb += 1
+        stop.record(stream)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        if ep > 0:
+            times.append(max(start.elapsed_time(stop) / 1e3, wall))
+    if ld.device_status() != 0:
+        raise SystemExit("bench.py: device status word is non-zero (loader_epoch)")
+    med = statistics.median(times)
+    per_img = 144 * 144 * 3 + 8 + 1 + 3 * 128 * 128 * 2 + 8
+    n = nb * 1024
+    del data
+    return {"api": "for x, idx in CudaResidentLoader(...)", "images": n_images, "batches": nb, "img_per_s": n / med,
+            "GB_per_s": n * per_img / med / 1e9, "frac_of_peak": n * per_img / med / 1e9 / peak,
+            "epochs_timed": len(times), "timing": "max(CUDA events on the consumer stream, host wall clock) per epoch, median"}
+
+
+def identity_leg(lib, torch, device, stream, peak, barrier, seed):
+    """The identity-size case of the resident loader (gather -> flip -> normalize -> layout/dtype, the
+    reference's normalize_gather_kernel operation): 1024 x 160x160 gathered from 20,000 resident
+    images, fp32 and bf16 NCHW."""
+    from turboloader_b200 import synthetic as S
+
+    n_ds, hw, bs = 20000, 160, 1024
+    g = torch.Generator(device=device)
+    g.manual_seed(seed + 5)
+    data = torch.randint(0, 256, (n_ds, hw, hw, 3), dtype=torch.uint8, device=device, generator=g)
+    res = {}
+    for dt in ("f32", "bf16"):
+        batches = []
+        for b in range(3):
+            sel = np.random.default_rng([seed, b]).permutation(n_ds)[:bs].astype(np.int64)
+            wl = S.Workload("identity_gather", np.empty(0, np.uint8), np.empty(0, np.int64),
+                            np.tile(np.array([[hw, hw]], np.int32), (n_ds, 1)), bs, hw, hw, sel=sel,
+                            flips=(np.random.default_rng([seed, b, 1]).random(bs) < 0.5).astype(np.uint8), dtype=dt,
+                            uniform_hw=(hw, hw))
+            batches.append(DeviceBatch(wl, device, src=data.view(-1)))
+        s = statistics.median(time_steps_repeated(batches, lib, stream, 50, 5, torch, barrier, repeats=3))
+        esz = 4 if dt == "f32" else 2
+        nbytes = bs * (hw * hw * 3 * (1 + esz) + 8 + 1 + 8)
+        res[dt] = {"img_per_s": 50 * bs / s, "GB_per_s": nbytes / (s / 50) / 1e9, "frac_of_peak": nbytes / (s / 50) / 1e9 / peak}
+    res["kernel"] = "normalize_copy_kernel"
+    res["workload"] = f"{bs} x {hw}x{hw} gathered from {n_ds} resident images, flips, NCHW"
+    del data
+    return res
 
 
 def e2e_steps(wl_sets, lib, stream, steps, warmup, torch, device):
@@ -582,12 +776,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="variable_rrc", choices=WORKLOADS)
     ap.add_argument("--seed", type=int, default=1234)
-    ap.add_argument("--sets", type=int, default=2, help="distinct input/output sets cycled through")
+    ap.add_argument("--sets", type=int, default=3, help="distinct input/output sets cycled through")
+    ap.add_argument("--repeats", type=int, default=5, help="times the K-step loop is timed (median reported)")
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, CPU baseline and the other workloads")
     ap.add_argument("--resident-images", type=int, default=100_000,
                     help="dataset size of the resident_epoch workload (smaller for profiler captures)")
     ap.add_argument("--video-only", action="store_true",
                     help="run only the YUV 4:2:0 clip leg and print its JSON (used for profiling that kernel)")
+    ap.add_argument("--identity-only", action="store_true",
+                    help="run only the identity-size gather leg and print its JSON (used for profiling that kernel)")
+    ap.add_argument("--antialias", action="store_true", help="set the descriptor's antialias flag on the workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -602,6 +800,15 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    cores = None
+    all_cores = os.sched_getaffinity(0)
+    if world > 1:
+        # Every rank feeds its GPU from its own block of host cores.
+        try:
+            cores = rank_cores(local_rank, world)
+            os.sched_setaffinity(0, cores)
+        except OSError:
+            cores = None
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     dist = None
@@ -616,47 +823,57 @@ def main():
 
     if not ops.cuda_available():
         raise SystemExit("bench.py: the C-ABI library did not find an sm_100 device (no fallback exists)")
-    if args.video_only:
-        peak, _ = measured_peak_gbs()
-        print(json.dumps(video_leg(torch, device, torch.cuda.current_stream(), peak, steps=max(3, min(args.steps, 30)))))
-        return
     lib = _capi.load()
-    # The timed stream carries nothing but this library's launches, one batch after another, which
-    # is the condition under which consecutive launches may overlap head to tail.
-    ops.set_launch_overlap(True)
     stream = torch.cuda.current_stream()
+    peak, peak_src = measured_peak_gbs()
+    if args.video_only:
+        print(json.dumps(video_leg(torch, device, stream, peak, steps=max(3, min(args.steps, 30)))))
+        return
+    if args.identity_only:
+        print(json.dumps(identity_leg(lib, torch, device, stream, peak, barrier, args.seed)))
+        return
     sampler = ClockSampler(local_rank)
     sampler.start()
 
     # Every rank owns a disjoint shard: its data are generated from a rank-specific seed.
     seed = args.seed + 100_003 * rank
     batches = make_device_batches(args.workload, seed, device, args.sets, args.resident_images)
+    # The timed stream carries nothing but this library's launches, one batch after another, each
+    # into its own output set: the condition under which consecutive launches may overlap.
+    for b in batches:
+        b.set_overlap(True)
+        if args.antialias:
+            b.desc.antialias = 1
     wl = batches[0].wl
     launches0 = ops.launch_count()
     sampler.sample()
-    secs = time_steps(batches, lib, stream, args.steps, args.warmup, torch, barrier)
+    secs_all = time_steps_repeated(batches, lib, stream, args.steps, args.warmup, torch, barrier, repeats=args.repeats)
     sampler.sample()
-    launches = ops.launch_count() - launches0 - args.warmup
+    launches = (ops.launch_count() - launches0 - args.warmup) // max(1, args.repeats)
     for b in batches:
         if int(b.status.item()) != 0:
             raise SystemExit("bench.py: device status word is non-zero")
-    t = torch.tensor([secs], dtype=torch.float64, device=device)
+    t = torch.tensor(secs_all, dtype=torch.float64, device=device)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    secs_max = float(t.item())
+    secs_max_all = [float(v) for v in t.tolist()]
+    secs_max = statistics.median(secs_max_all)
+    secs = statistics.median(secs_all)
     value = world * args.steps * wl.n / secs_max
 
     rd, wr = wl.algorithmic_bytes()
-    peak, peak_src = measured_peak_gbs()
     achieved = (rd + wr) / (secs / args.steps) / 1e9
+    cfg = bench_config(wl, args.seed)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * secs_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32 arithmetic, %s output" % wl.dtype, "data": "synthetic",
-        "config": {"workload": wl.name, "batch_per_gpu": wl.n, "dst": [wl.dst_h, wl.dst_w],
-                   "out": f"{wl.dtype} {'NHWC' if wl.channels_last else 'NCHW'}", "sharding": "disjoint shard per rank, no collective",
-                   "launch_overlap": "on (tlb_set_launch_overlap): back-to-back batches overlap head to tail; the "
-                                     "figure with every launch serialized is under 'serialized'",
+        "config": cfg,
+        "timing": {"repeats": args.repeats, "value_is": "median over repeats of the K-step loop (max over ranks each)",
+                   "img_per_s_min": world * args.steps * wl.n / max(secs_max_all),
+                   "img_per_s_max": world * args.steps * wl.n / min(secs_max_all),
+                   "launch_overlap": "on (TLB_FLAG_LAUNCH_OVERLAP per call): back-to-back batches overlap head to "
+                                     "tail; the figure with every launch serialized is under 'serialized'",
                    "l2": f"per-step traffic {(rd + wr) / 1e6:.0f} MB exceeds the 126 MB L2; {args.sets} distinct "
                          "input/output sets are cycled"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -664,22 +881,72 @@ def main():
                      "algorithmic_bytes_per_launch": rd + wr, "kernel": "fused_transform_kernel"},
         "gpu_launches": int(launches),
     }
+    if cores is not None:
+        line["host_cores_per_rank"] = len(cores)
 
-    if rank == 0 and world == 1 and not args.no_extras:
-        host_sets = [b.wl for b in batches]
-        ops.set_launch_overlap(False)
-        s_ser = time_steps(batches, lib, stream, args.steps, args.warmup, torch, barrier)
-        ops.set_launch_overlap(True)
+    host_sets = None
+    e_steps = max(3, min(args.steps, 20))
+    if not args.no_extras:
+        for b in batches:
+            b.set_overlap(False)
+        s_ser = statistics.median(time_steps_repeated(batches, lib, stream, args.steps, args.warmup, torch, barrier,
+                                                      repeats=max(1, min(args.repeats, 3))))
+        for b in batches:
+            b.set_overlap(True)
         line["serialized"] = {"value": args.steps * wl.n / s_ser, "unit": UNIT,
                               "GB_per_s": (rd + wr) / (s_ser / args.steps) / 1e9,
-                              "frac_of_peak": (rd + wr) / (s_ser / args.steps) / 1e9 / peak}
-        if args.workload in ("variable_rrc", "fixed_resize", "highres_nhwc"):
-            e_steps = max(3, min(args.steps, 20))
+                              "frac_of_peak": (rd + wr) / (s_ser / args.steps) / 1e9 / peak, "per": "rank"}
+    if not args.no_extras and args.workload in ("variable_rrc", "fixed_resize", "highres_nhwc"):
+        host_sets = [b.wl for b in batches]
+        path = ("tlb_crop_resize_normalize_to_device: pinned host pixels -> GPU-side gather of the crop rows over "
+                "PCIe -> fused kernel; status word read back")
+        if world == 1:
             es, h2d, d2h = e2e_steps(host_sets, lib, stream, e_steps, 3, torch, device)
             line["e2e"] = {"value": e_steps * wl.n / es, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                           "d2h_bytes_per_step": d2h, "steps": e_steps,
-                           "path": "tlb_crop_resize_normalize_to_device: pinned host pixels -> GPU-side gather of the crop rows over PCIe -> fused kernel; status word read back"}
-            line["cpu_baseline"] = cpu_baseline(host_sets[0])
+                           "d2h_bytes_per_step": d2h, "steps": e_steps, "h2d_GB_per_s": e_steps * h2d / es / 1e9,
+                           "path": path}
+        else:
+            # Every rank feeds its own GPU from its own pinned host shard: first one rank at a time
+            # (what one host-to-device path can do alone), then all together (what the host can feed).
+            alone = torch.zeros(world, dtype=torch.float64, device=device)
+            for r in range(world):
+                barrier()
+                if r == rank:
+                    es1, h2d, d2h = e2e_steps(host_sets, lib, stream, e_steps, 3, torch, device)
+                    alone[r] = e_steps * h2d / es1 / 1e9
+            dist.all_reduce(alone, op=dist.ReduceOp.SUM)
+            barrier()
+            es, h2d, d2h = e2e_steps(host_sets, lib, stream, e_steps, 3, torch, device)
+            te = torch.tensor([es], dtype=torch.float64, device=device)
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            tog = torch.zeros(world, dtype=torch.float64, device=device)
+            tog[rank] = e_steps * h2d / es / 1e9
+            dist.all_reduce(tog, op=dist.ReduceOp.SUM)
+            line["e2e"] = {"value": world * e_steps * wl.n / float(te.item()), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                           "d2h_bytes_per_step": d2h, "steps": e_steps, "path": path,
+                           "h2d_GB_per_s_per_rank_alone": [round(float(v), 2) for v in alone.tolist()],
+                           "h2d_GB_per_s_per_rank_together": [round(float(v), 2) for v in tog.tolist()],
+                           "host_cores_per_rank": len(cores) if cores else None,
+                           "note": "no collective is involved: the ranks share the host's memory system and PCIe "
+                                   "root ports; compare each rank's rate alone with its rate when all ranks run"}
+        if rank == 0:
+            # The CPU baseline uses every host core (its worker threads are created here, after the
+            # rank's own core block has been lifted), while the other ranks wait.
+            try:
+                os.sched_setaffinity(0, all_cores)
+                line["cpu_baseline"] = cpu_baseline(host_sets[0])
+            finally:
+                if cores is not None:
+                    os.sched_setaffinity(0, cores)
+    # The sharded scaling configuration runs at EVERY world size, 1 included.
+    if not args.no_extras:
+        del batches
+        torch.cuda.empty_cache()
+        line["sharded_scaling"] = sharded_scaling_leg(args, lib, torch, device, stream, rank, world, dist, barrier, peak)
+        torch.cuda.empty_cache()
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        if host_sets is not None:
             try:
                 rg = reference_gpu_leg(host_sets[0], lib, torch, device)
             except Exception as e:  # the comparison leg must never take the bench line down
@@ -692,46 +959,49 @@ def main():
                 line["video_clip"] = {"error": repr(e)}
         others = {}
         for name in WORKLOADS:
-            if name == args.workload:
+            if name in (args.workload, "sharded_scaling"):
                 continue
-            try:
-                del batches
-            except NameError:
-                pass
             torch.cuda.empty_cache()
-            batches = make_device_batches(name, seed, device, 2)
-            s = time_steps(batches, lib, stream, 50, 5, torch, barrier)
-            r, w = batches[0].wl.algorithmic_bytes()
-            ops.set_launch_overlap(False)
-            s1 = time_steps(batches, lib, stream, 50, 5, torch, barrier)
-            ops.set_launch_overlap(True)
-            others[name] = {"img_per_s": 50 * batches[0].wl.n / s, "GB_per_s": (r + w) / (s / 50) / 1e9,
-                            "frac_of_peak": (r + w) / (s / 50) / 1e9 / peak, "batch": batches[0].wl.n,
+            bb = make_device_batches(name, seed, device, 3)
+            for b in bb:
+                b.set_overlap(True)
+            s = statistics.median(time_steps_repeated(bb, lib, stream, 50, 5, torch, barrier, repeats=3))
+            r, w = bb[0].wl.algorithmic_bytes()
+            for b in bb:
+                b.set_overlap(False)
+            s1 = statistics.median(time_steps_repeated(bb, lib, stream, 50, 5, torch, barrier, repeats=3))
+            others[name] = {"img_per_s": 50 * bb[0].wl.n / s, "GB_per_s": (r + w) / (s / 50) / 1e9,
+                            "frac_of_peak": (r + w) / (s / 50) / 1e9 / peak, "batch": bb[0].wl.n,
                             "frac_of_peak_serialized": (r + w) / (s1 / 50) / 1e9 / peak}
+            del bb
         line["other_workloads"] = others
+        try:
+            torch.cuda.empty_cache()
+            line["identity_gather"] = identity_leg(lib, torch, device, stream, peak, barrier, args.seed)
+        except Exception as e:
+            line["identity_gather"] = {"error": repr(e)}
+        try:
+            torch.cuda.empty_cache()
+            line["loader_epoch"] = loader_epoch_leg(args, torch, device, peak, args.resident_images)
+            if "resident_epoch" in others:
+                line["loader_epoch"]["vs_raw_launch_loop"] = line["loader_epoch"]["img_per_s"] / others["resident_epoch"]["img_per_s"]
+        except Exception as e:
+            line["loader_epoch"] = {"error": repr(e)}
         # The opt-in antialiased (triangle filter) resize on the default workload: same inputs, the
         # descriptor's antialias flag set.  Quality path: 3-4x the arithmetic of the bilinear kernel.
         try:
             torch.cuda.empty_cache()
-            batches = make_device_batches(args.workload, seed, device, 2)
-            for b in batches:
+            bb = make_device_batches(args.workload, seed, device, 2)
+            for b in bb:
                 b.desc.antialias = 1
-            s = time_steps(batches, lib, stream, 20, 3, torch, barrier)
-            line["antialias"] = {"workload": args.workload, "img_per_s": 20 * batches[0].wl.n / s,
+            s = time_steps(bb, lib, stream, 20, 3, torch, barrier)
+            r, w = bb[0].wl.algorithmic_bytes()
+            line["antialias"] = {"workload": args.workload, "img_per_s": 20 * bb[0].wl.n / s,
+                                 "GB_per_s": (r + w) / (s / 20) / 1e9, "frac_of_peak": (r + w) / (s / 20) / 1e9 / peak,
                                  "kernel": "antialias_kernel"}
+            del bb
         except Exception as e:
             line["antialias"] = {"error": repr(e)}
-    elif world > 1:
-        # Multi-GPU: e2e at N GPUs = every rank feeding its own GPU from its own pinned host shard.
-        if args.workload in ("variable_rrc", "fixed_resize", "highres_nhwc") and not args.no_extras:
-            host_sets = make_host_workload(args.workload, seed, 1)
-            e_steps = max(3, min(args.steps, 10))
-            barrier()
-            es, h2d, d2h = e2e_steps(host_sets, lib, stream, e_steps, 3, torch, device)
-            te = torch.tensor([es], dtype=torch.float64, device=device)
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-            line["e2e"] = {"value": world * e_steps * wl.n / float(te.item()), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                           "d2h_bytes_per_step": d2h, "steps": e_steps}
     sampler.stop()
     line["clocks"] = sampler.summary()
     if rank == 0:

@@ -99,7 +99,31 @@ typedef struct tlb_transform_desc {
                                /*   src/transforms/simd_utils.hpp:1939-2014)                */
     int32_t max_crop_h;        /* antialias only: upper bound of any crop height; 0 = derive */
                                /*   (uniform box height, else src_h = the tallest image)    */
+
+    /* -- colour jitter (train_transform, src/metal/metal_transforms.mm:83-116) ---------- */
+    const float* jitter;       /* [n][3] per-sample (brightness, contrast, saturation), or   */
+                               /*   NULL.  Applied to rgb = code/255 between the 8-bit code  */
+                               /*   and the normalize, in the shader's order (:111-115):     */
+                               /*   rgb*=b; rgb=(rgb-0.5)*c+0.5; lum=(0.299r+0.587g)+0.114b; */
+                               /*   rgb=lum+(rgb-lum)*s; clamp to [0,1].  Every operation is */
+                               /*   rounded separately.  Needs normalize_01 = 1; bilinear    */
+                               /*   filter only.                                             */
+
+    /* -- launch flags (tlb_fused_transform only; the other entry points ignore them) ---- */
+    uint32_t flags;            /* OR of TLB_FLAG_*                                           */
 } tlb_transform_desc;
+
+/* TLB_FLAG_LAUNCH_OVERLAP: launch with programmatic stream serialization.  When the work directly
+ * before this call in its stream is another fused-transform launch, this one may start while that
+ * one drains its last CTAs, so consecutive batches leave no SM idle between them.  The kernel does
+ * not wait for its predecessor; by setting the flag the caller states that a KERNEL placed directly
+ * before this call in the same stream neither writes this call's inputs (pixels, tables) nor reads
+ * or writes its outputs.  Copies, memsets and event waits always keep full stream order.  A stream
+ * that carries only this library's launches, each into its own output buffer -- a loader's prefetch
+ * stream handing batches over by events -- meets the condition.  The choice is per call: a launch
+ * without the flag is never affected by other callers' launches.  No counterpart in the reference
+ * (its loaders synchronise after every batch). */
+#define TLB_FLAG_LAUNCH_OVERLAP 1u
 
 /* ---- capability ----------------------------------------------------------------------
  * Replace turboloader::cuda::available / device_name
@@ -116,7 +140,7 @@ TLB_API const char* tlb_last_error(void);
  *   turboloader::cuda::crop_resize_normalize_batch     (cuda_transforms.hpp:117-119, .cu:316-347)
  *   turboloader::cuda::normalize_resident_batch        (cuda_transforms.hpp:49-50,  .cu:475-507)
  *   turboloader::cuda::normalize_resident_gather_batch (cuda_transforms.hpp:54-55,  .cu:511-544)
- *   turboloader::cuda::resize_normalize_device_batch   (cuda_transforms.hpp:141-144, .cu:1008-1046)
+ * (resize_normalize_device_batch has its own entry point below: its images are separate allocations)
  * with ONE launch per batch on `stream` (a cudaStream_t passed as void*; NULL =
  * the legacy default stream), on the current device, with no synchronisation and
  * no allocation.  Parameters that live on the device cannot be checked by the
@@ -182,9 +206,10 @@ TLB_API int tlb_crop_resize_normalize_to_device(const tlb_image_ref* imgs, const
  * opts the kernels in to large shared memory; make that first call outside any stream capture.
  * Every call on a device uses the same array: it keeps the previous call's bytes (nothing in it
  * needs to start at zero -- each call overwrites what it reads), and two calls whose GPU work
- * overlaps (different streams, or concurrent host threads) race on it.  Issue the calls of one
- * device on one stream, one host thread at a time.  The tables are built in a fixed host buffer
- * of the library, which is a second reason for that rule.  Same arguments and results as
+ * overlaps (different streams, or concurrent host threads on one device) race on it.  Issue the
+ * calls of one device on one stream, one host thread at a time.  The per-sample tables are built in
+ * one fixed host buffer of the library; a lock serialises that step across all host threads, so
+ * threads that drive different GPUs may call concurrently.  Same arguments and results as
  * tlb_crop_resize_normalize_to_device. */
 #define TLB_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
 #define TLB_STATIC_MAX_SAMPLES 4096
@@ -205,6 +230,17 @@ TLB_API uintptr_t tlb_normalize_resident_batch(uintptr_t src_dev, int32_t n, int
 TLB_API uintptr_t tlb_normalize_resident_gather_batch(uintptr_t src_dev, uintptr_t sel_dev, int32_t n,
                                                       int32_t h, int32_t w, const float mean[3],
                                                       const float std_[3]);
+
+/* resize_normalize_device_batch (cuda_transforms.hpp:141-144, .cu:1008-1046): n ALREADY-DECODED
+ * images given as device addresses d_imgs[i] of tightly packed ws[i] x hs[i] x 3 uint8 pixels, each
+ * in its own device allocation (e.g. the outputs of an external GPU decoder), read in place ->
+ * device address of the [n,3,dst_h,dst_w] fp32 batch in the same 4-deep ring (valid until the
+ * 4th-next call of a pointer-returning form), or 0 on error.  Synchronises its stream before
+ * returning, as the function it replaces does.  One launch for the whole list; every image is
+ * checked against the allocation that holds it and no load leaves an image. */
+TLB_API uintptr_t tlb_resize_normalize_device_batch(const uintptr_t* d_imgs, const int32_t* ws, const int32_t* hs,
+                                                    int32_t n, int32_t dst_h, int32_t dst_w, const float mean[3],
+                                                    const float std_[3]);
 
 /* ---- YUV 4:2:0 video frames ----------------------------------------------------------------
  * Replaces turboloader::cuda::video_yuv420_batch and video_clip_yuv420
@@ -280,20 +316,32 @@ TLB_API int tlb_stream_next(tlb_stream_core* core, uintptr_t* out_dev, int32_t* 
 /* Drains the slots and returns the OR of the device status bits seen so far. */
 TLB_API int tlb_stream_status(tlb_stream_core* core, uint32_t* out_status);
 
-/* ---- back-to-back launches ----------------------------------------------------------------
- * No counterpart in the reference (its loaders synchronise after every batch).
- * With enable != 0 every later tlb_fused_transform launch is made with programmatic stream
- * serialization: when the work directly before it in its stream is another tlb_fused_transform
- * launch, it may start while that launch drains its last CTAs, so consecutive batches leave no
- * SM idle between them (the other entry points are unaffected: they stage their inputs in the
- * stream themselves and keep full stream order).  The kernel does not wait for its predecessor,
- * hence the condition the caller accepts by enabling this: a KERNEL placed directly before a
- * tlb_fused_transform call in the same stream must neither write that call's inputs nor read or
- * write its outputs (copies, memsets and event waits always keep full stream order, and two
- * batches of this library never depend on one another).  A stream that carries only this
- * library's calls -- a loader's own prefetch stream handing batches over by events -- meets it.
- * Off by default; process-wide; returns the previous setting. */
-TLB_API int tlb_set_launch_overlap(int enable);
+/* ---- resident epochs: one call per batch, no per-batch set-up on the host --------------------
+ * The batch loop of the resident loader (turboloader/cuda_loader.py:512-535: one
+ * normalize_resident(_gather)_batch call and one synchronisation per batch) as a pipeline: the
+ * library owns a prefetch stream and a ring of `ring` output slots in caller-allocated memory, keeps
+ * up to `ahead` batches enqueued beyond the one being handed out, and hands a batch over by making
+ * the consumer's stream wait for it -- the host never blocks.  Launches are enqueued `group` at a
+ * time, back to back, with TLB_FLAG_LAUNCH_OVERLAP (the prefetch stream carries nothing else, and
+ * consecutive launches write different slots, so the flag's condition holds by construction).
+ *
+ * `first` describes batch 0 of the epoch exactly as tlb_fused_transform would take it: n = the
+ * batch size; sel / boxes / flips / jitter (if given) point at epoch position 0 of tables that
+ * cover the whole epoch; out / out_indices / labels_out point at slot 0.  Batch b reads the tables
+ * at position b * n and writes slot b % ring (slots are out_slot_bytes, index_slot_bytes and
+ * label_slot_bytes apart).  With sel == NULL the dataset is read in order: batch b starts at image
+ * b * n of `first->src` (uniform layout only).  The last batch is short unless drop_last.
+ * A batch stays valid until `ring - ahead - group` further tlb_epoch_next calls have been made. */
+typedef struct tlb_epoch tlb_epoch;
+TLB_API tlb_epoch* tlb_epoch_create(const tlb_transform_desc* first, int64_t total, int32_t drop_last,
+                                    int64_t start_batch, int32_t ring, int32_t ahead, int32_t group,
+                                    int64_t out_slot_bytes, int64_t index_slot_bytes,
+                                    int64_t label_slot_bytes);       /* NULL on error */
+/* Next batch: *batch = its number in the epoch, *n = its samples (0: epoch finished), *slot = the
+ * ring slot that holds it.  consumer_stream (a cudaStream_t as void*, NULL = legacy default stream)
+ * is made to wait for the batch; slots are refilled only behind the work already enqueued on it. */
+TLB_API int tlb_epoch_next(tlb_epoch* e, int64_t* batch, int32_t* n, int32_t* slot, void* consumer_stream);
+TLB_API void tlb_epoch_destroy(tlb_epoch* e);
 
 /* ---- introspection ---------------------------------------------------------------------
  * Launch geometry the fused kernel would use for `desc` (for tests and the

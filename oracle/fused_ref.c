@@ -23,6 +23,10 @@
  *   src/pipeline/direct_batch_loader.hpp:55-59    inv_std = 1.0f / std
  *   src/python/turboloader_bindings.cpp:1198-1258 normalize_u8_gather (index gather)
  *   src/transforms/simd_utils.hpp:1939-2014  resize_triangle_antialias (opt-in quality resize)
+ *   src/metal/metal_transforms.mm:111-115    colour jitter of the train_transform shader
+ *       (PARITY UNPINNED for this one step: its only reference implementation is a Metal
+ *       shader, which cannot be executed here; the restatement applies the shader's five
+ *       lines to the CPU path's 8-bit code, each operation rounded separately)
  */
 #include <math.h>
 #include <stdint.h>
@@ -190,6 +194,36 @@ TLO_API void tlo_resize_antialias_u8(const uint8_t* src, uint8_t* dst, int sw, i
 }
 
 static int g_antialias = 0; /* set per call by tlo_fused_batch_aa; the oracle is single-threaded */
+static const float* g_jitter = NULL; /* (brightness, contrast, saturation) of the current sample, or NULL */
+
+/*
+ * u8 HWC -> colour jitter -> f32 planes.  The jitter is the train_transform shader's
+ * (src/metal/metal_transforms.mm:111-115), applied to rgb = u8 * (1/255):
+ *   rgb *= brightness;  rgb = (rgb - 0.5)*contrast + 0.5;
+ *   lum = dot(rgb, (0.299, 0.587, 0.114));  rgb = mix(lum, rgb, saturation);  clamp to [0,1]
+ * with dot() summed left to right and mix(x, y, a) = x + (y - x)*a; every multiply, add and
+ * subtract rounds to fp32 on its own (the file is compiled without contraction).
+ */
+static void tlo_jitter_normalize_hwc_to_chw(const uint8_t* src, float* dst, size_t npix, const float* jit,
+                                            const float* mean, const float* inv_std) {
+    const float s = 1.0f / 255.0f;
+    for (size_t i = 0; i < npix; ++i) {
+        float rgb[3];
+        for (int c = 0; c < 3; ++c) {
+            float v = (float)src[i * 3 + c] * s;
+            v = v * jit[0];
+            v = (v - 0.5f) * jit[1] + 0.5f;
+            rgb[c] = v;
+        }
+        const float lum = (rgb[0] * 0.299f + rgb[1] * 0.587f) + rgb[2] * 0.114f;
+        for (int c = 0; c < 3; ++c) {
+            float v = lum + (rgb[c] - lum) * jit[2];
+            v = v < 0.0f ? 0.0f : v;
+            v = v > 1.0f ? 1.0f : v;
+            dst[(size_t)c * npix + i] = (v - mean[c]) * inv_std[c];
+        }
+    }
+}
 
 static void tlo_one_sample(const uint8_t* img, int iw, int ih, int cx, int cy, int cw, int ch,
                            int flip, int dw, int dh, int normalize_01, const float* mean,
@@ -217,7 +251,10 @@ static void tlo_one_sample(const uint8_t* img, int iw, int ih, int cx, int cy, i
                 }
         }
     }
-    tlo_normalize_hwc_to_chw(resized, out_chw, (size_t)dw * dh, normalize_01, mean, inv_std);
+    if (g_jitter)
+        tlo_jitter_normalize_hwc_to_chw(resized, out_chw, (size_t)dw * dh, g_jitter, mean, inv_std);
+    else
+        tlo_normalize_hwc_to_chw(resized, out_chw, (size_t)dw * dh, normalize_01, mean, inv_std);
 }
 
 /*
@@ -269,6 +306,24 @@ TLO_API int tlo_fused_batch_aa(const uint8_t* src, const int64_t* offsets, const
                                    normalize_01, out);
     g_antialias = 0;
     return rc;
+}
+
+/* Same as tlo_fused_batch with per-sample colour jitter: jitter = n x (brightness, contrast,
+ * saturation).  mean/std are in [0,1] units (normalize_01 is implied). */
+TLO_API int tlo_fused_batch_jitter(const uint8_t* src, const int64_t* offsets, const int32_t* sizes,
+                                   int64_t n_src, const int64_t* sel, const int32_t* boxes,
+                                   const uint8_t* flips, int n, int dh, int dw, const float* mean,
+                                   const float* std_, const float* jitter, float* out) {
+    for (int i = 0; i < n; ++i) {
+        g_jitter = jitter + 3 * (size_t)i;
+        const int64_t one_sel = sel ? sel[i] : i;
+        const int rc = tlo_fused_batch(src, offsets, sizes, n_src, &one_sel, boxes ? boxes + 4 * (size_t)i : NULL,
+                                       flips ? flips + i : NULL, 1, dh, dw, mean, std_, 1,
+                                       out + (size_t)i * 3 * dh * dw);
+        g_jitter = NULL;
+        if (rc) return -(i + 1);
+    }
+    return 0;
 }
 
 /* NCHW f32 -> NHWC f32 (same values, permuted). */

@@ -21,6 +21,8 @@ import subprocess
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+# The reference tree: $TLB_REFERENCE_ROOT, else a checkout named "reference" beside this repository.
+REF_ROOT = os.environ.get("TLB_REFERENCE_ROOT") or os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
 PORT_SO = os.path.join(HERE, "libtl_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 
@@ -40,7 +42,7 @@ def build_port(force: bool = False) -> str:
     return PORT_SO
 
 
-def build_ref(ref_root: str = "/root/reference") -> bool:
+def build_ref(ref_root: str = REF_ROOT) -> bool:
     """Compile the reference headers in place; returns False when the tree is absent."""
     if not os.path.isdir(os.path.join(ref_root, "src", "transforms")):
         return False
@@ -79,6 +81,9 @@ def _load(impl: str) -> C.CDLL:
                                         C.c_int, C.c_int, _f32p, _f32p, C.c_int, _f32p]
         lib.tlo_fused_batch_aa.restype = C.c_int
         lib.tlo_fused_batch_aa.argtypes = lib.tlo_fused_batch.argtypes + [C.c_int]
+        lib.tlo_fused_batch_jitter.restype = C.c_int
+        lib.tlo_fused_batch_jitter.argtypes = [_u8p, _i64p, _i32p, C.c_int64, _i64p, _i32p, _u8p, C.c_int,
+                                               C.c_int, C.c_int, _f32p, _f32p, _f32p, _f32p]
         lib.tlo_resize_bilinear_u8.restype = None
         lib.tlo_resize_bilinear_u8.argtypes = [_u8p, _u8p, C.c_int, C.c_int, C.c_int, C.c_int]
         lib.tlo_f32_to_bf16_array.restype = None
@@ -106,9 +111,6 @@ def _load(impl: str) -> C.CDLL:
         lib.tlref_sampler_indices.restype = C.c_int64
         lib.tlref_sampler_indices.argtypes = [C.c_int64, C.c_int, C.c_int, C.c_int, C.c_uint64,
                                               C.c_uint64, C.c_int, _i64p, C.c_int64]
-        lib.tlref_direct_order.restype = C.c_int64
-        lib.tlref_direct_order.argtypes = [C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-                                           C.c_int, _i64p, C.c_int64]
     _libs[impl] = lib
     return lib
 
@@ -118,12 +120,14 @@ def _ptr(a, ty):
 
 
 def fused_batch(src, offsets, sizes, sel, boxes, flips, dst_h, dst_w, mean, std, normalize_01=True,
-                impl="port", threads=1, out=None, antialias=False):
+                impl="port", threads=1, out=None, antialias=False, jitter=None):
     """fp32 NCHW result of crop -> bilinear(u8, truncating) -> flip -> normalize.
 
     ``src`` packed uint8, ``offsets`` int64[n_src], ``sizes`` int32[n_src,2] as (w,h),
     ``sel`` int64[n] or None, ``boxes`` int32[n,4] (x,y,w,h) or None, ``flips`` uint8[n] or None.
-    Raises IndexError naming the first invalid sample.
+    ``jitter`` float32[n,3] (brightness, contrast, saturation) applies the colour jitter of the
+    reference's train_transform shader between the 8-bit code and the normalize (C restatement
+    only; needs ``normalize_01``).  Raises IndexError naming the first invalid sample.
     """
     src = np.ascontiguousarray(src, dtype=np.uint8).reshape(-1)
     offsets = np.ascontiguousarray(offsets, dtype=np.int64)
@@ -141,7 +145,12 @@ def fused_batch(src, offsets, sizes, sel, boxes, flips, dst_h, dst_w, mean, std,
     args = [_ptr(src, _u8p), _ptr(offsets, _i64p), _ptr(sizes, _i32p), n_src, _ptr(sel, _i64p),
             _ptr(boxes, _i32p), _ptr(flips, _u8p), n, dst_h, dst_w, _ptr(mean, _f32p),
             _ptr(std, _f32p), int(bool(normalize_01)), _ptr(out, _f32p)]
-    if antialias:
+    if jitter is not None:
+        if impl != "port" or antialias or not normalize_01:
+            raise ValueError("jitter: C restatement only, bilinear filter, normalize_01")
+        jitter = np.ascontiguousarray(jitter, dtype=np.float32).reshape(n, 3)
+        rc = lib.tlo_fused_batch_jitter(*args[:12], _ptr(jitter, _f32p), _ptr(out, _f32p))
+    elif antialias:
         rc = (lib.tlo_fused_batch_aa(*args, 1) if impl == "port"
               else lib.tlref_fused_batch_aa(*args, int(threads), 1))
     else:
@@ -208,11 +217,131 @@ def ref_sampler_indices(total, world, rank, shuffle, seed, epoch, drop_last):
 
 
 def ref_direct_order(total, shuffle, seed, epoch, distributed, rank, world):
-    lib = _load("ref-parity")
-    out = np.empty(max(int(total), 1), dtype=np.int64)
-    k = lib.tlref_direct_order(int(total), int(shuffle), int(seed), int(epoch), int(distributed),
-                               int(rank), int(world), _ptr(out, _i64p), out.size)
-    return out[:k].copy()
+    """Epoch order from DirectBatchCore::build_order, by running the compiled class over `total`
+    one-pixel samples."""
+    imgs = [np.zeros((1, 1, 3), np.uint8)] * int(total)
+    core = RefDirectBatchCore(imgs, 1, 1, 1, shuffle=bool(shuffle), seed=int(seed), distributed=bool(distributed),
+                              world_rank=int(rank), world_size=int(world))
+    core.begin_epoch(int(epoch))
+    return core.order()
+
+
+# ---- the reference's DirectBatchCore itself (oracle/_ref/libtl_ref_dbc.so) ---------------------
+
+REF_DBC_SO = os.path.join(REF_DIR, "libtl_ref_dbc.so")
+
+
+def build_ref_dbc(ref_root: str = REF_ROOT) -> bool:
+    if not os.path.isfile(os.path.join(ref_root, "src", "pipeline", "direct_batch_loader.hpp")):
+        return False
+    subprocess.check_call(["make", "-C", HERE, "refdbc", f"REF={ref_root}"], stdout=subprocess.DEVNULL)
+    return True
+
+
+def ref_dbc():
+    """ctypes handle of the compiled DirectBatchCore harness, or None when it was not built."""
+    if "dbc" not in _libs:
+        if not os.path.exists(REF_DBC_SO) or "avx2" not in _cpu_flags():
+            return None
+        lib = C.CDLL(REF_DBC_SO)
+        lib.tlref_dbc_create.restype = C.c_void_p
+        lib.tlref_dbc_create.argtypes = [_u8p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _f32p, _f32p,
+                                         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                         C.c_float]
+        lib.tlref_dbc_destroy.restype = None
+        lib.tlref_dbc_destroy.argtypes = [C.c_void_p]
+        lib.tlref_dbc_num_samples.restype = C.c_int64
+        lib.tlref_dbc_num_samples.argtypes = [C.c_void_p]
+        lib.tlref_dbc_begin_epoch.restype = None
+        lib.tlref_dbc_begin_epoch.argtypes = [C.c_void_p, C.c_int, C.c_int64]
+        lib.tlref_dbc_next.restype = C.c_int
+        lib.tlref_dbc_next.argtypes = [C.c_void_p, _i64p, _f32p]
+        lib.tlref_dbc_order.restype = C.c_int64
+        lib.tlref_dbc_order.argtypes = [C.c_void_p, _i64p, C.c_int64]
+        lib.tlref_dbc_pick_crops.restype = None
+        lib.tlref_dbc_pick_crops.argtypes = [C.c_void_p, _i32p, _i64p, C.c_int64, _i32p]
+        lib.tlref_dbc_decode_failures.restype = C.c_int64
+        lib.tlref_dbc_decode_failures.argtypes = [C.c_void_p]
+        _libs["dbc"] = lib
+    return _libs["dbc"]
+
+
+def raw8_tar(images) -> np.ndarray:
+    """An in-memory ustar archive with one "RAW8" sample (header + HWC RGB pixels, the container the
+    stand-in decoder of the DirectBatchCore harness reads) per image, named 000000.jpg, 000001.jpg ..."""
+    import io
+    import tarfile
+
+    buf = io.BytesIO()
+    with tarfile.open(fileobj=buf, mode="w", format=tarfile.USTAR_FORMAT) as tf:
+        for i, im in enumerate(images):
+            im = np.ascontiguousarray(im, dtype=np.uint8)
+            h, w = im.shape[:2]
+            payload = b"RAW8" + np.array([w, h], dtype="<i4").tobytes() + im.tobytes()
+            info = tarfile.TarInfo(f"{i:06d}.jpg")
+            info.size = len(payload)
+            tf.addfile(info, io.BytesIO(payload))
+    return np.frombuffer(buf.getvalue(), dtype=np.uint8).copy()
+
+
+class RefDirectBatchCore:
+    """The reference's DirectBatchCore (unmodified, compiled in place) over an in-memory archive of
+    pre-decoded images.  Same constructor arguments as the C++ class
+    (src/pipeline/direct_batch_loader.hpp:34-41)."""
+
+    def __init__(self, images, batch_size, target_h, target_w, *, chw=True, normalize_01=True, mean=None, std=None,
+                 shuffle=False, seed=0, distributed=False, world_rank=0, world_size=1, drop_last=False,
+                 antialias=False, train_aug=False, hflip_prob=0.5):
+        self._lib = ref_dbc()
+        if self._lib is None:
+            raise FileNotFoundError("the DirectBatchCore harness (oracle/_ref/libtl_ref_dbc.so) is not built")
+        tar = raw8_tar(images)
+        m = None if mean is None else np.asarray(mean, np.float32)
+        s = None if std is None else np.asarray(std, np.float32)
+        self._h = self._lib.tlref_dbc_create(_ptr(tar, _u8p), tar.size, int(batch_size), int(target_h), int(target_w),
+                                             int(chw), int(normalize_01), _ptr(m, _f32p), _ptr(s, _f32p), int(shuffle),
+                                             int(seed), int(distributed), int(world_rank), int(world_size),
+                                             int(drop_last), int(antialias), int(train_aug), float(hflip_prob))
+        if not self._h:
+            raise RuntimeError("DirectBatchCore constructor failed")
+        self.batch_size, self.h, self.w, self.chw = int(batch_size), int(target_h), int(target_w), bool(chw)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.tlref_dbc_destroy(self._h)
+            self._h = None
+
+    def num_samples(self):
+        return int(self._lib.tlref_dbc_num_samples(self._h))
+
+    def begin_epoch(self, epoch, start_batch=0):
+        self._lib.tlref_dbc_begin_epoch(self._h, int(epoch), int(start_batch))
+
+    def order(self):
+        out = np.empty(1 << 20, np.int64)
+        k = self._lib.tlref_dbc_order(self._h, _ptr(out, _i64p), out.size)
+        return out[:k].copy()
+
+    def next(self):
+        """(indices int64[bs], float32 batch) or None at the end of the epoch."""
+        idx = np.empty(self.batch_size, np.int64)
+        shape = (self.batch_size, 3, self.h, self.w) if self.chw else (self.batch_size, self.h, self.w, 3)
+        out = np.empty(shape, np.float32)
+        bs = self._lib.tlref_dbc_next(self._h, _ptr(idx, _i64p), _ptr(out, _f32p))
+        if bs == 0:
+            return None
+        return idx[:bs].copy(), out[:bs].copy()
+
+    def pick_crops(self, sizes_wh, indices):
+        """int32[n,5] (x, y, w, h, flip) from DirectBatchCore::pick_crop for the current epoch."""
+        sizes = np.ascontiguousarray(sizes_wh, np.int32).reshape(-1, 2)
+        idx = np.ascontiguousarray(indices, np.int64)
+        out = np.empty((len(idx), 5), np.int32)
+        self._lib.tlref_dbc_pick_crops(self._h, _ptr(sizes, _i32p), _ptr(idx, _i64p), len(idx), _ptr(out, _i32p))
+        return out
+
+    def decode_failures(self):
+        return int(self._lib.tlref_dbc_decode_failures(self._h))
 
 
 # ---- the reference's own CUDA kernels, compiled in place (oracle/_ref/libtl_ref_cuda.so) ---------
@@ -222,7 +351,7 @@ REF_CUDA_NOFMA_SO = os.path.join(REF_DIR, "libtl_ref_cuda_nofma.so")  # same sou
 _ref_cuda = {}
 
 
-def build_ref_cuda(ref_root: str = "/root/reference") -> bool:
+def build_ref_cuda(ref_root: str = REF_ROOT) -> bool:
     if not os.path.isfile(os.path.join(ref_root, "src", "cuda", "cuda_transforms.cu")):
         return False
     subprocess.check_call(["make", "-C", HERE, "refcuda", f"REF={ref_root}"], stdout=subprocess.DEVNULL)

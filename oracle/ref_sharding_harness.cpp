@@ -2,12 +2,8 @@
 // (src/distributed/sharding_strategies.hpp, src/distributed/distributed_dataloader.hpp),
 // compiled in place from the reference tree, through a C interface so the tests can
 // compare the package's own index math with them and so tests/golden/ can be generated.
-// DirectBatchCore::build_order (src/pipeline/direct_batch_loader.hpp:116-135) lives in a
-// header that needs libjpeg and cannot be built here; its rule is replayed below with
-// the same standard-library calls (iota, mt19937_64(seed+epoch), std::shuffle, rank block).
+// (DirectBatchCore::build_order is exposed by ref_dbc_harness.cpp, which runs that class itself.)
 #include <cstdint>
-#include <numeric>
-#include <random>
 #include <vector>
 
 #include "src/distributed/distributed_dataloader.hpp"
@@ -46,22 +42,4 @@ API int64_t tlref_sampler_indices(int64_t total, int world, int rank, int shuffl
     } catch (...) {
         return -1;
     }
-}
-
-API int64_t tlref_direct_order(int64_t total, int shuffle, int seed, int epoch, int distributed,
-                               int rank, int world, int64_t* out, int64_t cap) {
-    std::vector<size_t> all((size_t)total);
-    std::iota(all.begin(), all.end(), 0);
-    if (shuffle) {
-        std::mt19937_64 rng(static_cast<uint64_t>(seed) + static_cast<uint64_t>(epoch));
-        std::shuffle(all.begin(), all.end(), rng);
-    }
-    size_t s = 0, e = all.size();
-    if (distributed && world > 1) {
-        size_t per = (size_t)total / (size_t)world;
-        s = (size_t)rank * per;
-        e = s + per;
-    }
-    for (size_t i = s; i < e && (int64_t)(i - s) < cap; ++i) out[i - s] = (int64_t)all[i];
-    return (int64_t)(e - s);
 }

@@ -60,16 +60,21 @@ def _desc(**kw):
 
 def test_plan_is_computed_without_a_gpu():
     plan = ops.fused_plan(_desc(dst_h=224, dst_w=224, src_w=256, src_h=256, n=256, n_src=256))
-    assert plan["block"] == 224 + 32 and plan["tile_cols"] == 224 and plan["smem_bytes"] <= 227 * 1024
+    # Two columns per lane (c and c + 32 of a 64-column strip), one planner warp on top.
+    assert plan["tile_cols"] == 256 and plan["block"] == 32 * (4 + 1) and plan["smem_bytes"] <= 227 * 1024
     assert plan["grid"] == 256 * -(-224 // plan["tile_rows"])
-    wide = ops.fused_plan(_desc(dst_h=8, dst_w=600, src_w=700, src_h=60))
-    assert wide["tile_cols"] <= 256 and wide["tile_cols"] % 16 == 0
+    narrow = ops.fused_plan(_desc(dst_h=24, dst_w=24, src_w=256, src_h=256, n=256, n_src=256))
+    assert narrow["tile_cols"] == 32 and narrow["block"] == 32 * (1 + 1)  # one column per lane
+    wide = ops.fused_plan(_desc(dst_h=8, dst_w=1200, src_w=1400, src_h=60))
+    assert wide["tile_cols"] <= 512 and wide["tile_cols"] % 32 == 0 and wide["block"] <= 288
+    assert wide["grid"] == 4 * -(-1200 // wide["tile_cols"])
 
 
 @pytest.mark.parametrize("kw,code", [
     (dict(dst_h=0), 1), (dict(out_dtype=7), 1), (dict(out_layout=3), 1), (dict(src=None), 1), (dict(n_src=0), 1),
     (dict(std=_capi.f3((1, 0, 1))), 1), (dict(n=9), 3), (dict(uniform_box=(C.c_int32 * 4)(30, 0, 8, 8)), 2),
-    (dict(src_w=0, src_h=0), 1),
+    (dict(src_w=0, src_h=0), 1), (dict(flags=2), 1), (dict(jitter=0x3000, normalize_01=0), 1),
+    (dict(jitter=0x3000, normalize_01=1, antialias=1), 1),
 ])
 def test_invalid_descriptors_are_rejected_on_the_host(kw, code):
     lib = _capi.load()

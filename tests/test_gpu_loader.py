@@ -310,3 +310,54 @@ def test_against_the_reference_gpu_kernels():
     d = np.abs(ours.astype(np.float64) - ref)
     # 1.001: the two coordinate formulas round differently, which moves a blend by ~2e-4 of a code
     assert (d <= step * 1.001).all() and d.mean() > 1e-4  # truncation really differs, by < 1 code
+
+
+def test_device_images_in_separate_allocations():
+    """cuda_resize_normalize_from_device (resize_normalize_device_batch, cuda_transforms.hpp:141-144):
+    every image lives in its own device allocation, sizes are ragged and odd so that rows and image
+    ends sit off the 16-byte grid; the result is the oracle's, the ring is shared with the other
+    pointer-returning forms, and an image that does not fit its allocation is refused."""
+    import torch
+    rs = np.random.RandomState(21)
+    shapes = [(50, 70), (33, 21), (64, 64), (9, 201), (17, 5), (1, 1), (120, 37)]
+    images = [rs.randint(0, 256, size=(h, w, 3), dtype=np.uint8) for h, w in shapes]
+    # One device buffer per image (small blocks of torch's allocator, spread apart by 2 MiB fillers),
+    # passed in an order that is not the address order.
+    devs = [torch.empty(im.size + 0, dtype=torch.uint8, device="cuda") for im in images]
+    pad = [torch.empty(1 << 21, dtype=torch.uint8, device="cuda") for _ in images]  # spread the blocks apart
+    for d, im in zip(devs, images):
+        d.copy_(torch.from_numpy(im.reshape(-1)))
+    order = [3, 0, 6, 1, 5, 2, 4]  # not in address order
+    ptrs = [devs[i].data_ptr() for i in order]
+    ws = [shapes[i][1] for i in order]
+    hs = [shapes[i][0] for i in order]
+    flat, offsets, sizes = S.pack_images([images[i] for i in order])
+    want = O.fused_batch(flat, offsets, sizes, None, None, None, 40, 56, MEAN, STD, True)
+    out = t.cuda_resize_normalize_from_device(ptrs, ws, hs, 40, 56)
+    got = torch.as_tensor(t._CudaArray(out, (len(order), 3, 40, 56)), device="cuda").cpu().numpy()
+    assert np.array_equal(got, want)
+    out2 = t.cuda_resize_normalize_from_device(ptrs[:2], ws[:2], hs[:2], 40, 56)
+    assert out2 != out
+    with pytest.raises(RuntimeError):
+        t.cuda_resize_normalize_from_device(ptrs, ws, hs[:-1], 40, 56)
+    with pytest.raises(RuntimeError):
+        t.cuda_resize_normalize_from_device([0], [4], [4], 8, 8)
+    # an image claimed larger than the allocation that holds it
+    whole = torch.empty(1 << 22, dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError):
+        t.cuda_resize_normalize_from_device([whole.data_ptr()], [4096], [4096], 8, 8)
+    del pad
+
+
+def test_resident_gather_is_bounded_by_the_allocation():
+    """The legacy gather form does not say how many images the dataset holds; the bound is the end
+    of the device allocation, so an index far beyond it is not read (the sample is zero-filled)."""
+    import torch
+    data = _dataset(16, 24)
+    gpu = torch.empty(1 << 22, dtype=torch.uint8, device="cuda")  # a whole 4 MiB block of its own
+    gpu[:data.size] = torch.from_numpy(data.reshape(-1)).cuda()
+    sel = torch.from_numpy(np.array([3, 1 << 34, 7], dtype=np.int64)).cuda()
+    ptr = t.cuda_normalize_resident_gather(gpu.data_ptr(), sel.data_ptr(), 3, 24, 24)
+    got = torch.as_tensor(t._CudaArray(ptr, (3, 3, 24, 24)), device="cuda").cpu().numpy()
+    want = _oracle_uniform(data, sel=np.array([3, 7], np.int64))
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[2], want[1]) and (got[1] == 0).all()

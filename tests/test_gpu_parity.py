@@ -130,28 +130,57 @@ def test_invalid_samples_are_zero_filled_and_reported():
 
 
 def test_back_to_back_launches_may_overlap():
-    """tlb_set_launch_overlap: consecutive launches into distinct outputs give the same bits as
-    serialized launches; the switch reports its previous setting and defaults to off."""
+    """TLB_FLAG_LAUNCH_OVERLAP (per call): consecutive flagged launches into distinct outputs give
+    the same bits as plain launches."""
     import torch
 
     import turboloader_b200 as t
-    assert t.set_launch_overlap(True) is False
-    try:
-        wl = S.config2(n=24, seed=5, lo=60, hi=140, dst=64)
-        want = expected(wl)
-        flat = torch.from_numpy(wl.src).cuda()
-        offs = torch.from_numpy(wl.offsets).cuda()
-        sizes = torch.from_numpy(np.ascontiguousarray(wl.sizes)).cuda()
-        boxes = torch.from_numpy(np.ascontiguousarray(wl.boxes)).cuda()
-        flips = torch.from_numpy(wl.flips).cuda()
-        outs = [torch.full((wl.n, 3, 64, 64), -7.0, device="cuda") for _ in range(8)]
-        status = torch.zeros(1, dtype=torch.int32, device="cuda")
-        for o in outs:
-            t.fused_transform(flat, n=wl.n, dst_h=64, dst_w=64, out=o, src_offsets=offs, src_sizes=sizes, boxes=boxes,
-                              flips=flips, mean=wl.mean, std=wl.std, max_crop_w=int(wl.boxes[:, 2].max()), status=status)
+    wl = S.config2(n=24, seed=5, lo=60, hi=140, dst=64)
+    want = expected(wl)
+    flat = torch.from_numpy(wl.src).cuda()
+    offs = torch.from_numpy(wl.offsets).cuda()
+    sizes = torch.from_numpy(np.ascontiguousarray(wl.sizes)).cuda()
+    boxes = torch.from_numpy(np.ascontiguousarray(wl.boxes)).cuda()
+    flips = torch.from_numpy(wl.flips).cuda()
+    outs = [torch.full((wl.n, 3, 64, 64), -7.0, device="cuda") for _ in range(8)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for o in outs:
+        t.fused_transform(flat, n=wl.n, dst_h=64, dst_w=64, out=o, src_offsets=offs, src_sizes=sizes, boxes=boxes,
+                          flips=flips, mean=wl.mean, std=wl.std, max_crop_w=int(wl.boxes[:, 2].max()), status=status,
+                          launch_overlap=True)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for o in outs:
+        assert np.array_equal(o.cpu().numpy(), want)
+
+
+def test_unflagged_launch_keeps_stream_order_behind_a_producer_kernel():
+    """A launch WITHOUT the overlap flag must see what a kernel directly before it in the same
+    stream wrote -- here the gather indices and the flip flags -- even when other launches in the
+    process use the flag.  (The flag is per call; it must never change an unflagged launch.)"""
+    import torch
+
+    import turboloader_b200 as t
+    wl = S.config3(seed=11, n_dataset=64, batch=32, batch_index=0)
+    data = torch.from_numpy(wl.src).cuda()
+    boxes = torch.from_numpy(np.ascontiguousarray(wl.boxes)).cuda()
+    sel_final = torch.from_numpy(wl.sel).cuda()
+    flips_final = torch.from_numpy(wl.flips).cuda()
+    h, w = wl.uniform_hw
+    want = expected(wl)
+    for rep in range(6):
+        sel = torch.zeros_like(sel_final)
+        flips = torch.zeros_like(flips_final)
+        out = torch.empty((wl.n, 3, wl.dst_h, wl.dst_w), dtype=torch.bfloat16, device="cuda")
+        warm = torch.empty_like(out)
+        # A flagged launch first, so that the stream's previous kernel is one that signals early.
+        t.fused_transform(data, n=wl.n, n_src=wl.n_src, src_w=w, src_h=h, dst_h=wl.dst_h, dst_w=wl.dst_w, out=warm,
+                          sel=sel_final, boxes=boxes, flips=flips_final, mean=wl.mean, std=wl.std,
+                          max_crop_w=int(wl.boxes[:, 2].max()), launch_overlap=True)
+        sel.copy_(sel_final + 0)        # producer kernels (elementwise add, then copy) on the same stream
+        flips.copy_(flips_final | 0)
+        t.fused_transform(data, n=wl.n, n_src=wl.n_src, src_w=w, src_h=h, dst_h=wl.dst_h, dst_w=wl.dst_w, out=out,
+                          sel=sel, boxes=boxes, flips=flips, mean=wl.mean, std=wl.std,
+                          max_crop_w=int(wl.boxes[:, 2].max()))
         torch.cuda.synchronize()
-        assert int(status.item()) == 0
-        for o in outs:
-            assert np.array_equal(o.cpu().numpy(), want)
-    finally:
-        assert t.set_launch_overlap(False) is True
+        assert np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), want), f"repetition {rep}"

@@ -85,7 +85,7 @@ def test_config5_shards_are_equal_blocks():
             assert np.array_equal(idx, t.direct_order(32768, False, 0, 0, True, r, ws))
 
 
-@pytest.mark.skipif(not O.ref_available("parity"), reason="compiled reference harness not present")
+@pytest.mark.skipif(not O.ref_available("parity") or O.ref_dbc() is None, reason="compiled reference harness not present")
 def test_against_live_reference():
     for kind in (0, 1, 2):
         for total, world in [(0, 2), (1, 1), (17, 5), (4096, 8)]:

@@ -61,13 +61,9 @@ def test_dataloader_argument_errors_do_not_need_a_gpu(tmp_path):
     import turboloader_b200 as t
     with pytest.raises(ValueError, match="output_format"):
         t.DataLoader("x.tbl", output_format="dict")
-    with pytest.raises(ValueError, match="train_aug"):
-        t.DataLoader("x.tbl", train_aug=True)
+    with pytest.raises(ValueError, match="image_size is required"):
+        t.DataLoader(arrays=[np.zeros((4, 5, 3), np.uint8), np.zeros((6, 3, 3), np.uint8)], train_aug=True)
     with pytest.raises(ValueError, match="ImageNetNormalize"):
         t.DataLoader("x.tbl", transform=object())
     with pytest.raises(ValueError, match="RAW_U8 .tbl"):
         t.DataLoader("x.tar")
-    path = tmp_path / "x.tbl"
-    tbl.write_raw_tbl(path, _data())
-    with pytest.raises(ValueError, match="image_size"):
-        t.DataLoader(path, image_size=160)

@@ -4,9 +4,10 @@ Some users of this library cannot allocate memory when they ask for a batch: the
 handed the whole GPU to a training memory pool, or runs under a rule that forbids allocation
 after start-up.  For them the library offers one entry point that stages the crops in a fixed
 device array inside the library instead of a growable ring.  This file checks, through the C
-ABI, that it produces exactly what the regular entry point produces -- twice in a row, because
-the fixed array keeps the bytes of the previous call -- and that it refuses batches beyond its
-stated limits.  It is named to be collected last.
+ABI, that it produces exactly what the regular entry point and the CPU oracle produce -- twice in
+a row, because the fixed array keeps the bytes of the previous call --, that a call leaves the
+amount of free device memory as it found it, and that it refuses batches beyond its stated
+limits.  It is named to be collected last.
 """
 import ctypes as C
 
@@ -15,6 +16,8 @@ import pytest
 
 from turboloader_b200 import _capi
 from turboloader_b200 import synthetic as S
+
+from helpers import expected
 
 pytestmark = pytest.mark.gpu
 
@@ -53,6 +56,35 @@ def test_static_entry_matches_the_regular_entry_twice_in_a_row():
         want = _run(lib.tlb_crop_resize_normalize_to_device, wl, refs, crops, dtype, layout)
         got = _run(lib.tlb_crop_resize_normalize_to_device_static, wl, refs, crops, dtype, layout)
         assert np.array_equal(got, want)  # bit-identical: same kernel, same inputs, different staging
+        # ... and directly against the CPU oracle, in the same layout and dtype
+        wl.dtype = "f32" if dtype == _capi.TLB_F32 else "bf16"
+        wl.channels_last = layout == _capi.TLB_NHWC
+        ref = expected(wl)
+        ref = ref.view(np.int32) if dtype == _capi.TLB_F32 else ref.view(np.int16)
+        assert np.array_equal(got, ref.reshape(-1))
+
+
+def test_static_entry_allocates_no_device_memory():
+    """After the first call on the device (which only looks the array's address up), a call must
+    leave the free device memory exactly as it found it: the staging lives in the library image."""
+    import torch
+    lib = _capi.load()
+    wl = S.config2(seed=33, n=9, lo=30, hi=120, dst=56)
+    refs, crops = _refs(wl)
+    _run(lib.tlb_crop_resize_normalize_to_device_static, wl, refs, crops, _capi.TLB_F32, _capi.TLB_NCHW)  # set-up call
+    out = torch.empty(wl.n * 3 * wl.dst_h * wl.dst_w, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        rc = lib.tlb_crop_resize_normalize_to_device_static(refs, crops, wl.n, wl.dst_h, wl.dst_w, _capi.f3(wl.mean),
+                                                            _capi.f3(wl.std), 1, out.data_ptr(), _capi.TLB_F32,
+                                                            _capi.TLB_NCHW, status.data_ptr(), stream)
+        assert rc == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before and int(status.item()) == 0
 
 
 def test_static_entry_rejects_what_does_not_fit():

@@ -18,6 +18,7 @@ TLB_NCHW, TLB_NHWC = 0, 1
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024  # TLB_STATIC_SCRATCH_BYTES
 STATIC_MAX_SAMPLES = 4096                # TLB_STATIC_MAX_SAMPLES
 DEV_BAD_INDEX, DEV_BAD_BOX, DEV_TOO_WIDE, DEV_COPY_TIMEOUT = 1, 2, 4, 8
+FLAG_LAUNCH_OVERLAP = 1                  # TLB_FLAG_LAUNCH_OVERLAP
 
 
 class TransformDesc(C.Structure):
@@ -50,6 +51,8 @@ class TransformDesc(C.Structure):
         ("status", C.c_void_p),
         ("antialias", C.c_int32),
         ("max_crop_h", C.c_int32),
+        ("jitter", C.c_void_p),
+        ("flags", C.c_uint32),
     ]
 
 
@@ -137,6 +140,9 @@ def load() -> C.CDLL:
     lib.tlb_normalize_resident_gather_batch.argtypes = [C.c_size_t, C.c_size_t, C.c_int32, C.c_int32, C.c_int32,
                                                         _F3, _F3]
     up = C.POINTER(C.c_size_t)
+    lib.tlb_resize_normalize_device_batch.restype = C.c_size_t
+    lib.tlb_resize_normalize_device_batch.argtypes = [up, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32,
+                                                      C.c_int32, C.c_int32, _F3, _F3]
     lib.tlb_video_yuv420.restype = C.c_int
     lib.tlb_video_yuv420.argtypes = [C.POINTER(VideoDesc), C.c_void_p]
     lib.tlb_video_yuv420_batch.restype = C.c_size_t
@@ -156,11 +162,17 @@ def load() -> C.CDLL:
     lib.tlb_stream_next.argtypes = [C.c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_int32), C.c_void_p]
     lib.tlb_stream_status.restype = C.c_int
     lib.tlb_stream_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
+    lib.tlb_epoch_create.restype = C.c_void_p
+    lib.tlb_epoch_create.argtypes = [C.POINTER(TransformDesc), C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
+                                     C.c_int32, C.c_int64, C.c_int64, C.c_int64]
+    lib.tlb_epoch_next.restype = C.c_int
+    lib.tlb_epoch_next.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                   C.c_void_p]
+    lib.tlb_epoch_destroy.restype = None
+    lib.tlb_epoch_destroy.argtypes = [C.c_void_p]
     lib.tlb_fused_plan.restype = C.c_int
     lib.tlb_fused_plan.argtypes = [C.POINTER(TransformDesc)] + [C.POINTER(C.c_int32)] * 5
     lib.tlb_launch_count.restype = C.c_uint64
-    lib.tlb_set_launch_overlap.restype = C.c_int
-    lib.tlb_set_launch_overlap.argtypes = [C.c_int]
     i64p = C.POINTER(C.c_int64)
     lib.tlb_shard_indices.restype = C.c_int64
     lib.tlb_shard_indices.argtypes = [C.c_int32, C.c_int64, C.c_int64, C.c_int64, i64p, C.c_int64]

@@ -129,37 +129,38 @@ int grow(Buffer& b, size_t need) {
 int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl) {
     const int W = d.dst_w, H = d.dst_h;
     const int esz = d.out_dtype == TLB_F32 ? 4 : 2;
-    const int V = 16 / esz;
-    pl.n_col_tiles = (W + tlb::kMaxTileCols - 1) / tlb::kMaxTileCols;
-    pl.tile_cols = std::min(tlb::kMaxTileCols, round_up((W + pl.n_col_tiles - 1) / pl.n_col_tiles, tlb::kStripCols));
+    const bool base_ok = (reinterpret_cast<uintptr_t>(d.out) & 15u) == 0;
+    // Two columns per lane (c and c + 32 of a 64-column strip) unless the output is narrower than
+    // one such strip.
+    pl.cpl = W > 32 ? 2 : 1;
+    if (const int forced = env_int("TLB_CPL", 0); forced == 1) pl.cpl = 1;
+    const int strip_cols = 32 * pl.cpl;
+    const int max_cols = tlb::kMaxStrips * strip_cols;
+    pl.n_col_tiles = (W + max_cols - 1) / max_cols;
+    pl.tile_cols = std::min(max_cols, round_up((W + pl.n_col_tiles - 1) / pl.n_col_tiles, strip_cols));
     pl.n_col_tiles = (W + pl.tile_cols - 1) / pl.tile_cols;
-    pl.strips = pl.tile_cols / tlb::kStripCols;  // one compute warp per 32 output columns
-    // Row tiles of equal height, at most kMaxTileRows (or TLB_TILE_ROWS) rows each.
-    const int max_rows = std::clamp(env_int("TLB_TILE_ROWS", tlb::kMaxTileRows), 1, tlb::kMaxTileRows);
+    pl.strips = pl.tile_cols / strip_cols;  // one compute warp per strip
+    // Row tiles of equal height, at most TLB_TILE_ROWS (default 64) rows each.
+    const int max_rows = std::clamp(env_int("TLB_TILE_ROWS", 64), 1, tlb::kMaxTileRows);
     pl.n_row_tiles = (H + max_rows - 1) / max_rows;
     pl.tile_rows = (H + pl.n_row_tiles - 1) / pl.n_row_tiles;
     pl.n_row_tiles = (H + pl.tile_rows - 1) / pl.tile_rows;
     // Widest source footprint of one column tile (crop-local columns) -> worst-case row pitch.
     long long fw = std::min<long long>(max_crop_w, (static_cast<long long>(pl.tile_cols) * max_crop_w + W - 1) / W + 3);
     pl.pitch = round_up(static_cast<int>(fw) * 3 + 30, 16);
-    // Shared memory: a CTA stages Rr = (var - 2*hrow) / (kNBuf*own_pitch + hrow) new source rows per
-    // pass, using its own (usually narrower) footprint pitch.  The widest crop gets >= kMinRows.
-    constexpr int kMinRows = 4;
-    const int hrow = pl.strips * tlb::kStripRowBytes;
-    const int per_row_worst = tlb::kNBuf * pl.pitch + hrow;
-    // Default budget: 8 KB per strip + 8 KB, at most 56 KB (narrow tiles get more CTAs per SM;
-    // measured on 128- and 224-column outputs).
-    const int dflt_budget = std::min(56 * 1024, (pl.strips + 1) * 8 * 1024);
-    const int budget = std::clamp(env_int("TLB_SMEM_BUDGET", dflt_budget), 8 * 1024, 226 * 1024);
-    int var = std::max(budget - tlb::kSmemVar, kMinRows * per_row_worst + 2 * hrow);
-    var = std::min(var, tlb::kMaxNewRows * per_row_worst + 2 * hrow);
+    // Shared memory: kNBuf raw buffers of Rr rows; a CTA derives Rr from its own (usually narrower)
+    // footprint pitch.  Default: room for TLB_RAW_ROWS (8) rows of the widest crop per buffer.
+    const int want_rows = std::clamp(env_int("TLB_RAW_ROWS", 8), 2, tlb::kMaxNewRows);
+    int var = want_rows * tlb::kNBuf * pl.pitch;
+    if (const int budget = env_int("TLB_SMEM_BUDGET", 0); budget > 0)
+        var = std::clamp(budget - tlb::kSmemVar, 2 * tlb::kNBuf * pl.pitch, tlb::kMaxNewRows * tlb::kNBuf * pl.pitch);
     pl.smem_bytes = tlb::kSmemVar + var;
     if (pl.smem_bytes > 227 * 1024) {
         pl.smem_bytes = 227 * 1024;
-        if (tlb::raw_rows_for(pl.smem_bytes - tlb::kSmemVar, pl.pitch, pl.strips) < 2)
+        if (tlb::raw_rows_for(pl.smem_bytes - tlb::kSmemVar, pl.pitch) < 2)
             return fail(TLB_ERR_TOO_WIDE, "crop width %d does not fit the shared-memory staging buffers", max_crop_w);
     }
-    const bool base_ok = (reinterpret_cast<uintptr_t>(d.out) & 15u) == 0;
+    const int V = 16 / esz;
     if (d.out_layout == TLB_NCHW)
         pl.vec_ok = base_ok && (W % V == 0);
     else
@@ -185,6 +186,10 @@ int check_common(const tlb_transform_desc* d) {
     for (int c = 0; c < 3; ++c)
         if (!(d->std[c] != 0.0f)) return fail(TLB_ERR_INVALID_ARG, "std[%d] must be non-zero", c);
     if (d->labels_out && !d->labels_in) return fail(TLB_ERR_INVALID_ARG, "labels_out given without labels_in");
+    if (d->jitter && !d->normalize_01)
+        return fail(TLB_ERR_INVALID_ARG, "colour jitter works on rgb in [0,1]: it needs normalize_01 = 1 (mean/std in [0,1] units)");
+    if (d->jitter && d->antialias) return fail(TLB_ERR_INVALID_ARG, "colour jitter is not available with the antialiased filter");
+    if (d->flags & ~static_cast<uint32_t>(TLB_FLAG_LAUNCH_OVERLAP)) return fail(TLB_ERR_INVALID_ARG, "unknown bits in flags: 0x%x", d->flags);
     if (!d->boxes && d->uniform_box[2] != 0) {
         const int* b = d->uniform_box;
         if (b[2] < 0 || b[3] <= 0 || b[0] < 0 || b[1] < 0) return fail(TLB_ERR_BAD_BOX, "uniform box (%d,%d,%d,%d) invalid", b[0], b[1], b[2], b[3]);
@@ -219,6 +224,8 @@ void fill_params(const tlb_transform_desc& d, tlb::FusedParams& p) {
     }
     p.pre_scale = d.normalize_01 ? (1.0f / 255.0f) : 1.0f;
     p.one = 1.0f;
+    p.neg_k_pre = -8388608.0f * p.pre_scale;
+    p.jitter = d.jitter;
     p.status = d.status;
 }
 
@@ -228,15 +235,17 @@ int derive_max_crop_w(const tlb_transform_desc& d) {
     return d.src_w;
 }
 
-// `may_overlap`: the launch may start before the previous fused launch in the stream has drained
-// (only when the caller enabled it, and only for the entry point whose inputs the library did not
-// itself produce in the stream just before).
-int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool may_overlap = false) {
+// `honour_flags`: only tlb_fused_transform, whose inputs the caller staged itself, passes the
+// descriptor's launch flags on (TLB_FLAG_LAUNCH_OVERLAP); every other entry point stages inputs in
+// the stream just before the kernel and launches in full stream order.
+int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool honour_flags = false,
+                bool per_image_region = false) {
     int dev;
     if (int rc = current_device(&dev)) return rc;
     if (int rc = ensure_prepared(g_dev[dev])) return rc;
     tlb::FusedParams p{};
     fill_params(d, p);
+    p.per_image_region = per_image_region ? 1 : 0;
     if (d.antialias) {
         // Opt-in triangle filter: its own kernel; tap tables are sized from the largest crop.
         int max_crop_h = d.max_crop_h;
@@ -259,16 +268,17 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
         return TLB_OK;
     }
     if (int rc = make_plan(d, max_crop_w, p.plan)) return rc;
+    const unsigned lflags = (honour_flags && (d.flags & TLB_FLAG_LAUNCH_OVERLAP)) ? tlb::kLaunchOverlap : 0u;
     // Identity size (no resampling) on a uniform dataset: a plain streaming kernel does the job.
     const bool uniform = !d.boxes && !d.src_sizes && !d.src_offsets;
     const int cw = d.uniform_box[2] > 0 ? d.uniform_box[2] : d.src_w;
     const int ch = d.uniform_box[2] > 0 ? d.uniform_box[3] : d.src_h;
-    if (uniform && cw == d.dst_w && ch == d.dst_h && env_int("TLB_IDENTITY_FAST", 1) != 0) {
+    if (uniform && !d.jitter && cw == d.dst_w && ch == d.dst_h && env_int("TLB_IDENTITY_FAST", 1) != 0) {
         cudaError_t ce = static_cast<cudaError_t>(tlb::launch_normalize_copy(p, d.out_dtype, d.out_layout, stream));
         if (ce != cudaSuccess) return cuda_fail(ce, "normalize_copy_kernel launch");
         return TLB_OK;
     }
-    cudaError_t e = static_cast<cudaError_t>(tlb::launch_fused(p, d.out_dtype, d.out_layout, stream, may_overlap));
+    cudaError_t e = static_cast<cudaError_t>(tlb::launch_fused(p, d.out_dtype, d.out_layout, stream, lflags));
     if (e != cudaSuccess) return cuda_fail(e, "fused_transform_kernel launch");
     return TLB_OK;
 }
@@ -611,6 +621,46 @@ int sync_host_form(const tlb_image_ref* imgs, const tlb_crop_params* crops, int 
     return TLB_OK;
 }
 
+// Bytes that are readable from `p` to the end of the device allocation that contains it (the
+// driver's cuMemGetAddressRange, reached through the runtime's entry-point lookup so that the
+// library needs no link-time dependency on the driver).  Returns false when the driver cannot
+// tell (not a device allocation of the current context).
+bool readable_extent(const void* p, size_t* bytes) {
+    using Fn = int (*)(unsigned long long*, size_t*, unsigned long long);
+    static Fn fn = [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            sym = nullptr;
+        }
+        return reinterpret_cast<Fn>(sym);
+    }();
+    if (!fn) return false;
+    unsigned long long base = 0;
+    size_t size = 0;
+    const unsigned long long a = reinterpret_cast<unsigned long long>(p);
+    if (fn(&base, &size, a) != 0 || a < base || a >= base + size) return false;
+    *bytes = static_cast<size_t>(base + size - a);
+    return true;
+}
+
+// Output slot of the pointer-returning forms: a 4-deep ring of library-owned device buffers.
+int ring_slot(DeviceState& st, size_t bytes, void** out, int* slot_out) {
+    const int slot = st.out_next;
+    if (bytes > st.out_cap[slot]) {
+        if (st.out_ring[slot]) cudaFree(st.out_ring[slot]);
+        st.out_ring[slot] = nullptr;
+        st.out_cap[slot] = 0;
+        TLB_CUDA(cudaMalloc(&st.out_ring[slot], bytes));
+        st.out_cap[slot] = bytes;
+    }
+    *out = st.out_ring[slot];
+    *slot_out = slot;
+    return TLB_OK;
+}
+
 uintptr_t resident_form(uintptr_t src_dev, uintptr_t sel_dev, bool gather, int n, int h, int w, const float mean[3],
                         const float std_[3]) {
     if (!src_dev || (gather && !sel_dev) || n <= 0 || h <= 0 || w <= 0 || !mean || !std_) {
@@ -626,32 +676,37 @@ uintptr_t resident_form(uintptr_t src_dev, uintptr_t sel_dev, bool gather, int n
         return 0;
     }
     const size_t bytes = static_cast<size_t>(n) * 3 * h * w * sizeof(float);
-    const int slot = st.out_next;
-    if (bytes > st.out_cap[slot]) {
-        if (st.out_ring[slot]) cudaFree(st.out_ring[slot]);
-        st.out_ring[slot] = nullptr;
-        st.out_cap[slot] = 0;
-        cudaError_t e = cudaMalloc(&st.out_ring[slot], bytes);
-        if (e != cudaSuccess) {
-            cuda_fail(e, "cudaMalloc(resident output ring)");
-            return 0;
-        }
-        st.out_cap[slot] = bytes;
-    }
+    void* out = nullptr;
+    int slot = 0;
+    if (ring_slot(st, bytes, &out, &slot)) return 0;
     tlb_transform_desc d{};
     d.src = reinterpret_cast<const uint8_t*>(src_dev);
-    // Without a gather the batch is the first n images at src_dev.  With one, the caller's
-    // dataset extent is unknown to this legacy signature: indices are trusted, as in the
-    // function it replaces, and the readable region is left unbounded.
-    d.n_src = gather ? (1ll << 40) : n;
-    d.src_bytes = gather ? ~0ull >> 1 : static_cast<uint64_t>(n) * h * w * 3;
+    // Without a gather the batch is the first n images at src_dev.  With one, this legacy signature
+    // does not say how many images the dataset holds: the bound is the end of the device allocation
+    // that contains src_dev (asked from the driver), so an index beyond it is reported
+    // (TLB_DEV_BAD_INDEX, sample zero-filled) instead of read, and no row copy is rounded out past it.
+    // Only when the driver cannot name the allocation are indices trusted, as in the function replaced.
+    const size_t img_bytes = static_cast<size_t>(h) * w * 3;
+    if (gather) {
+        size_t extent = 0;
+        if (readable_extent(d.src, &extent) && extent >= img_bytes) {
+            d.n_src = static_cast<int64_t>(extent / img_bytes);
+            d.src_bytes = static_cast<uint64_t>(d.n_src) * img_bytes;
+        } else {
+            d.n_src = 1ll << 40;
+            d.src_bytes = ~0ull >> 1;
+        }
+    } else {
+        d.n_src = n;
+        d.src_bytes = static_cast<uint64_t>(n) * img_bytes;
+    }
     d.src_w = w;
     d.src_h = h;
     d.n = n;
     d.sel = gather ? reinterpret_cast<const int64_t*>(sel_dev) : nullptr;
     d.dst_h = h;
     d.dst_w = w;
-    d.out = st.out_ring[slot];
+    d.out = out;
     d.out_dtype = TLB_F32;
     d.out_layout = TLB_NCHW;
     for (int c = 0; c < 3; ++c) {
@@ -667,7 +722,89 @@ uintptr_t resident_form(uintptr_t src_dev, uintptr_t sel_dev, bool gather, int n
         return 0;
     }
     st.out_next = (slot + 1) % 4;
-    return reinterpret_cast<uintptr_t>(st.out_ring[slot]);
+    return reinterpret_cast<uintptr_t>(out);
+}
+
+// resize_normalize_device_batch: already-decoded images in SEPARATE device allocations.
+uintptr_t device_images_form(const uintptr_t* d_imgs, const int32_t* ws, const int32_t* hs, int n, int dst_h, int dst_w,
+                             const float mean[3], const float std_[3]) {
+    if (!d_imgs || !ws || !hs || n <= 0 || dst_h <= 0 || dst_w <= 0 || !mean || !std_) {
+        fail(TLB_ERR_INVALID_ARG, "resize_normalize_device_batch: NULL pointer, empty list or non-positive size");
+        return 0;
+    }
+    int dev;
+    if (current_device(&dev)) return 0;
+    DeviceState& st = g_dev[dev];
+    // One base + non-negative offsets: the lowest address is the base.  Every image is checked
+    // against the device allocation that holds it, and the kernel is told that images are separate
+    // regions, so that no load (not even the 16-byte round-out of a row copy) leaves an image.
+    uintptr_t lo = ~static_cast<uintptr_t>(0), hi = 0;
+    int max_w = 1;
+    for (int i = 0; i < n; ++i) {
+        if (!d_imgs[i] || ws[i] <= 0 || hs[i] <= 0 || static_cast<long long>(ws[i]) * hs[i] * 3 > 0x7fffffffll) {
+            fail(TLB_ERR_INVALID_ARG, "resize_normalize_device_batch: image %d has a NULL address or a bad size", i);
+            return 0;
+        }
+        const size_t bytes = static_cast<size_t>(ws[i]) * hs[i] * 3;
+        size_t extent = 0;
+        if (readable_extent(reinterpret_cast<const void*>(d_imgs[i]), &extent) && extent < bytes) {
+            fail(TLB_ERR_BAD_INDEX, "resize_normalize_device_batch: image %d (%dx%d) does not fit its device allocation", i, ws[i], hs[i]);
+            return 0;
+        }
+        lo = std::min(lo, d_imgs[i]);
+        hi = std::max(hi, d_imgs[i] + bytes);
+        max_w = std::max(max_w, ws[i]);
+    }
+    std::unique_lock<std::mutex> lk(st.mu);
+    if (!st.stream && cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking) != cudaSuccess) {
+        fail(TLB_ERR_CUDA, "cudaStreamCreate failed");
+        return 0;
+    }
+    void* out = nullptr;
+    int slot = 0;
+    if (ring_slot(st, static_cast<size_t>(n) * 3 * dst_h * dst_w * sizeof(float), &out, &slot)) return 0;
+    Buffer& buf = st.params[st.params_next];
+    st.params_next = (st.params_next + 1) % 4;
+    if (grow(buf, 16 * static_cast<size_t>(n))) return 0;
+    auto* h_off = static_cast<long long*>(buf.host);
+    auto* h_size = reinterpret_cast<int*>(static_cast<unsigned char*>(buf.host) + 8 * static_cast<size_t>(n));
+    for (int i = 0; i < n; ++i) {
+        h_off[i] = static_cast<long long>(d_imgs[i] - lo);
+        h_size[2 * i] = ws[i];
+        h_size[2 * i + 1] = hs[i];
+    }
+    if (cudaMemcpyAsync(buf.dev, buf.host, 16 * static_cast<size_t>(n), cudaMemcpyHostToDevice, st.stream) != cudaSuccess) {
+        cuda_fail(cudaGetLastError(), "resize_normalize_device_batch: table upload");
+        return 0;
+    }
+    tlb_transform_desc d{};
+    d.src = reinterpret_cast<const uint8_t*>(lo);
+    d.src_bytes = hi - lo;
+    d.n_src = n;
+    d.src_offsets = static_cast<const int64_t*>(buf.dev);
+    d.src_sizes = reinterpret_cast<const int32_t*>(static_cast<unsigned char*>(buf.dev) + 8 * static_cast<size_t>(n));
+    d.src_w = max_w;
+    d.n = n;
+    d.dst_h = dst_h;
+    d.dst_w = dst_w;
+    d.out = out;
+    d.out_dtype = TLB_F32;
+    d.out_layout = TLB_NCHW;
+    for (int c = 0; c < 3; ++c) {
+        d.mean[c] = mean[c];
+        d.std[c] = std_[c];
+    }
+    d.normalize_01 = 1;
+    d.max_crop_w = max_w;
+    if (check_common(&d)) return 0;
+    if (launch_desc(d, max_w, st.stream, false, /*per_image_region=*/true)) return 0;
+    cudaError_t e = cudaStreamSynchronize(st.stream);  // also makes the pinned table buffer reusable
+    if (e != cudaSuccess) {
+        cuda_fail(e, "resize_normalize_device_batch");
+        return 0;
+    }
+    st.out_next = (slot + 1) % 4;
+    return reinterpret_cast<uintptr_t>(out);
 }
 
 }  // namespace
@@ -710,7 +847,7 @@ int tlb_fused_transform(const tlb_transform_desc* desc, void* stream) {
     const int mcw = derive_max_crop_w(*desc);
     if (mcw <= 0)
         return fail(TLB_ERR_INVALID_ARG, "max_crop_w is required when sizes and boxes are per-sample device tables");
-    return launch_desc(*desc, mcw, stream, /*may_overlap=*/true);
+    return launch_desc(*desc, mcw, stream, /*honour_flags=*/true);
 }
 
 int tlb_fused_transform_host_params(const tlb_transform_desc* desc, void* stream) {
@@ -805,6 +942,11 @@ uintptr_t tlb_normalize_resident_gather_batch(uintptr_t src_dev, uintptr_t sel_d
     return resident_form(src_dev, sel_dev, true, n, h, w, mean, std_);
 }
 
+uintptr_t tlb_resize_normalize_device_batch(const uintptr_t* d_imgs, const int32_t* ws, const int32_t* hs, int32_t n,
+                                            int32_t dst_h, int32_t dst_w, const float mean[3], const float std_[3]) {
+    return device_images_form(d_imgs, ws, hs, n, dst_h, dst_w, mean, std_);
+}
+
 int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block, int32_t* smem_bytes,
                    int32_t* tile_rows, int32_t* tile_cols) {
     if (int rc = check_common(desc)) return rc;
@@ -819,8 +961,6 @@ int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block
     if (tile_cols) *tile_cols = pl.tile_cols;
     return TLB_OK;
 }
-
-int tlb_set_launch_overlap(int enable) { return tlb::set_launch_overlap(enable); }
 
 uint64_t tlb_launch_count(void) {
     return tlb::launch_count() + tlb::video_launch_count() + tlb::antialias_launch_count() + tlb::normalize_copy_launch_count() +
@@ -884,6 +1024,11 @@ int tlb_crop_resize_normalize_to_device_static(const tlb_image_ref* imgs, const 
     if (n > TLB_STATIC_MAX_SAMPLES)
         return fail(TLB_ERR_TOO_LARGE, "n = %d exceeds the %d samples the allocation-free entry point supports", n,
                     TLB_STATIC_MAX_SAMPLES);
+    // One call at a time fills the shared host table buffer: the lock is held until the tables have
+    // been handed to the copy engine (uploads from pageable host memory are staged before
+    // cudaMemcpyAsync returns), so two host threads driving two different GPUs do not mix tables.
+    static std::mutex tables_mu;
+    std::lock_guard<std::mutex> tables_lock(tables_mu);
     StaticTables& t = g_static_tables;
     // ---- validate every crop on the host and lay the packed crops out ------------------------
     size_t pix = 0;
@@ -1336,6 +1481,151 @@ int tlb_stream_status(tlb_stream_core* core, uint32_t* out_status) {
     for (cudaStream_t s : core->streams) TLB_CUDA(cudaStreamSynchronize(s));
     TLB_CUDA(cudaMemcpy(out_status, core->status, 4, cudaMemcpyDeviceToHost));
     return TLB_OK;
+}
+
+}  // extern "C"
+
+// ---- resident epochs ---------------------------------------------------------------------------
+// Replaces the per-batch call + synchronise loop of the reference's resident loader
+// (turboloader/cuda_loader.py:512-535) by a prefetching pipeline on a library-owned stream.
+struct tlb_epoch {
+    int dev = 0;
+    tlb_transform_desc first{};
+    int max_crop_w = 0;
+    int64_t total = 0, n_batches = 0;
+    int64_t enqueued = 0, returned = 0;
+    int ring = 0, ahead = 0, group = 0;
+    int64_t out_slot = 0, idx_slot = 0, label_slot = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t consumed = nullptr;
+    std::vector<cudaEvent_t> ready;
+};
+
+namespace {
+
+int epoch_enqueue(tlb_epoch* e, int64_t count, void* consumer_stream) {
+    // Slots about to be overwritten were handed out at least ring - ahead - group calls ago: order the
+    // prefetch stream behind everything the consumer has enqueued so far, once per group.
+    TLB_CUDA(cudaEventRecord(e->consumed, static_cast<cudaStream_t>(consumer_stream)));
+    TLB_CUDA(cudaStreamWaitEvent(e->stream, e->consumed, 0));
+    for (int64_t i = 0; i < count; ++i) {
+        const int64_t b = e->enqueued;
+        const int64_t pos = b * e->first.n;
+        const int slot = static_cast<int>(b % e->ring);
+        tlb_transform_desc d = e->first;
+        d.n = static_cast<int32_t>(std::min<int64_t>(e->first.n, e->total - pos));
+        if (d.sel) {
+            d.sel += pos;
+        } else {  // sequential: the batch is a contiguous slice of the uniform dataset
+            const uint64_t img = static_cast<uint64_t>(d.src_w) * d.src_h * 3;
+            d.src += pos * img;
+            d.src_bytes = static_cast<uint64_t>(d.n) * img;
+            d.n_src = d.n;
+            if (d.labels_in) d.labels_in += pos;
+        }
+        if (d.boxes) d.boxes += 4 * pos;
+        if (d.flips) d.flips += pos;
+        if (d.jitter) d.jitter += 3 * pos;
+        d.out = static_cast<char*>(d.out) + slot * e->out_slot;
+        if (d.out_indices) d.out_indices = reinterpret_cast<int64_t*>(reinterpret_cast<char*>(d.out_indices) + slot * e->idx_slot);
+        if (d.labels_out) d.labels_out = reinterpret_cast<int64_t*>(reinterpret_cast<char*>(d.labels_out) + slot * e->label_slot);
+        d.flags = TLB_FLAG_LAUNCH_OVERLAP;
+        if (int rc = launch_desc(d, e->max_crop_w, e->stream, /*honour_flags=*/true)) return rc;
+        TLB_CUDA(cudaEventRecord(e->ready[slot], e->stream));
+        e->enqueued = b + 1;
+    }
+    return TLB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+tlb_epoch* tlb_epoch_create(const tlb_transform_desc* first, int64_t total, int32_t drop_last, int64_t start_batch,
+                            int32_t ring, int32_t ahead, int32_t group, int64_t out_slot_bytes,
+                            int64_t index_slot_bytes, int64_t label_slot_bytes) {
+    if (check_common(first)) return nullptr;
+    if (first->n <= 0 || total <= 0 || start_batch < 0) {
+        fail(TLB_ERR_INVALID_ARG, "epoch: batch size, total and start_batch must be positive / non-negative");
+        return nullptr;
+    }
+    if (group < 1 || ahead < group || ring < ahead + group + 1) {
+        fail(TLB_ERR_INVALID_ARG, "epoch: need group >= 1, ahead >= group and ring >= ahead + group + 1 (got ring %d, ahead %d, group %d)", ring, ahead, group);
+        return nullptr;
+    }
+    if (!first->sel && (first->src_offsets || first->src_sizes)) {
+        fail(TLB_ERR_INVALID_ARG, "epoch: reading the dataset in order needs the uniform layout (or pass sel)");
+        return nullptr;
+    }
+    if (!first->sel && static_cast<int64_t>(first->n_src) < total) {
+        fail(TLB_ERR_BAD_INDEX, "epoch: total = %lld exceeds n_src = %lld", static_cast<long long>(total), static_cast<long long>(first->n_src));
+        return nullptr;
+    }
+    if (out_slot_bytes <= 0 || (first->out_indices && index_slot_bytes <= 0) || (first->labels_out && label_slot_bytes <= 0)) {
+        fail(TLB_ERR_INVALID_ARG, "epoch: slot strides must be positive");
+        return nullptr;
+    }
+    const int mcw = derive_max_crop_w(*first);
+    if (mcw <= 0) {
+        fail(TLB_ERR_INVALID_ARG, "epoch: max_crop_w is required when sizes and boxes are per-sample device tables");
+        return nullptr;
+    }
+    int dev;
+    if (current_device(&dev)) return nullptr;
+    auto* e = new tlb_epoch;
+    e->dev = dev;
+    e->first = *first;
+    e->max_crop_w = mcw;
+    e->total = total;
+    e->n_batches = drop_last ? total / first->n : (total + first->n - 1) / first->n;
+    e->enqueued = e->returned = std::min<int64_t>(start_batch, e->n_batches);
+    e->ring = ring; e->ahead = ahead; e->group = group;
+    e->out_slot = out_slot_bytes; e->idx_slot = index_slot_bytes; e->label_slot = label_slot_bytes;
+    e->ready.assign(ring, nullptr);
+    bool ok = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&e->consumed, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; ok && i < ring; ++i) ok = cudaEventCreateWithFlags(&e->ready[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) {
+        cuda_fail(cudaGetLastError(), "epoch: creating the prefetch stream and events");
+        tlb_epoch_destroy(e);
+        return nullptr;
+    }
+    return e;
+}
+
+int tlb_epoch_next(tlb_epoch* e, int64_t* batch, int32_t* n, int32_t* slot, void* consumer_stream) {
+    if (!e || !batch || !n || !slot) return fail(TLB_ERR_INVALID_ARG, "epoch: NULL argument");
+    *n = 0;
+    if (e->returned >= e->n_batches) return TLB_OK;  // epoch finished
+    TLB_CUDA(cudaSetDevice(e->dev));
+    // Keep `ahead` batches in flight beyond the one handed out now, topping up a group at a time.
+    const int64_t want = std::min<int64_t>(e->n_batches, e->returned + 1 + e->ahead);
+    // Batch q overwrites the slot of batch q - ring; with q <= returned + ahead and
+    // ring >= ahead + group + 1 that batch was handed out more than `group` calls ago, i.e. its
+    // validity (ring - ahead - group further calls) has run out.
+    if (e->enqueued <= e->returned || want - e->enqueued >= e->group || (want == e->n_batches && e->enqueued < want))
+        if (int rc = epoch_enqueue(e, want - e->enqueued, consumer_stream)) return rc;
+    const int64_t b = e->returned;
+    const int s = static_cast<int>(b % e->ring);
+    TLB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(consumer_stream), e->ready[s], 0));
+    *batch = b;
+    *n = static_cast<int32_t>(std::min<int64_t>(e->first.n, e->total - b * e->first.n));
+    *slot = s;
+    e->returned = b + 1;
+    return TLB_OK;
+}
+
+void tlb_epoch_destroy(tlb_epoch* e) {
+    if (!e) return;
+    cudaSetDevice(e->dev);
+    if (e->stream) {
+        cudaStreamSynchronize(e->stream);
+        cudaStreamDestroy(e->stream);
+    }
+    for (cudaEvent_t ev : e->ready)
+        if (ev) cudaEventDestroy(ev);
+    if (e->consumed) cudaEventDestroy(e->consumed);
+    delete e;
 }
 
 }  // extern "C"

@@ -5,21 +5,21 @@
 
 namespace tlb {
 
-constexpr int kStripCols = 32;     // output columns owned by one compute warp
-constexpr int kStripRowBytes = 400; // one h row of a strip: 3 x 32 floats + 16 B of bank stagger
 constexpr int kMaxNewRows = 32;    // one planner lane issues the copy of one new source row
-constexpr int kMaxTileCols = 256;  // output columns per CTA (8 strips)
+constexpr int kMaxStrips = 8;      // compute warps per CTA
+constexpr int kMaxTileRows = 128;  // output rows per CTA (row tables are sized for this)
 
 // Launch geometry chosen on the host from sizes only (never from device data).
 struct Plan {
     int tile_rows;    // output rows per CTA
-    int tile_cols;    // output columns per CTA (multiple of 32, <= kMaxTileCols)
+    int tile_cols;    // output columns per CTA (multiple of strip_cols)
     int n_col_tiles;  // ceil(dst_w / tile_cols)
     int n_row_tiles;  // ceil(dst_h / tile_rows)
-    int strips;       // compute warps = tile_cols / 32; CTA size = 32 * (strips + 1)
+    int strips;       // compute warps; CTA size = 32 * (strips + 1)
+    int cpl;          // output columns owned by one lane: c and c + 32 of a 64-column strip (2), or one (1)
     int pitch;        // bytes per staged raw row at the widest crop (multiple of 16)
     int smem_bytes;   // dynamic shared memory per CTA
-    int vec_ok;       // 1: every 16-byte output chunk is aligned and whole -> vector stores
+    int vec_ok;       // 1: every 16-byte output chunk is aligned and whole (identity-size kernel only)
     long long grid;   // CTAs
 };
 
@@ -44,15 +44,16 @@ struct FusedParams {
     float inv_std[3];  // 1.0f / std formed on the host in fp32 (direct_batch_loader.hpp:57)
     float pre_scale;   // 1/255 when normalize_01 else 1
     float one;         // 1.0f, deliberately a run-time value (see add2_exact in the kernel)
+    float neg_k_pre;   // -2^23 * pre_scale (exact: a power-of-two scaling)
+    const float* jitter;  // [n][3] per-sample (brightness, contrast, saturation) factors, or NULL
+    int per_image_region; // 1: images are separate allocations -- no load may leave the image itself
     unsigned int* status;
     Plan plan;
 };
 
-// Shared-memory layout.  A fixed header is followed by a region the CTA carves up itself
-// from its own footprint width: kNBuf raw staging buffers of Rr source rows each (filled by
-// bulk async copies, the planner runs that many passes ahead) and, per 32-column strip, a ring of Rh = Rr + 2 rows
-// of horizontally-interpolated fp32 values (kStripRowBytes each).
-constexpr int kMaxTileRows = 64;   // output rows per CTA (row tables are sized for this)
+// Shared-memory layout: a fixed header followed by kNBuf raw staging buffers of Rr source rows
+// each (filled by bulk async copies; the planner runs that many passes ahead).  Rr is derived per
+// CTA from its own footprint width.
 #ifndef TLB_NBUF
 #define TLB_NBUF 3
 #endif
@@ -60,28 +61,29 @@ constexpr int kNBuf = TLB_NBUF;    // raw staging buffers = passes the planner m
 constexpr int kSlots = kNBuf + 1;  // pass records kept (a record outlives its raw buffer by one pass)
 constexpr int kSmemFull = 0;       // kNBuf x 8 B mbarriers: raw buffer b filled (transaction count)
 constexpr int kSmemEmpty = 32;     // kNBuf x 8 B mbarriers: raw buffer b consumed by every compute warp
-constexpr int kSmemMeta = 64;      // kSlots x int4 {output rows, new source rows, last pass?, first output row}
-constexpr int kSmemRowOff = 256;   // kSlots x 32 x int2 {raw byte offset, ring byte offset} per new source row of a pass
-constexpr int kSmemRowp = 256 + 1280;          // kMaxTileRows x float4 {ring byte offset of y0 row, of y1 row, dy, 1-dy}
-constexpr int kSmemRowY = 256 + 1280 + 1024;   // kMaxTileRows x int2 {y0, y1} crop-local source rows
-constexpr int kSmemVar = 256 + 1280 + 1024 + 512;  // = 3072, start of the carved region (128-byte multiple)
-static_assert(kNBuf >= 2 && kNBuf <= 4 && kSlots * 256 <= 1280, "header slots are sized for at most 4 buffers");
+constexpr int kSmemMeta = 64;      // kSlots x int4 {new source rows, output rows emitted before the first of them, last pass?, -}
+constexpr int kSmemSrcRec = 256;   // kSlots x 32 x int2 {byte offset of a new source row in shared memory, output rows emitted after it}
+constexpr int kSmemRowW = kSmemSrcRec + kSlots * 32 * 8;   // kMaxTileRows x float4 {wA, wA, wB, wB}: vertical weights of the two row buffers
+constexpr int kSmemRowY = kSmemRowW + kMaxTileRows * 16;   // kMaxTileRows x int: y0, the upper source row (crop-local)
+constexpr int kSmemVar = (kSmemRowY + kMaxTileRows * 4 + 127) & ~127;  // start of the raw buffers
+static_assert(kNBuf >= 2 && kNBuf <= 4, "header slots are sized for at most 4 buffers");
 
-inline __host__ __device__ int raw_rows_for(int var_bytes, int own_pitch, int strips) {
-    const int hrow = strips * kStripRowBytes;
-    int r = (var_bytes - 2 * hrow) / (kNBuf * own_pitch + hrow);
+inline __host__ __device__ int raw_rows_for(int var_bytes, int own_pitch) {
+    const int r = var_bytes / (kNBuf * own_pitch);
     return r > kMaxNewRows ? kMaxNewRows : r;
 }
 
+// Launch flags (per call).
+constexpr unsigned kLaunchOverlap = 1u;  // programmatic stream serialization: may start while the previous kernel drains
+
 // Implemented in fused_transform.cu.  Returns a cudaError_t as int.
-int launch_fused(const FusedParams& p, int out_dtype, int out_layout, void* stream, bool may_overlap);
+int launch_fused(const FusedParams& p, int out_dtype, int out_layout, void* stream, unsigned flags);
 // One-time per-device opt-in to large dynamic shared memory; returns a cudaError_t as int.
 int prepare_device();
 unsigned long long launch_count();
-int set_launch_overlap(int enable);  // returns the previous setting
 
 // Implemented in normalize_copy.cu: the identity-size case (crop size == output size, uniform
-// dataset, no per-sample boxes).  Uses p.plan.vec_ok only.  Returns a cudaError_t as int.
+// dataset, no per-sample boxes).  Returns a cudaError_t as int.
 int launch_normalize_copy(const FusedParams& p, int out_dtype, int out_layout, void* stream);
 unsigned long long normalize_copy_launch_count();
 

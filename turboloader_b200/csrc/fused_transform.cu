@@ -1,4 +1,5 @@
-// Fused crop -> hflip -> bilinear resize -> normalize -> layout/cast kernel for sm_100a.
+// Fused crop -> hflip -> bilinear resize -> (colour jitter) -> normalize -> layout/cast kernel
+// for sm_100a.
 //
 // Replaces TurboLoader's per-image kernels resize_normalize_kernel /
 // crop_resize_normalize_kernel (src/cuda/cuda_transforms.cu:35-80) and its
@@ -14,27 +15,29 @@
 // in the CPU path's order, so fp32 output is bit-identical to it.
 //
 // Structure of one CTA = one tile of `tile_rows` x `tile_cols` outputs of one sample.  One
-// warp per 32-column strip computes; one more warp only plans and copies.  No CTA-wide barrier
-// is used after the prologue: the warps meet through mbarriers only.
-//   planner warp: walks down the tile in passes of at most Rr NEW source rows (rows the strips
-//      do not hold yet).  One lane per output row looks up (y0, y1) in a per-tile row table; the
-//      first and last rows are exchanged with warp shuffles to find the range of new rows.  It
-//      issues one 1-D bulk async copy (cp.async.bulk, global -> this CTA's shared memory,
-//      completion on a "full" mbarrier) per new source row, each rounded out to 16-byte
+// warp per strip of 32*CPL output columns computes; one more warp only plans and copies.  No
+// CTA-wide barrier is used after the prologue: the warps meet through mbarriers only.
+//   planner warp: walks down the tile in passes of at most Rr NEW source rows (rows the compute
+//      warps have not consumed yet).  One lane per output row looks up (y0, y1) in a per-tile row
+//      table; the first and last rows are exchanged with warp shuffles to find the range of new
+//      rows.  It issues one 1-D bulk async copy (cp.async.bulk, global -> this CTA's shared
+//      memory, completion on a "full" mbarrier) per new source row, each rounded out to 16-byte
 //      boundaries; bytes that cannot be reached on a 16-byte grid inside the readable region are
-//      fetched with plain loads.  Raw rows are double buffered; a buffer is refilled once every
-//      compute warp has arrived on its "empty" mbarrier.
-//   compute warp, "H" step: every new source row is interpolated horizontally once,
-//      h = p[x0]*(1-dx) + p[x1]*dx, into a ring of fp32 rows private to the strip.  Each lane owns
-//      one output column for the whole tile and keeps its weights in registers.
-//   compute warp, "V" step: each lane owns 4 (fp32) or 8 (bf16) adjacent pixels of the strip and
-//      the warp covers 8 / 4 output rows at a time: v = h[y0]*(1-dy) + h[y1]*dy, truncate,
-//      normalize, cast, three 16-byte stores per row.  The layout of a ring row (planar for
-//      NCHW, interleaved for NHWC, rows staggered by 16 bytes) makes every input a
-//      conflict-free 16-byte shared load.  The fp32 arithmetic uses the packed two-lane forms
-//      (mul/fma .f32x2) of sm_100; they round each lane exactly like the scalar instructions.
-// The bilinear blend is exactly separable in this order (top and bot depend on one
-// source row each), so sharing h between neighbouring output rows changes no bit.
+//      fetched with plain loads.  kNBuf raw buffers let it run that many passes ahead; a buffer is
+//      refilled once every compute warp has arrived on its "empty" mbarrier.
+//   compute warp: each lane owns output columns c and c + 32 of the strip (CPL = 2; offsets and
+//      weights of their source columns stay in registers) and walks DOWN the tile, consuming the
+//      staged source rows in order.  It keeps the horizontally interpolated values
+//      h = p[x0]*(1-dx) + p[x1]*dx of the two most recent source rows in two register buffers; a
+//      new source row costs one "H step" (six byte loads per column from the staged row, into the
+//      buffer that holds the older row), and every output row that is complete after it one
+//      "V step": v = hA*wA + hB*wB, truncate, normalize, cast, store.  Nothing but the staged bytes
+//      ever goes through shared memory: the blend is exactly separable in this order (top and bot
+//      depend on one source row each), so reusing h between neighbouring output rows changes no
+//      bit.  Across a warp each store covers 32 adjacent pixels.  The fp32 arithmetic uses the
+//      packed two-lane forms (fma/mul/add .f32x2) of sm_100 with the two columns of a lane
+//      (CPL = 2) or two channels (CPL = 1) in the two halves; they round each half exactly like
+//      the scalar instructions.
 //
 // No tensor-core instruction is used: there is no contraction in this operation.
 // No cluster launch and no multicast form of any copy is used; every load reads the
@@ -51,11 +54,6 @@
 namespace tlb {
 namespace {
 
-#ifndef TLB_H_UNROLL
-#define TLB_H_UNROLL 4
-#endif
-constexpr int kHUnroll = TLB_H_UNROLL;  // source rows in flight per lane in the H step
-
 constexpr unsigned kDevBadIndex = 1u, kDevBadBox = 2u, kDevTooWide = 4u, kDevCopyTimeout = 8u;
 constexpr unsigned kWaitLimit = 1u << 20;  // bounded mbarrier polling (each poll may suspend briefly)
 
@@ -71,8 +69,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t mbar, uint32_t by
 }
 // One poll.  The suspend-time hint lets the hardware park the warp until the phase completes
 // (or the hint expires) instead of returning at once: a warp that waits does not burn issue
-// slots re-polling -- with plain polls the waiting planner and compute warps executed more than
-// a quarter of all instructions of the kernel.
+// slots re-polling.
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t mbar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -112,6 +109,16 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
         "l"(src), "r"(bytes), "r"(mbar)
         : "memory");
 }
+// Hardware named barriers (1..15) between the compute warps and the planner warp of one CTA: a
+// compute warp signals "done with raw buffer b" without blocking, the planner blocks (issuing
+// nothing) until all of them have.  Like __syncthreads, this waits only for warps of the same CTA,
+// all of which always get there: their own waits on asynchronous copies are bounded.
+__device__ __forceinline__ void named_arrive(int id, int threads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 // simd_utils.hpp:100-103, with each operation rounded separately.
 __device__ __forceinline__ float src_coord(int i, float scale) {
@@ -122,16 +129,11 @@ __device__ __forceinline__ float src_coord(int i, float scale) {
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 
 // Packed two-lane fp32 multiply / add of sm_100 (mul.f32x2, add.f32x2) with explicit rounding.
-// Each lane rounds like the scalar instruction.  CAUTION: the assembler was observed to
+// Each half rounds like the scalar instruction.  CAUTION: the assembler was observed to
 // contract a packed multiply feeding a packed add into one FMA even with explicit .rn and with
 // fmad disabled (it flips ~1e-5 of the 8-bit codes and the last bit of most normalized
-// values).  So wherever a product feeds a sum, the sum is done with the scalar __fadd_rn,
-// which is never contracted; packed adds are used only where no product is an input.
-#ifdef TLB_NO_PACKED
-__device__ __forceinline__ float2 mul2_rn(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
-__device__ __forceinline__ float2 add2_rn(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
-__device__ __forceinline__ float2 add2_rz(float2 a, float2 b) { return make_float2(__fadd_rz(a.x, b.x), __fadd_rz(a.y, b.y)); }
-#else
+// values).  So wherever a product feeds a sum, the sum is issued through add2_exact below;
+// the plain packed add is used only where no product is an input.
 #define TLB_F32X2_OP(name, op)                                                                   \
     __device__ __forceinline__ float2 name(float2 a, float2 b) {                                 \
         float2 d;                                                                                \
@@ -142,16 +144,11 @@ __device__ __forceinline__ float2 add2_rz(float2 a, float2 b) { return make_floa
         return d;                                                                                \
     }
 TLB_F32X2_OP(mul2_rn, "mul.rn.f32x2")
-TLB_F32X2_OP(add2_rn, "add.rn.f32x2")
 TLB_F32X2_OP(add2_rz, "add.rz.f32x2")
 #undef TLB_F32X2_OP
-#endif
-// Packed FMA.  Used only where the fused result is exactly the wanted singly-rounded product
-// (see byte_product2).
+// Packed FMA.  Used only where the fused result is exactly the wanted singly-rounded value
+// (byte_product2, add2_exact).
 __device__ __forceinline__ float2 fma2_rn(float2 a, float2 b, float2 c) {
-#ifdef TLB_NO_PACKED
-    return make_float2(__fmaf_rn(a.x, b.x, c.x), __fmaf_rn(a.y, b.y, c.y));
-#endif
     float2 d;
     asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
         "mov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
@@ -170,21 +167,18 @@ __device__ __forceinline__ float2 byte_product2(unsigned b0, unsigned b1, float2
 }
 // Packed sum a + b where a is a packed product: issued as fma(a, one, b) with `one` = 1.0f
 // held in a register the assembler cannot see through (it comes from the kernel parameters).
-// a*1 is exact, so the result is RN(a + b) lane by lane; and because the instruction already
+// a*1 is exact, so the result is RN(a + b) half by half; and because the instruction already
 // is an FMA whose multiplicand is a finished (rounded) product, nothing can be contracted
-// into it.  This is what a packed add of products would be if it were safe (see above).
+// into it.
 __device__ __forceinline__ float2 add2_exact(float2 a, float2 b, float2 one) { return fma2_rn(a, one, b); }
 
-template <int DTYPE>
-struct OutT;
-template <>
-struct OutT<0> {
-    static constexpr int V = 4;
-};
-template <>
-struct OutT<1> {
-    static constexpr int V = 8;
-};
+// (x - mean) * inv_std for x = code*pre;  x - m == x + (-m) bit for bit.  floor(v) for 0 <= v < 2^22
+// needs no float->int->float round trip: adding 2^23 with round-toward-zero drops the fraction.  The
+// CPU path's clamp to [0,255] before its uint8 cast cannot change the code: v is a convex blend of
+// values in [0,255], so 0 <= v < 256 always.
+__device__ __forceinline__ float2 normalize2(float2 x, float2 neg_mean, float2 istd, float2 one) {
+    return mul2_rn(add2_exact(x, neg_mean, one), istd);
+}
 
 template <int DTYPE>
 __device__ __forceinline__ void store_scalar(void* out, long long idx, float v) {
@@ -193,49 +187,16 @@ __device__ __forceinline__ void store_scalar(void* out, long long idx, float v) 
     else
         static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
 }
-
-// One 16-byte store of V finished outputs (fp32: 4 values, bf16: 8 values rounded RNE).
 template <int DTYPE>
-__device__ __forceinline__ void store_chunk(char* ptr, const float2* v) {
-    if constexpr (DTYPE == 0) {
-        *reinterpret_cast<float4*>(ptr) = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
-    } else {
-        uint4 u;
-        __nv_bfloat162 a = __float22bfloat162_rn(v[0]);
-        __nv_bfloat162 b = __float22bfloat162_rn(v[1]);
-        __nv_bfloat162 c = __float22bfloat162_rn(v[2]);
-        __nv_bfloat162 d = __float22bfloat162_rn(v[3]);
-        u.x = *reinterpret_cast<uint32_t*>(&a);
-        u.y = *reinterpret_cast<uint32_t*>(&b);
-        u.z = *reinterpret_cast<uint32_t*>(&c);
-        u.w = *reinterpret_cast<uint32_t*>(&d);
-        *reinterpret_cast<uint4*>(ptr) = u;
-    }
+__device__ __forceinline__ void store1(char* ptr, float v) {
+    if constexpr (DTYPE == 0)
+        *reinterpret_cast<float*>(ptr) = v;
+    else
+        *reinterpret_cast<__nv_bfloat16*>(ptr) = __float2bfloat16_rn(v);
 }
-
-// Two outputs at once: blend of the two source rows, truncation to the 8-bit code and
-// normalization, each lane rounded exactly like the scalar sequence
-//   v = a*(1-dy) + b*dy;  code = floor(v);  out = (code*pre - mean) * inv_std.
-// floor(v) for 0 <= v < 2^22 without a float->int->float round trip: adding 2^23 with
-// round-toward-zero drops the fraction, subtracting it back is exact.  The CPU path's clamp
-// to [0,255] before its uint8 cast cannot change the code: v is a convex blend of values in
-// [0,255], so 0 <= v < 256 always.
-__device__ __forceinline__ float2 finish2(float2 a, float2 b, float2 idy, float2 dy, float2 pre, float2 neg_mean,
-                                          float2 istd, float2 one) {
-    const float2 k = f2(8388608.0f, 8388608.0f), nk = f2(-8388608.0f, -8388608.0f);
-    float2 v = add2_exact(mul2_rn(a, idy), mul2_rn(b, dy), one);
-    v = add2_rn(add2_rz(v, k), nk);                                        // floor(v)
-    return mul2_rn(add2_exact(mul2_rn(v, pre), neg_mean, one), istd);  // x - m == x + (-m) bit for bit
-}
-
-// Plain (release) arrival on an mbarrier.
-__device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar) : "memory");
-}
-
 // Everything the planner warp needs to plan a pass and issue its copies.
 struct PassCtx {
-    int ty0, ty1, iw, cx, cy, fx_lo, fw, Rr, Rh, pitch, rpi;
+    int ty0, ty1, iw, cx, cy, ch, fx_lo, fw, Rr, pitch;
     bool pairs;  // vertical downscale steeper than 2x: output rows share no source row
     const unsigned char* img;
     unsigned long long reg_lo, reg_hi;
@@ -244,59 +205,64 @@ struct PassCtx {
 // Planner state carried from one pass to the next (uniform across the warp).
 struct PassState {
     int yb;           // first output row of the next pass to plan
-    int staged_last;  // last source row already present in the strips' rings (contiguous mode), or -1
+    int staged_last;  // last virtual source row already handed to the compute warps (contiguous mode), or -1
     int index;        // number of passes planned so far
 };
 
 // Executed by all 32 lanes of the planner warp.  Plans the pass that starts at output row st.yb
-// from the per-tile row table: one lane per output row; the first row's y0 and the last row's
-// y1 are exchanged with warp shuffles to find the range of NEW source rows.  Writes the pass
-// record into slot (index % kSlots) of the header and issues one bulk copy per new source row
-// into raw buffer (index % kNBuf), completing on that buffer's "full" mbarrier.
-__device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, unsigned char* smem,
-                                               unsigned char* raw, int lane) {
-    const int slot3 = st.index % kSlots, buf = st.index % kNBuf;
+// from the per-tile row table, one lane per output row.  Output row y blends source rows y0 and
+// y0 + 1; row y0 + 1 may be the "virtual" row ch, which stands for a second copy of row ch - 1
+// (the bottom clamp), so that every output row needs two consecutive rows and the compute warps
+// need no special case.  In contiguous mode the virtual rows of a tile are staged consecutively,
+// each exactly once; the first row's y0 and the last row's y0 + 1 are exchanged with warp
+// shuffles to find the range of NEW rows.  The pass record {new rows, output rows to emit before
+// the first new row, last pass?} goes to slot (index % kSlots) of the header, together with one
+// record per new row {its byte offset in shared memory, output rows to emit once it has been
+// consumed}; one bulk copy per new row goes into raw buffer (index % kNBuf), completing on that
+// buffer's "full" mbarrier.
+__device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, unsigned char* smem, int lane) {
+    const int slot = st.index % kSlots, buf = st.index % kNBuf;
     int4* meta = reinterpret_cast<int4*>(smem + kSmemMeta);
-    int2* rowoff = reinterpret_cast<int2*>(smem + kSmemRowOff) + slot3 * 32;
-    const int2* rowy = reinterpret_cast<const int2*>(smem + kSmemRowY);
-    unsigned char* rawbuf = raw + buf * c.Rr * c.pitch;
+    int2* srcrec = reinterpret_cast<int2*>(smem + kSmemSrcRec) + slot * 32;
+    const int* rowy = reinterpret_cast<const int*>(smem + kSmemRowY);
+    const int buf_off = kSmemVar + buf * c.Rr * c.pitch;
     const uint32_t mbar = smem_addr(smem + kSmemFull + 8 * buf);
     const int yb = st.yb;
 
     const int y = yb + lane;
     const bool valid = y < c.ty1;
-    const int2 yy = rowy[min(y, c.ty1 - 1) - c.ty0];  // {y0, y1} of this lane's output row
-    int nrows, nnew, new_first = 0;
+    const int y0 = rowy[min(y, c.ty1 - 1) - c.ty0];
+    const int y1v = y0 + 1;  // second (possibly virtual) source row of this lane's output row
+    int nrows, nnew, new_first = 0, jlast;
     if (c.pairs) {
         nrows = min(c.Rr >> 1, min(c.ty1 - yb, 32));
-        if (nrows > c.rpi) nrows -= nrows % c.rpi;
         nnew = 2 * nrows;
+        jlast = 2 * lane + 1;
     } else {
-        const int first = __shfl_sync(0xffffffffu, yy.x, 0);
+        const int first = __shfl_sync(0xffffffffu, y0, 0);
         new_first = max(first, st.staged_last + 1);
-        // Output rows whose source rows fit among the Rr rows this pass may add form a prefix
-        // (y1 is non-decreasing in y).
-        const unsigned fits = __ballot_sync(0xffffffffu, valid && (yy.y - new_first + 1 <= c.Rr));
+        // Output rows whose rows fit among the Rr rows this pass may add form a prefix (y0 is
+        // non-decreasing in y); the first row always fits (it needs at most two new rows).
+        const unsigned fits = __ballot_sync(0xffffffffu, valid && (y1v - new_first + 1 <= c.Rr));
         nrows = __popc(fits);
-        // Whole groups of `rpi` rows keep every lane of the V step busy; the tile's tail is exempt.
-        if (nrows > c.rpi && yb + nrows < c.ty1) nrows -= nrows % c.rpi;
-        const int last_y1 = __shfl_sync(0xffffffffu, yy.y, nrows - 1);
-        nnew = max(last_y1 - new_first + 1, 0);
-        st.staged_last = max(st.staged_last, last_y1);
+        const int last_y1v = __shfl_sync(0xffffffffu, y1v, nrows - 1);
+        nnew = max(last_y1v - new_first + 1, 0);
+        st.staged_last = max(st.staged_last, last_y1v);
+        jlast = y1v - new_first;  // negative: both rows were consumed in an earlier pass
     }
+    const bool in_pass = lane < nrows;
+    const unsigned pre_mask = __ballot_sync(0xffffffffu, in_pass && jlast < 0);
     const int ynext = yb + nrows;
-    if (lane == 0) meta[slot3] = make_int4(nrows, nnew, ynext >= c.ty1 ? 1 : 0, yb);
+    if (lane == 0) meta[slot] = make_int4(nnew, __popc(pre_mask), ynext >= c.ty1 ? 1 : 0, 0);
+    // Output rows that become ready after new row j: lanes with the same jlast form a group.
+    const unsigned grp = __match_any_sync(0xffffffffu, (in_pass && jlast >= 0) ? jlast : 64 + lane);
+
     const int j = lane;  // new source row staged by this lane
-    const int ya = __shfl_sync(0xffffffffu, yy.x, j >> 1);
-    const int yc = __shfl_sync(0xffffffffu, yy.y, j >> 1);
-    const int srow = c.pairs ? ((j & 1) ? yc : ya) : (new_first + j);
-    // Ring position of a source row: its row number (contiguous mode) or its sequence number
-    // 2*(y - ty0) + {0,1} (pairs mode), modulo the ring depth -- the same rule the row table uses.
-    const int q0 = (c.pairs ? 2 * (yb - c.ty0) : new_first) % c.Rh;  // uniform
-    int q = q0 + j;
-    if (q >= c.Rh) q -= c.Rh;  // j < Rr < Rh
+    const int ya = __shfl_sync(0xffffffffu, y0, j >> 1);
+    const int srow = c.pairs ? ya + (j & 1) : min(new_first + j, c.ch - 1);
     unsigned bytes = 0;
     unsigned long long lo = 0, a0 = 0, a1 = 0, hi = 0;
+    unsigned char* row = smem + buf_off + j * c.pitch;
     if (j < nnew) {
         const unsigned off = (static_cast<unsigned>(c.cy + srow) * c.iw + (c.cx + c.fx_lo)) * 3u;
         a0 = reinterpret_cast<unsigned long long>(c.img) + off;
@@ -306,41 +272,43 @@ __device__ __forceinline__ void plan_and_issue(const PassCtx& c, PassState& st, 
         hi = (a1 + 15ull) & ~15ull;
         if (hi > c.reg_hi) hi = c.reg_hi & ~15ull;  // region does not end on the 16-byte grid
         bytes = hi > lo ? static_cast<unsigned>(hi - lo) : 0u;
-        rowoff[j] = make_int2(j * c.pitch + static_cast<int>(a0 & 15ull), q * kStripRowBytes);
+        srcrec[j] = make_int2(buf_off + j * c.pitch + static_cast<int>(a0 & 15ull), 0);
         // Ragged edges outside the 16-byte grid of the readable region (rare): plain loads, stored
         // before the arrival below so that the "full" barrier publishes them too.
-        unsigned char* slot = rawbuf + j * c.pitch;
-        const unsigned long long origin = a0 & ~15ull;  // global address of slot byte 0
+        const unsigned long long origin = a0 & ~15ull;  // global address of row byte 0
         const unsigned long long head_end = bytes ? lo : a1;
         for (unsigned long long a = a0; a < head_end && a < a1; ++a)
-            slot[a - origin] = *reinterpret_cast<const unsigned char*>(a);
+            row[a - origin] = *reinterpret_cast<const unsigned char*>(a);
         if (bytes)
             for (unsigned long long a = (hi > a0 ? hi : a0); a < a1; ++a)
-                slot[a - origin] = *reinterpret_cast<const unsigned char*>(a);
+                row[a - origin] = *reinterpret_cast<const unsigned char*>(a);
     }
+    __syncwarp();  // the per-row records exist before the group leaders add their counts
+    if (in_pass && jlast >= 0 && (__ffs(grp) - 1) == lane) srcrec[jlast].y = __popc(grp);
     unsigned total = bytes;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
     fence_proxy_async();  // earlier generic reads of this staging buffer precede the new copies
-    __syncwarp();         // the record and the row offsets are written before the arrival publishes them
+    __syncwarp();         // the records are written before the arrival publishes them
     if (lane == 0) mbar_arrive_expect_tx(mbar, total);
     __syncwarp();
-    if (j < nnew) {
-        unsigned char* slot = rawbuf + j * c.pitch;
-        const unsigned long long origin = a0 & ~15ull;  // global address of slot byte 0
-        if (bytes) bulk_copy_g2s(smem_addr(slot + (lo - origin)), reinterpret_cast<const void*>(lo), bytes, mbar);
+    if (j < nnew && bytes) {
+        const unsigned long long origin = a0 & ~15ull;
+        bulk_copy_g2s(smem_addr(row + (lo - origin)), reinterpret_cast<const void*>(lo), bytes, mbar);
     }
     st.yb = ynext;
     st.index += 1;
 }
 
-template <int DTYPE, int LAYOUT>
-__global__ void __launch_bounds__(32 * (kMaxTileCols / kStripCols + 1))
+#ifndef TLB_MIN_CTAS
+#define TLB_MIN_CTAS 3
+#endif
+
+template <int DTYPE, int LAYOUT, int CPL, bool JIT>
+__global__ void __launch_bounds__(32 * (kMaxStrips + 1), TLB_MIN_CTAS)
 fused_transform_kernel(const __grid_constant__ FusedParams p) {
-    constexpr int V = OutT<DTYPE>::V;       // outputs per 16-byte chunk
-    constexpr int G = kStripCols / V;       // pixel groups per strip row (8 fp32, 4 bf16)
-    constexpr int RPI = 32 / G;             // output rows one V step covers (4 fp32, 8 bf16)
     constexpr int ESZ = DTYPE == 0 ? 4 : 2;
+    constexpr int NP = CPL == 2 ? 3 : 2;  // packed pairs per lane: (colA, colB) x 3 channels, or (c0, c1), (c2, c2)
     extern __shared__ __align__(128) unsigned char smem[];
     const Plan& pl = p.plan;
     const int tid = threadIdx.x;
@@ -412,7 +380,7 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         const int fx_hi = min(hi0 + 1, cw - 1);
         fw = fx_hi - fx_lo + 1;
         own_pitch = (fw * 3 + 30 + 15) & ~15;
-        Rr = raw_rows_for(pl.smem_bytes - kSmemVar, own_pitch, strips);
+        Rr = raw_rows_for(pl.smem_bytes - kSmemVar, own_pitch);
         if (Rr < 2) bad = kDevTooWide;
     }
 
@@ -432,125 +400,259 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         return;
     }
 
-    // ---- carve the variable part of shared memory for this tile's footprint ----------
-    const int Rh = Rr + 2;  // ring depth: the new rows of a pass plus at most two carried rows
-    unsigned char* raw = smem + kSmemVar;                    // kNBuf buffers of Rr x own_pitch bytes
-    unsigned char* rings = raw + kNBuf * Rr * own_pitch;    // strips x Rh x kStripRowBytes
     const int4* meta = reinterpret_cast<const int4*>(smem + kSmemMeta);
 
     if (tid == 0) {
-        for (int b = 0; b < kNBuf; ++b) {
-            mbar_init(smem_addr(smem + kSmemFull + 8 * b), 1);
-            mbar_init(smem_addr(smem + kSmemEmpty + 8 * b), strips);
-        }
+        for (int b = 0; b < kNBuf; ++b) mbar_init(smem_addr(smem + kSmemFull + 8 * b), 1);
         fence_proxy_async();
     }
-    // ---- row table of the tile: one thread per output row, once ------------------------
-    const bool pairs = ch > 2 * H;  // steeper than 2x: every output row has its own two source rows
-    if (tid < ty1 - ty0) {
-        const int y = ty0 + tid;
-        const float sy = src_coord(y, yscale);
+    // ---- row table of the tile, once ---------------------------------------------------
+    // Output row y blends source rows y0 and y0 + 1 (see plan_and_issue for the virtual bottom
+    // row).  The compute warps keep the two most recent rows in two register buffers A and B and
+    // write the n-th row they consume (n = 0, 1, ... from the top of the tile) into buffer n & 1, so
+    // which buffer holds the row of weight dy is known here: the table stores the weight OF EACH
+    // BUFFER, and the blend a*(1-dy) + b*dy (a sum, so its order is free) needs no case split.
+    // Pairs mode (steeper than 2x): every output row consumes two fresh rows, y0 + 1 always lands in B.
+    const bool pairs = ch > 2 * H;
+    const int kbase = min(static_cast<int>(src_coord(ty0, yscale)), ch - 1);  // first row the tile consumes
+    for (int r = tid; r < ty1 - ty0; r += blockDim.x) {
+        const float sy = src_coord(ty0 + r, yscale);
         const int y0 = min(static_cast<int>(sy), ch - 1);
-        const int y1 = min(y0 + 1, ch - 1);
         const float dy = __fsub_rn(sy, static_cast<float>(y0));
-        // Ring slot of a source row: row number (or, in pairs mode, sequence number) modulo Rh.
-        const int q0 = pairs ? 2 * tid : y0;
-        const int q1 = pairs ? 2 * tid + 1 : y1;
-        reinterpret_cast<float4*>(smem + kSmemRowp)[tid] =
-            make_float4(__int_as_float((q0 % Rh) * kStripRowBytes), __int_as_float((q1 % Rh) * kStripRowBytes), dy,
-                        __fsub_rn(1.0f, dy));
-        reinterpret_cast<int2*>(smem + kSmemRowY)[tid] = make_int2(y0, y1);
+        const float idy = __fsub_rn(1.0f, dy);
+        const bool new_in_b = pairs || (((y0 + 1 - kbase) & 1) != 0);
+        const float wa = new_in_b ? idy : dy, wb = new_in_b ? dy : idy;
+        reinterpret_cast<float4*>(smem + kSmemRowW)[r] = make_float4(wa, wa, wb, wb);
+        reinterpret_cast<int*>(smem + kSmemRowY)[r] = y0;
     }
     __syncthreads();  // the only CTA-wide barrier: tables and mbarriers are ready
 
     if (warp == strips) {
         // ================= planner warp =================================================================
         PassCtx pc;
-        pc.ty0 = ty0; pc.ty1 = ty1; pc.iw = iw; pc.cx = cx; pc.cy = cy;
-        pc.fx_lo = fx_lo; pc.fw = fw; pc.Rr = Rr; pc.Rh = Rh; pc.pitch = own_pitch; pc.rpi = RPI;
+        pc.ty0 = ty0; pc.ty1 = ty1; pc.iw = iw; pc.cx = cx; pc.cy = cy; pc.ch = ch;
+        pc.fx_lo = fx_lo; pc.fw = fw; pc.Rr = Rr; pc.pitch = own_pitch;
         pc.pairs = pairs;
         pc.img = p.src + img_off;
-        pc.reg_lo = reinterpret_cast<unsigned long long>(p.src);
-        pc.reg_hi = pc.reg_lo + p.src_bytes;
+        // Readable region for the 16-byte round-out of the row copies: the whole source buffer, or,
+        // when the images are separate allocations, the image itself.
+        if (p.per_image_region) {
+            pc.reg_lo = reinterpret_cast<unsigned long long>(pc.img);
+            pc.reg_hi = pc.reg_lo + static_cast<unsigned long long>(iw) * ih * 3ull;
+        } else {
+            pc.reg_lo = reinterpret_cast<unsigned long long>(p.src);
+            pc.reg_hi = pc.reg_lo + p.src_bytes;
+        }
         PassState st;
         st.yb = ty0; st.staged_last = -1; st.index = 0;
-        for (int n = 0; n < kNBuf && st.yb < ty1; ++n) plan_and_issue(pc, st, smem, raw, lane);  // passes 0 .. kNBuf-1
+        const int cta_threads = 32 * (strips + 1);
+        for (int n = 0; n < kNBuf && st.yb < ty1; ++n) plan_and_issue(pc, st, smem, lane);  // passes 0 .. kNBuf-1
+        int released = 0;  // passes whose raw buffer the compute warps have handed back
         while (st.yb < ty1) {
-            // Pass n reuses the raw buffer of pass n - kNBuf: wait until every compute warp has
+            // Pass n reuses the raw buffer of pass n - kNBuf: block until every compute warp has
             // finished reading that buffer.
-            const int n = st.index;
-            const uint32_t mb = smem_addr(smem + kSmemEmpty + 8 * (n % kNBuf));
-            if (!mbar_wait_bounded(mb, static_cast<uint32_t>(n / kNBuf - 1) & 1u)) {
-                if (lane == 0 && p.status) atomicOr(p.status, kDevCopyTimeout);
-            }
-            plan_and_issue(pc, st, smem, raw, lane);
+            named_sync(1 + released % kNBuf, cta_threads);
+            ++released;
+            plan_and_issue(pc, st, smem, lane);
         }
+        // Match the remaining hand-backs, so that no barrier is left half-way when the CTA retires.
+        for (; released < st.index; ++released) named_sync(1 + released % kNBuf, cta_threads);
         return;
     }
 
-    // ================= compute warps: one 32-column strip each ===========================================
-    unsigned char* ring = rings + warp * Rh * kStripRowBytes;
-    // ---- H step ownership: one output column per lane, weights in registers ---------
-    const int hx = warp * kStripCols + lane;  // column inside the tile
-    int off0 = 0, off1 = 0;
-    float2 wx = f2(0.0f, 0.0f);                // (1-dx, dx)
-    const bool h_active = hx < tcw;
-    if (h_active) {
-        const int x = tx0 + hx;
-        const int ox = flip ? (W - 1 - x) : x;
-        const float sx = src_coord(ox, xscale);
-        const int x0 = min(static_cast<int>(sx), cw - 1);
-        const int x1 = min(x0 + 1, cw - 1);
-        const float dx = __fsub_rn(sx, static_cast<float>(x0));
-        off0 = (x0 - fx_lo) * 3;
-        off1 = (x1 - fx_lo) * 3;
-        wx = f2(__fsub_rn(1.0f, dx), dx);
+    // ================= compute warps: one strip each ======================================================
+    // ---- column ownership: lane l owns columns l and l + 32 of the strip (CPL = 2) --------------
+    // Neighbouring lanes read neighbouring source pixels, so the byte loads of a warp fall into
+    // distinct banks, and a warp's store covers 32 adjacent pixels.
+    const int colA = warp * (32 * CPL) + lane;  // inside the tile
+    const int colB = colA + 32;
+    const bool validA = colA < tcw;
+    const bool validB = CPL == 2 && colB < tcw;
+    int offA0 = 0, offA1 = 0, offB0 = 0, offB1 = 0;  // byte offsets of the source pixels inside a staged row
+    float2 W0 = f2(0.0f, 0.0f), W1 = f2(0.0f, 0.0f);  // (1-dx) and dx of the lane's pairs
+    {
+        auto column = [&](int hx, int& o0, int& o1, float& w0, float& w1) {
+            const int x = tx0 + hx;
+            const int ox = flip ? (W - 1 - x) : x;
+            const float sx = src_coord(ox, xscale);
+            const int x0 = min(static_cast<int>(sx), cw - 1);
+            const int x1 = min(x0 + 1, cw - 1);
+            const float dx = __fsub_rn(sx, static_cast<float>(x0));
+            o0 = (x0 - fx_lo) * 3;
+            o1 = (x1 - fx_lo) * 3;
+            w0 = __fsub_rn(1.0f, dx);
+            w1 = dx;
+        };
+        if (validA) column(colA, offA0, offA1, W0.x, W1.x);
+        if constexpr (CPL == 2) {
+            if (validB) column(colB, offB0, offB1, W0.y, W1.y);
+        } else {
+            W0.y = W0.x;
+            W1.y = W1.x;
+        }
     }
-    const float2 nwx = f2(__fmul_rn(-8388608.0f, wx.x), __fmul_rn(-8388608.0f, wx.y));
-    // Ring row layout.  NCHW: three planes of 32 floats.  NHWC: 32 x 3 interleaved floats.
-    float* const h_store = reinterpret_cast<float*>(ring) + (LAYOUT == 0 ? lane : 3 * lane);
-    // ---- V step ownership: V adjacent pixels x RPI rows per step ------------------------
-    const int vg = lane % G;
-    const int vr = lane / G;
-    const int px0 = warp * kStripCols + vg * V;  // first pixel of the group inside the tile
-    const bool v_active = px0 < tcw;
-    const bool v_full = pl.vec_ok && (px0 + V <= tcw);
-    const float2 pre2 = f2(p.pre_scale, p.pre_scale);
+    const float2 NW0 = f2(__fmul_rn(-8388608.0f, W0.x), __fmul_rn(-8388608.0f, W0.y));
+    const float2 NW1 = f2(__fmul_rn(-8388608.0f, W1.x), __fmul_rn(-8388608.0f, W1.y));
     const float2 one2 = f2(p.one, p.one);
-    long long obase;                              // element index of (row 0, this group) of the sample
+    const float2 pre2 = f2(p.pre_scale, p.pre_scale);
+    const float2 nkpre2 = f2(p.neg_k_pre, p.neg_k_pre);
+    const float2 k2 = f2(8388608.0f, 8388608.0f);
+    // Normalization constants of the NP pairs.
+    float2 nmean2[NP], istd2[NP];
+    if constexpr (CPL == 2) {
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            nmean2[c] = f2(-p.mean[c], -p.mean[c]);
+            istd2[c] = f2(p.inv_std[c], p.inv_std[c]);
+        }
+    } else {
+        nmean2[0] = f2(-p.mean[0], -p.mean[1]);
+        nmean2[1] = f2(-p.mean[2], -p.mean[2]);
+        istd2[0] = f2(p.inv_std[0], p.inv_std[1]);
+        istd2[1] = f2(p.inv_std[2], p.inv_std[2]);
+    }
+    // Colour jitter factors of this sample (uniform across the CTA).
+    float jb = 1.0f, jc = 1.0f, js = 1.0f;
+    if constexpr (JIT) {
+        jb = p.jitter[3 * static_cast<long long>(k)];
+        jc = p.jitter[3 * static_cast<long long>(k) + 1];
+        js = p.jitter[3 * static_cast<long long>(k) + 2];
+    }
+
+    // ---- output addressing: one pointer per channel plane (NCHW) or one in all (NHWC) ----------
+    long long obase;  // element index of (row ty0, column A) of the sample
     if constexpr (LAYOUT == 0)
-        obase = static_cast<long long>(k) * 3 * H * W + tx0 + px0;
+        obase = (static_cast<long long>(k) * 3 * H + ty0) * W + tx0 + colA;
     else
-        obase = (static_cast<long long>(k) * H * W + tx0 + px0) * 3;
-    // Byte offset of this group's first 16-byte chunk inside a ring row (plane 0 for NCHW).
-    const unsigned char* const h_load = ring + (LAYOUT == 0 ? vg * V * 4 : vg * V * 12);
-    void* const outp = p.out;
-    char* const obytes = static_cast<char*>(p.out) + obase * ESZ;
+        obase = ((static_cast<long long>(k) * H + ty0) * W + tx0 + colA) * 3;
+    char* o0 = static_cast<char*>(p.out) + obase * ESZ;
     const long long row_bytes = static_cast<long long>(W) * ESZ * (LAYOUT == 0 ? 1 : 3);
     const long long chan_bytes = static_cast<long long>(H) * W * ESZ;  // NCHW plane stride
-    const float4* const rowp_tile = reinterpret_cast<const float4*>(smem + kSmemRowp);
+    char* o1 = o0 + chan_bytes;
+    char* o2 = o1 + chan_bytes;
+    constexpr int kColB = LAYOUT == 0 ? 32 * ESZ : 96 * ESZ;  // byte distance of column B's pixel
+    const float4* roww = reinterpret_cast<const float4*>(smem + kSmemRowW);
 
-    // One 16-byte chunk q of an output row: blend the two ring rows ra / rb, truncate, normalize.
-    // NCHW: chunk q = channel q of the group's V pixels.  NHWC: chunk q = elements [q*V, q*V+V) of
-    // the group's 3V interleaved elements (element e has channel e % 3).
-    auto chunk = [&](const unsigned char* ra, const unsigned char* rb, float2 idy2, float2 dy2, auto qc, float2* v) {
-        constexpr int q = decltype(qc)::value;
+    float2 hA[NP], hB[NP];
 #pragma unroll
-        for (int i = 0; i < V / 4; ++i) {
-            constexpr int base = LAYOUT == 0 ? q * kStripCols * 4 : q * V * 4;
-            const float4 a = *reinterpret_cast<const float4*>(ra + base + 16 * i);
-            const float4 b = *reinterpret_cast<const float4*>(rb + base + 16 * i);
-            const int c0 = LAYOUT == 0 ? q : (q * V + 4 * i + 0) % 3;
-            const int c1 = LAYOUT == 0 ? q : (q * V + 4 * i + 1) % 3;
-            const int c2 = LAYOUT == 0 ? q : (q * V + 4 * i + 2) % 3;
-            const int c3 = LAYOUT == 0 ? q : (q * V + 4 * i + 3) % 3;
-            v[2 * i] = finish2(f2(a.x, a.y), f2(b.x, b.y), idy2, dy2, pre2, f2(-p.mean[c0], -p.mean[c1]),
-                               f2(p.inv_std[c0], p.inv_std[c1]), one2);
-            v[2 * i + 1] = finish2(f2(a.z, a.w), f2(b.z, b.w), idy2, dy2, pre2, f2(-p.mean[c2], -p.mean[c3]),
-                                   f2(p.inv_std[c2], p.inv_std[c3]), one2);
+    for (int i = 0; i < NP; ++i) hA[i] = hB[i] = f2(0.0f, 0.0f);
+
+    // H step: one staged source row -> the lane's horizontally interpolated values.
+    auto hstep = [&](const unsigned char* row, float2* h) {
+        const unsigned char* a0 = row + offA0;
+        const unsigned char* a1 = row + offA1;
+        if constexpr (CPL == 2) {
+            const unsigned char* b0 = row + offB0;
+            const unsigned char* b1 = row + offB1;
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                const float2 t0 = byte_product2(a0[c], b0[c], W0, NW0);
+                const float2 t1 = byte_product2(a1[c], b1[c], W1, NW1);
+                h[c] = add2_exact(t0, t1, one2);
+            }
+        } else {
+            const unsigned p0 = a0[0], p1 = a0[1], p2 = a0[2], q0 = a1[0], q1 = a1[1], q2 = a1[2];
+            h[0] = add2_exact(byte_product2(p0, p1, W0, NW0), byte_product2(q0, q1, W1, NW1), one2);
+            h[1] = add2_exact(byte_product2(p2, p2, W0, NW0), byte_product2(q2, q2, W1, NW1), one2);
         }
     };
 
+    // One output row: blend the two row buffers with the row's weights, truncate, (jitter,) normalize,
+    // store.  Lanes without a column compute on zeros and only skip the stores.
+    auto vrow = [&](const float4 w) {  // {wA, wA, wB, wB}
+        const float2 wa2 = f2(w.x, w.y), wb2 = f2(w.z, w.w);
+        float2 v[NP];
+#pragma unroll
+        for (int q = 0; q < NP; ++q) {
+            // v = a*(1-dy) + b*dy;  code = floor(v) as RZ(v + 2^23) - 2^23;  x = code*pre.  The last two
+            // steps are one fma((2^23 + code), pre, -2^23*pre): exact product, one rounding.
+            const float2 blend = add2_exact(mul2_rn(hA[q], wa2), mul2_rn(hB[q], wb2), one2);
+            v[q] = fma2_rn(add2_rz(blend, k2), pre2, nkpre2);
+        }
+        if constexpr (JIT) {
+            // Colour jitter on rgb = code/255 in the order of the reference's train_transform shader
+            // (src/metal/metal_transforms.mm:111-115), every operation rounded separately: brightness,
+            // contrast about 0.5, saturation as lum + (rgb-lum)*s with lum = (0.299 r + 0.587 g) + 0.114 b,
+            // clamp to [0,1].
+            float r[CPL][3];
+#pragma unroll
+            for (int e = 0; e < CPL; ++e) {
+                if constexpr (CPL == 2) {
+                    r[e][0] = e ? v[0].y : v[0].x;
+                    r[e][1] = e ? v[1].y : v[1].x;
+                    r[e][2] = e ? v[2].y : v[2].x;
+                } else {
+                    r[e][0] = v[0].x; r[e][1] = v[0].y; r[e][2] = v[1].x;
+                }
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    float x = __fmul_rn(r[e][c], jb);
+                    x = __fadd_rn(__fmul_rn(__fsub_rn(x, 0.5f), jc), 0.5f);
+                    r[e][c] = x;
+                }
+                const float lum = __fadd_rn(__fadd_rn(__fmul_rn(r[e][0], 0.299f), __fmul_rn(r[e][1], 0.587f)),
+                                            __fmul_rn(r[e][2], 0.114f));
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    float x = __fadd_rn(lum, __fmul_rn(__fsub_rn(r[e][c], lum), js));
+                    r[e][c] = fminf(fmaxf(x, 0.0f), 1.0f);
+                }
+            }
+            if constexpr (CPL == 2) {
+#pragma unroll
+                for (int c = 0; c < 3; ++c) v[c] = f2(r[0][c], r[1][c]);
+            } else {
+                v[0] = f2(r[0][0], r[0][1]);
+                v[1] = f2(r[0][2], r[0][2]);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < NP; ++q) v[q] = normalize2(v[q], nmean2[q], istd2[q], one2);
+        // ---- store: per channel the warp covers 32 adjacent pixels (twice for CPL = 2) ----
+        if constexpr (CPL == 2) {
+            if constexpr (LAYOUT == 0) {
+                if (validA) {
+                    store1<DTYPE>(o0, v[0].x);
+                    store1<DTYPE>(o1, v[1].x);
+                    store1<DTYPE>(o2, v[2].x);
+                }
+                if (validB) {
+                    store1<DTYPE>(o0 + kColB, v[0].y);
+                    store1<DTYPE>(o1 + kColB, v[1].y);
+                    store1<DTYPE>(o2 + kColB, v[2].y);
+                }
+            } else {
+                if (validA) {
+                    store1<DTYPE>(o0, v[0].x);
+                    store1<DTYPE>(o0 + ESZ, v[1].x);
+                    store1<DTYPE>(o0 + 2 * ESZ, v[2].x);
+                }
+                if (validB) {
+                    store1<DTYPE>(o0 + kColB, v[0].y);
+                    store1<DTYPE>(o0 + kColB + ESZ, v[1].y);
+                    store1<DTYPE>(o0 + kColB + 2 * ESZ, v[2].y);
+                }
+            }
+        } else if (validA) {
+            if constexpr (LAYOUT == 0) {
+                store1<DTYPE>(o0, v[0].x);
+                store1<DTYPE>(o1, v[0].y);
+                store1<DTYPE>(o2, v[1].x);
+            } else {
+                store1<DTYPE>(o0, v[0].x);
+                store1<DTYPE>(o0 + ESZ, v[0].y);
+                store1<DTYPE>(o0 + 2 * ESZ, v[1].x);
+            }
+        }
+        o0 += row_bytes;
+        if constexpr (LAYOUT == 0) {
+            o1 += row_bytes;
+            o2 += row_bytes;
+        }
+    };
+
+    const int cta_threads = 32 * (strips + 1);
+    bool next_in_b = false;  // buffer the next consumed row goes to (uniform across the warp)
     for (int i = 0;; ++i) {
         // ---- wait for the raw rows of pass i ---------------------------------------------
         const int b = i % kNBuf;
@@ -563,95 +665,31 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
             if (lane == 0 && p.status) atomicOr(p.status, kDevCopyTimeout);
             mbar_wait_bounded(full, full_parity);
         }
-        const int4 m = meta[i % kSlots];  // {output rows, new source rows, last?, first output row}
+        const int4 m = meta[i % kSlots];  // {new source rows, output rows before the first, last?, -}
+        const int2* srcrec = reinterpret_cast<const int2*>(smem + kSmemSrcRec) + (i % kSlots) * 32;
+        const int2* const srcend = srcrec + m.x;
 
-        // ---- H step: new source rows -> horizontally interpolated fp32 in the strip's ring ----
-        if (h_active) {
-            const unsigned char* rawb = raw + b * Rr * own_pitch;
-            const int2* rowoff = reinterpret_cast<const int2*>(smem + kSmemRowOff) + (i % kSlots) * 32;
-#pragma unroll kHUnroll
-            for (int j = 0; j < m.y; ++j) {
-                const int2 ro = rowoff[j];  // {raw byte offset of the row, byte offset of its ring slot}
-                const unsigned char* q0 = rawb + off0 + ro.x;
-                const unsigned char* q1 = rawb + off1 + ro.x;
-                const float2 t0 = byte_product2(q0[0], q1[0], wx, nwx);
-                const float2 t1 = byte_product2(q0[1], q1[1], wx, nwx);
-                const float2 t2 = byte_product2(q0[2], q1[2], wx, nwx);
-                float* h = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(h_store) + ro.y);
-                if constexpr (LAYOUT == 0) {
-                    h[0] = __fadd_rn(t0.x, t0.y);
-                    h[kStripCols] = __fadd_rn(t1.x, t1.y);
-                    h[2 * kStripCols] = __fadd_rn(t2.x, t2.y);
-                } else {
-                    h[0] = __fadd_rn(t0.x, t0.y);
-                    h[1] = __fadd_rn(t1.x, t1.y);
-                    h[2] = __fadd_rn(t2.x, t2.y);
-                }
-            }
+        for (int emit = m.y; emit > 0; --emit) vrow(*roww++);  // rows whose source rows came earlier
+        while (srcrec != srcend) {
+            const int2 rec = *srcrec++;  // {byte offset of the staged row, output rows ready after it}
+            if (next_in_b)
+                hstep(smem + rec.x, hB);
+            else
+                hstep(smem + rec.x, hA);
+            next_in_b = !next_in_b;
+            for (int emit = rec.y; emit > 0; --emit) vrow(*roww++);
         }
-        __syncwarp();  // the strip's new h rows are visible to the whole warp; raw reads are done
-        if (lane == 0) mbar_arrive(smem_addr(smem + kSmemEmpty + 8 * b));  // this warp is done with raw buffer b
-
-        // ---- V step: blend, truncate, normalize, store --------------------------------------
-        if (v_active) {
-            const float4* rowp = rowp_tile + (m.w - ty0);
-            if (v_full) {
-                char* orow = obytes + (m.w + vr) * row_bytes;
-                const long long ostep = RPI * row_bytes;
-                for (int l = vr; l < m.x; l += RPI, orow += ostep) {
-                    const float4 rp = rowp[l];  // {ring byte offset of y0 row, of y1 row, dy, 1-dy}
-                    const float2 dy2 = f2(rp.z, rp.z), idy2 = f2(rp.w, rp.w);
-                    const unsigned char* ra = h_load + __float_as_int(rp.x);
-                    const unsigned char* rb = h_load + __float_as_int(rp.y);
-                    float2 v[V / 2];
-                    chunk(ra, rb, idy2, dy2, std::integral_constant<int, 0>{}, v);
-                    store_chunk<DTYPE>(orow, v);
-                    chunk(ra, rb, idy2, dy2, std::integral_constant<int, 1>{}, v);
-                    store_chunk<DTYPE>(orow + (LAYOUT == 0 ? chan_bytes : 16), v);
-                    chunk(ra, rb, idy2, dy2, std::integral_constant<int, 2>{}, v);
-                    store_chunk<DTYPE>(orow + (LAYOUT == 0 ? 2 * chan_bytes : 32), v);
-                }
-            } else {
-                // Ragged or unaligned rows: element-wise guarded stores.
-                for (int l = vr; l < m.x; l += RPI) {
-                    const float4 rp = rowp[l];
-                    const float2 dy2 = f2(rp.z, rp.z), idy2 = f2(rp.w, rp.w);
-                    const unsigned char* ra = h_load + __float_as_int(rp.x);
-                    const unsigned char* rb = h_load + __float_as_int(rp.y);
-                    const int y = m.w + l;
-                    auto emit = [&](auto qc) {
-                        constexpr int q = decltype(qc)::value;
-                        float2 v[V / 2];
-                        chunk(ra, rb, idy2, dy2, qc, v);
-                        long long idx;
-                        if constexpr (LAYOUT == 0)
-                            idx = obase + static_cast<long long>((q * H + y) * W);
-                        else
-                            idx = obase + static_cast<long long>(y) * W * 3 + q * V;
-#pragma unroll
-                        for (int e = 0; e < V; ++e) {
-                            const float val = (e & 1) ? v[e >> 1].y : v[e >> 1].x;
-                            const bool in = LAYOUT == 0 ? (px0 + e < tcw) : (3 * px0 + q * V + e < 3 * tcw);
-                            if (in) store_scalar<DTYPE>(outp, idx + e, val);
-                        }
-                    };
-                    emit(std::integral_constant<int, 0>{});
-                    emit(std::integral_constant<int, 1>{});
-                    emit(std::integral_constant<int, 2>{});
-                }
-            }
-        }
+        __syncwarp();                      // every lane is done reading raw buffer b
+        named_arrive(1 + b, cta_threads);  // hand it back to the planner
         if (m.z) break;
-        __syncwarp();  // every lane has consumed pass i before the ring slots are rewritten
     }
 }
 
 std::atomic<unsigned long long> g_launches{0};
-std::atomic<int> g_overlap{0};
 
-template <int DTYPE, int LAYOUT>
-int launch_one(const FusedParams& p, cudaStream_t st, bool may_overlap) {
-    auto kern = fused_transform_kernel<DTYPE, LAYOUT>;
+template <int DTYPE, int LAYOUT, int CPL, bool JIT>
+int launch_one(const FusedParams& p, cudaStream_t st, unsigned flags) {
+    auto kern = fused_transform_kernel<DTYPE, LAYOUT, CPL, JIT>;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(p.plan.grid));
     cfg.blockDim = dim3(32 * (p.plan.strips + 1));
@@ -661,41 +699,56 @@ int launch_one(const FusedParams& p, cudaStream_t st, bool may_overlap) {
     // is a launch of this same kernel (which signals early, see the top of the kernel), this one
     // may begin while that one drains its last CTAs; the head and tail of back-to-back batches
     // then overlap instead of leaving SMs idle.  Behind a copy, a memset or a kernel that does not
-    // signal early the usual stream order holds.  The caller opts in (tlb_set_launch_overlap)
-    // because the kernel does not wait on its predecessor: see the header for the condition.
+    // signal early the usual stream order holds.  Requested per call, because the kernel does not
+    // wait on its predecessor.
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = (may_overlap && g_overlap.load(std::memory_order_relaxed)) ? 1 : 0;
+    cfg.numAttrs = (flags & kLaunchOverlap) ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kern, p);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return static_cast<int>(cudaGetLastError());
 }
 
-template <int DTYPE, int LAYOUT>
+template <int DTYPE, int LAYOUT, int CPL, bool JIT>
 int opt_in_smem() {
-    return static_cast<int>(cudaFuncSetAttribute(fused_transform_kernel<DTYPE, LAYOUT>,
+    return static_cast<int>(cudaFuncSetAttribute(fused_transform_kernel<DTYPE, LAYOUT, CPL, JIT>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+}
+
+template <int DTYPE, int LAYOUT>
+int launch_dl(const FusedParams& p, cudaStream_t st, unsigned flags) {
+    const bool jit = p.jitter != nullptr;
+    if (p.plan.cpl == 2)
+        return jit ? launch_one<DTYPE, LAYOUT, 2, true>(p, st, flags) : launch_one<DTYPE, LAYOUT, 2, false>(p, st, flags);
+    return jit ? launch_one<DTYPE, LAYOUT, 1, true>(p, st, flags) : launch_one<DTYPE, LAYOUT, 1, false>(p, st, flags);
+}
+
+template <int DTYPE, int LAYOUT>
+int opt_in_dl() {
+    int e = opt_in_smem<DTYPE, LAYOUT, 1, false>();
+    if (!e) e = opt_in_smem<DTYPE, LAYOUT, 1, true>();
+    if (!e) e = opt_in_smem<DTYPE, LAYOUT, 2, false>();
+    if (!e) e = opt_in_smem<DTYPE, LAYOUT, 2, true>();
+    return e;
 }
 
 }  // namespace
 
 int prepare_device() {
-    int e = opt_in_smem<0, 0>();
-    if (!e) e = opt_in_smem<0, 1>();
-    if (!e) e = opt_in_smem<1, 0>();
-    if (!e) e = opt_in_smem<1, 1>();
+    int e = opt_in_dl<0, 0>();
+    if (!e) e = opt_in_dl<0, 1>();
+    if (!e) e = opt_in_dl<1, 0>();
+    if (!e) e = opt_in_dl<1, 1>();
     return e;
 }
 
-int launch_fused(const FusedParams& p, int out_dtype, int out_layout, void* stream, bool may_overlap) {
+int launch_fused(const FusedParams& p, int out_dtype, int out_layout, void* stream, unsigned flags) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (out_dtype == 0) return out_layout == 0 ? launch_one<0, 0>(p, st, may_overlap) : launch_one<0, 1>(p, st, may_overlap);
-    return out_layout == 0 ? launch_one<1, 0>(p, st, may_overlap) : launch_one<1, 1>(p, st, may_overlap);
+    if (out_dtype == 0) return out_layout == 0 ? launch_dl<0, 0>(p, st, flags) : launch_dl<0, 1>(p, st, flags);
+    return out_layout == 0 ? launch_dl<1, 0>(p, st, flags) : launch_dl<1, 1>(p, st, flags);
 }
-
-int set_launch_overlap(int enable) { return g_overlap.exchange(enable ? 1 : 0, std::memory_order_relaxed); }
 
 unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 

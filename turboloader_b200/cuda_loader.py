@@ -11,7 +11,8 @@ Additions that default to the reference behaviour: ``crop_size`` / ``output_size
 ``dtype`` (float32 | bfloat16), ``channels_last``, and ``state_dict`` /
 ``load_state_dict`` with the same dict the CPU loaders use
 (turboloader/__init__.py:689-700).  Unlike the reference there is no per-batch
-synchronisation: batches are enqueued on the current stream.
+synchronisation: the library prefetches batches on its own stream (``tlb_epoch_*``) and the
+consumer's current stream is made to wait for each batch as it is handed out.
 """
 from __future__ import annotations
 
@@ -27,9 +28,12 @@ __all__ = ["CudaResidentLoader", "_CudaArray"]
 class _CudaArray:
     """A CUDA device pointer as a ``__cuda_array_interface__`` v3 float32 array
     (turboloader/cuda_loader.py:37-55) so torch/cupy adopt it without a copy:
-    ``torch.as_tensor(x, device='cuda')``.  ``owner`` keeps the backing allocation alive."""
+    ``torch.as_tensor(x, device='cuda')``.  ``owner`` keeps the backing allocation alive.
+    It also speaks DLPack (``__dlpack__`` / ``__dlpack_device__``), so ``torch.from_dlpack(x)``,
+    ``cupy.from_dlpack(x)`` or ``jax.dlpack.from_dlpack(x)`` adopt the same memory; bfloat16 and
+    channels-last batches are handed out as torch tensors, whose own ``__dlpack__`` serves those."""
 
-    def __init__(self, ptr, shape, owner=None, stream=None):
+    def __init__(self, ptr, shape, owner=None, stream=None, device=None):
         self.__cuda_array_interface__ = {
             "data": (int(ptr), False),
             "shape": tuple(int(s) for s in shape),
@@ -39,6 +43,7 @@ class _CudaArray:
         if stream is not None:
             self.__cuda_array_interface__["stream"] = int(stream)
         self._owner = owner
+        self._device = device
 
     @property
     def shape(self):
@@ -47,24 +52,29 @@ class _CudaArray:
     def __len__(self):
         return self.shape[0]
 
+    def _device_index(self):
+        if self._device is None:
+            import torch
+            self._device = torch.cuda.current_device()
+        return int(self._device)
+
+    def __dlpack_device__(self):
+        return (2, self._device_index())  # (kDLCUDA, ordinal)
+
+    def __dlpack__(self, stream=None, **kwargs):
+        """Zero-copy DLPack capsule of the same device memory (the capsule keeps this object, and
+        with it the backing allocation, alive)."""
+        import torch
+        t = torch.as_tensor(self, device=torch.device("cuda", self._device_index()))
+        return t.__dlpack__(stream=stream) if stream is not None else t.__dlpack__()
+
 
 class CudaResidentLoader:
     def __init__(self, paths, image_size=160, batch_size=64, *, mean=ops.IMAGENET_MEAN, std=ops.IMAGENET_STD,
                  drop_last=True, num_workers=8, shuffle=False, seed=42, return_indices=False, **extra):
-        from concurrent.futures import ThreadPoolExecutor
+        from .tbl import decode_to_array
 
-        from PIL import Image
-
-        paths = list(paths)
-        H = W = int(image_size)
-        arr = np.empty((len(paths), H, W, 3), dtype=np.uint8)
-
-        def _load(i):
-            with Image.open(paths[i]) as im:
-                arr[i] = np.asarray(im.convert("RGB").resize((W, H)))
-
-        with ThreadPoolExecutor(max_workers=max(1, int(num_workers))) as ex:
-            list(ex.map(_load, range(len(paths))))
+        arr = decode_to_array(paths, int(image_size), int(image_size), workers=num_workers)
         self._init_common(arr, batch_size, mean=mean, std=std, drop_last=drop_last, shuffle=shuffle, seed=seed,
                           return_indices=return_indices, **extra)
 
@@ -91,7 +101,7 @@ class CudaResidentLoader:
     def _init_common(self, array, batch_size, *, mean=ops.IMAGENET_MEAN, std=ops.IMAGENET_STD, drop_last=True,
                      shuffle=False, seed=42, return_indices=False, crop_size=None, output_size=None,
                      hflip_prob=0.0, boxes=None, dtype=None, channels_last=False, as_tensor=None, labels=None,
-                     ring=4, device=None, flips=None, train_aug=False, antialias=False):
+                     ring=8, device=None, flips=None, train_aug=False, antialias=False, jitter=None):
         import torch
 
         if not ops.cuda_available():
@@ -149,8 +159,14 @@ class CudaResidentLoader:
         plain = self.dtype == torch.float32 and not self.channels_last
         self._as_tensor = (not plain) if as_tensor is None else bool(as_tensor) or not plain
         self._labels = None if labels is None else torch.as_tensor(np.asarray(labels), dtype=torch.int64).to(self._device)
-        self._ring = [None] * max(2, int(ring))
-        self._ring_pos = 0
+        # Batches are prefetched on a stream of the library: `ring` output slots, `ahead` batches in
+        # flight beyond the one handed out, enqueued `group` at a time (so that launches overlap head to
+        # tail).  A batch stays valid for ring - ahead - group further batches (3 by default).
+        self._ring_slots = max(3, int(ring))
+        self._group = 2 if self._ring_slots >= 6 else 1
+        self._ahead = max(self._group, (self._ring_slots - self._group) // 2)
+        self._ring = None
+        self._jitter_fn = jitter  # callable(epoch, order) -> float32[len(order), 3] (brightness, contrast, saturation), or None
         self._epoch = 0
         self._resume_batches = 0
         self._batches_served = 0
@@ -190,22 +206,9 @@ class CudaResidentLoader:
             return np.zeros(self._n, dtype=np.uint8)
         return (np.random.default_rng([self.seed, e, 7]).random(self._n) < self.hflip_prob).astype(np.uint8)
 
-    def _out_buffer(self, n):
-        torch = self._torch
-        shape = (n, self._oh, self._ow, 3) if self.channels_last else (n, 3, self._oh, self._ow)
-        slot = self._ring_pos
-        self._ring_pos = (slot + 1) % len(self._ring)
-        buf = self._ring[slot]
-        if buf is None or buf.shape[0] < self.batch_size:
-            full = (self.batch_size,) + shape[1:]
-            buf = torch.empty(full, dtype=self.dtype, device=self._device)
-            self._ring[slot] = buf
-        return buf[:n]
-
     def __iter__(self):
         torch = self._torch
         bs = self.batch_size
-        end = (self._n // bs) * bs if self.drop_last else self._n
         order = self.epoch_order()
         aug_boxes = None
         if self._train_aug:
@@ -218,7 +221,9 @@ class CudaResidentLoader:
                 raise ValueError("flips callable must return one flag per epoch position")
         else:
             flips = self.epoch_flips()
+        lib = _capi.load()
         with torch.cuda.device(self._device):
+            # ---- whole-epoch tables on the device, once -----------------------------------------
             d_order = torch.from_numpy(order).to(self._device) if self.shuffle else None
             d_flips = torch.from_numpy(flips).to(self._device) if (self.hflip_prob > 0.0 or self._flips_fn is not None) else None
             d_boxes = None
@@ -234,66 +239,84 @@ class CudaResidentLoader:
                 max_cw = int(b[:, 2].max())
             else:
                 max_cw = self._box[2]
-            d_idx_ring = [torch.empty(bs, dtype=torch.int64, device=self._device) for _ in self._ring] \
-                if (self.return_indices and self.shuffle) else None
-            d_lab_ring = [torch.empty(bs, dtype=torch.int64, device=self._device) for _ in self._ring] \
-                if self._labels is not None else None
-            lib = _capi.load()
-            start = self._resume_batches * bs
-            self._batches_served = self._resume_batches
+            d_jit = None
+            if self._jitter_fn is not None:
+                j = np.ascontiguousarray(self._jitter_fn(self._epoch, order), dtype=np.float32).reshape(-1, 3)
+                if j.shape[0] != self._n:
+                    raise ValueError("jitter callable must return one (brightness, contrast, saturation) per epoch position")
+                d_jit = torch.from_numpy(j).to(self._device)
+            # ---- output ring: slot s of every buffer belongs to batch b with b % ring == s --------
+            R = self._ring_slots
+            shape = (bs, self._oh, self._ow, 3) if self.channels_last else (bs, 3, self._oh, self._ow)
+            if self._ring is None or tuple(self._ring.shape) != (R,) + shape:
+                self._ring = torch.empty((R,) + shape, dtype=self.dtype, device=self._device)
+            ring = self._ring
+            want_idx = self.return_indices and self.shuffle
+            idx_ring = torch.empty((R, bs), dtype=torch.int64, device=self._device) if want_idx else None
+            lab_ring = torch.empty((R, bs), dtype=torch.int64, device=self._device) if self._labels is not None else None
+            # ---- batch 0 as the fused transform takes it; the library walks the epoch from there ----
+            d = _capi.TransformDesc()
+            d.src = self._gpu.data_ptr()
+            d.src_bytes = self._gpu.numel()
+            d.n_src = self._n
+            d.src_w, d.src_h = self._W, self._H
+            d.n = bs
+            if d_order is not None:
+                d.sel = d_order.data_ptr()
+            if d_boxes is not None:
+                d.boxes = d_boxes.data_ptr()
+            else:
+                d.uniform_box = (C.c_int32 * 4)(*self._box)
+            if d_flips is not None:
+                d.flips = d_flips.data_ptr()
+            if d_jit is not None:
+                d.jitter = d_jit.data_ptr()
+            d.dst_h, d.dst_w = self._oh, self._ow
+            d.out = ring.data_ptr()
+            d.out_dtype = _capi.TLB_F32 if self.dtype == torch.float32 else _capi.TLB_BF16
+            d.out_layout = _capi.TLB_NHWC if self.channels_last else _capi.TLB_NCHW
+            if idx_ring is not None:
+                d.out_indices = idx_ring.data_ptr()
+            if lab_ring is not None:
+                d.labels_in = self._labels.data_ptr()
+                d.labels_out = lab_ring.data_ptr()
+            d.mean = _capi.f3(self.mean)
+            d.std = _capi.f3(self.std)
+            d.normalize_01 = 1
+            d.max_crop_w = max_cw
+            d.antialias = int(self.antialias)
+            d.status = self._status.data_ptr()
+            start = self._resume_batches
+            self._batches_served = start
             self._resume_batches = 0
-            stride = self._H * self._W * 3
-            for b0 in range(start, end, bs):
-                n = min(bs, self._n - b0)
-                out = self._out_buffer(n)
-                slot = (self._ring_pos - 1) % len(self._ring)
-                d = _capi.TransformDesc()
-                if d_order is not None:
-                    d.src = self._gpu.data_ptr()
-                    d.src_bytes = self._gpu.numel()
-                    d.n_src = self._n
-                    d.sel = d_order.data_ptr() + 8 * b0
-                else:  # sequential: the batch is a contiguous slice of the dataset
-                    d.src = self._gpu.data_ptr() + b0 * stride
-                    d.src_bytes = n * stride
-                    d.n_src = n
-                d.src_w, d.src_h = self._W, self._H
-                d.n = n
-                if d_boxes is not None:
-                    d.boxes = d_boxes.data_ptr() + 16 * b0
-                else:
-                    d.uniform_box = (C.c_int32 * 4)(*self._box)
-                if d_flips is not None:
-                    d.flips = d_flips.data_ptr() + b0
-                d.dst_h, d.dst_w = self._oh, self._ow
-                d.out = out.data_ptr()
-                d.out_dtype = _capi.TLB_F32 if self.dtype == torch.float32 else _capi.TLB_BF16
-                d.out_layout = _capi.TLB_NHWC if self.channels_last else _capi.TLB_NCHW
-                if d_idx_ring is not None:
-                    d.out_indices = d_idx_ring[slot].data_ptr()
-                if d_lab_ring is not None:
-                    d.labels_in = self._labels.data_ptr()
-                    d.labels_out = d_lab_ring[slot].data_ptr()
-                    if d_order is None:  # labels of a sequential slice start at b0
-                        d.labels_in = self._labels.data_ptr() + 8 * b0
-                d.mean = _capi.f3(self.mean)
-                d.std = _capi.f3(self.std)
-                d.normalize_01 = 1
-                d.max_crop_w = max_cw
-                d.antialias = int(self.antialias)
-                d.status = self._status.data_ptr()
-                stream = torch.cuda.current_stream(self._device)
-                _capi.check(lib.tlb_fused_transform(C.byref(d), C.c_void_p(stream.cuda_stream)))
-                self._batches_served += 1
-                if self._as_tensor:
-                    batch = out.permute(0, 3, 1, 2) if self.channels_last else out
-                else:
-                    batch = _CudaArray(out.data_ptr(), (n, 3, self._oh, self._ow), owner=out)
-                items = [batch]
-                if d_lab_ring is not None:
-                    items.append(d_lab_ring[slot][:n])
-                if self.return_indices:
-                    items.append(d_idx_ring[slot][:n] if d_idx_ring is not None else np.arange(b0, b0 + n))
-                yield items[0] if len(items) == 1 else tuple(items)
+            plan = lib.tlb_epoch_create(C.byref(d), self._n, int(self.drop_last), start, R, self._ahead, self._group,
+                                        ring[0].numel() * ring.element_size(), 8 * bs, 8 * bs)
+            if not plan:
+                raise _capi.TurboLoaderB200Error(1, lib.tlb_last_error().decode(errors="replace"))
+            b_no, n_out, slot = C.c_int64(0), C.c_int32(0), C.c_int32(0)
+            try:
+                while True:
+                    stream = torch.cuda.current_stream(self._device)  # the consumer's stream, asked at every batch
+                    _capi.check(lib.tlb_epoch_next(plan, C.byref(b_no), C.byref(n_out), C.byref(slot),
+                                                   C.c_void_p(stream.cuda_stream)))
+                    n = n_out.value
+                    if n == 0:
+                        break
+                    out = ring[slot.value, :n]
+                    self._batches_served += 1
+                    if self._as_tensor:
+                        batch = out.permute(0, 3, 1, 2) if self.channels_last else out
+                    else:
+                        batch = _CudaArray(out.data_ptr(), (n, 3, self._oh, self._ow), owner=ring,
+                                           device=self._device.index)
+                    items = [batch]
+                    if lab_ring is not None:
+                        items.append(lab_ring[slot.value, :n])
+                    if self.return_indices:
+                        b0 = b_no.value * bs
+                        items.append(idx_ring[slot.value, :n] if idx_ring is not None else np.arange(b0, b0 + n))
+                    yield items[0] if len(items) == 1 else tuple(items)
+            finally:
+                lib.tlb_epoch_destroy(plan)
             self._batches_served = 0
             self._epoch_done = True

@@ -124,14 +124,6 @@ def video_yuv420(y_ptrs, cb_ptrs, cr_ptrs, *, out, stream=None, **kw):
     return out
 
 
-def set_launch_overlap(enable: bool) -> bool:
-    """Let consecutive launches of the fused kernel overlap head to tail (``tlb_set_launch_overlap``).
-
-    Enable it only for a stream in which the kernel directly before each launch is another launch
-    of this library (or does not touch the launch's inputs and outputs); returns the old setting."""
-    return bool(_capi.load().tlb_set_launch_overlap(1 if enable else 0))
-
-
 def launch_count() -> int:
     return int(_capi.load().tlb_launch_count())
 
@@ -217,6 +209,24 @@ def cuda_normalize_resident_gather(src_dev, sel_dev, N, H, W, mean=IMAGENET_MEAN
     return int(ptr)
 
 
+def cuda_resize_normalize_from_device(ptrs, ws, hs, dst_h, dst_w, mean=IMAGENET_MEAN, std=IMAGENET_STD) -> int:
+    """ALREADY-DECODED device images (device addresses ``ptrs`` of HWC uint8 RGB pixels with sizes
+    ``ws`` x ``hs``, each in its own allocation, e.g. the outputs of a GPU decoder) -> device address
+    (int) of the ``(N, 3, dst_h, dst_w)`` float32 batch, valid until the 4th-next call
+    (``turboloader.cuda_resize_normalize_from_device``, turboloader_bindings.cpp:1900-1918)."""
+    n = len(ptrs)
+    if not (len(ws) == len(hs) == n) or n == 0:
+        raise RuntimeError("cuda_resize_normalize_from_device: ptrs, ws and hs must be equally long and non-empty")
+    wa = (C.c_int32 * n)(*[int(v) for v in ws])
+    ha = (C.c_int32 * n)(*[int(v) for v in hs])
+    out = _capi.load().tlb_resize_normalize_device_batch(_addr_array(ptrs), wa, ha, n, int(dst_h), int(dst_w),
+                                                         _capi.f3(mean), _capi.f3(std))
+    if not out:
+        raise RuntimeError("cuda_resize_normalize_from_device failed: " +
+                           _capi.load().tlb_last_error().decode(errors="replace"))
+    return int(out)
+
+
 # ---- the general device-resident call ---------------------------------------------------------
 
 def _dev_ptr(t, dtype, what):
@@ -236,8 +246,13 @@ def _dev_ptr(t, dtype, what):
 def make_desc(src, *, n, dst_h, dst_w, out, src_w=0, src_h=0, n_src=None, src_offsets=None, src_sizes=None,
               sel=None, boxes=None, uniform_box=None, flips=None, mean=IMAGENET_MEAN, std=IMAGENET_STD,
               normalize_01=True, channels_last=False, out_indices=None, labels_in=None, labels_out=None,
-              max_crop_w=0, status=None, antialias=False, max_crop_h=0):
-    """Fill a ``tlb_transform_desc`` from CUDA tensors (all tables on the device)."""
+              max_crop_w=0, status=None, antialias=False, max_crop_h=0, jitter=None, launch_overlap=False):
+    """Fill a ``tlb_transform_desc`` from CUDA tensors (all tables on the device).
+
+    ``jitter``: optional float32 ``(n, 3)`` CUDA tensor of per-sample (brightness, contrast,
+    saturation) factors.  ``launch_overlap``: set ``TLB_FLAG_LAUNCH_OVERLAP`` -- only for a stream
+    in which the kernel directly before this launch neither writes its inputs nor touches its
+    outputs (e.g. a prefetch stream carrying only this library's launches)."""
     import torch
 
     d = _capi.TransformDesc()
@@ -278,6 +293,11 @@ def make_desc(src, *, n, dst_h, dst_w, out, src_w=0, src_h=0, n_src=None, src_of
     d.antialias = int(bool(antialias))  # the reference's opt-in triangle-filter resize
     d.max_crop_h = int(max_crop_h)
     d.status = _dev_ptr(status, torch.int32, "status")
+    if jitter is not None:
+        if tuple(jitter.shape) != (int(n), 3):
+            raise ValueError("jitter must have shape (n, 3)")
+        d.jitter = _dev_ptr(jitter, torch.float32, "jitter")
+    d.flags = _capi.FLAG_LAUNCH_OVERLAP if launch_overlap else 0
     return d
 
 

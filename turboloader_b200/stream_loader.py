@@ -28,20 +28,9 @@ __all__ = ["CudaStreamLoader"]
 class CudaStreamLoader:
     def __init__(self, paths, image_size=160, batch_size=64, *, mean=ops.IMAGENET_MEAN, std=ops.IMAGENET_STD,
                  drop_last=True, num_workers=8, slots=3, **extra):
-        from concurrent.futures import ThreadPoolExecutor
+        from .tbl import decode_to_array
 
-        from PIL import Image
-
-        paths = list(paths)
-        H = W = int(image_size)
-        arr = np.empty((len(paths), H, W, 3), dtype=np.uint8)
-
-        def _load(i):
-            with Image.open(paths[i]) as im:
-                arr[i] = np.asarray(im.convert("RGB").resize((W, H)))
-
-        with ThreadPoolExecutor(max_workers=max(1, int(num_workers))) as ex:
-            list(ex.map(_load, range(len(paths))))
+        arr = decode_to_array(paths, int(image_size), int(image_size), workers=num_workers)
         self._init_common(arr, batch_size, mean=mean, std=std, drop_last=drop_last, slots=slots, **extra)
 
     @classmethod

@@ -98,3 +98,26 @@ def write_raw_tbl(path, array) -> int:
         f.write(idx.tobytes())
         f.write(a.tobytes())
     return n
+
+
+def decode_to_array(paths, height, width, workers=8) -> np.ndarray:
+    """One-time ingest of image FILES for the resident and streaming loaders: every file is opened
+    with PIL, converted to RGB and resized to ``width`` x ``height``; returns ``(N, height, width, 3)``
+    uint8.  (Decode is outside the GPU path; this mirrors what the reference's loaders do once at
+    construction, turboloader/cuda_loader.py:417-436.)"""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from PIL import Image
+
+    files = [os.fspath(f) for f in paths]
+    out = np.empty((len(files), int(height), int(width), 3), dtype=np.uint8)
+
+    def fill(slot_and_file):
+        slot, name = slot_and_file
+        with Image.open(name) as picture:
+            out[slot] = np.asarray(picture.convert("RGB").resize((int(width), int(height))))
+
+    with ThreadPoolExecutor(max_workers=max(1, int(workers))) as pool:
+        for _ in pool.map(fill, enumerate(files)):
+            pass
+    return out
