@@ -682,7 +682,7 @@ def loader_epoch_leg(args, torch, device, peak, n_images):
             "epochs_timed": len(times), "timing": "max(CUDA events on the consumer stream, host wall clock) per epoch, median"}
 
 
-def identity_leg(lib, torch, device, stream, peak, barrier, seed):
+def identity_leg(lib, torch, device, stream, peak, barrier, seed, dtypes=("f32", "bf16")):
     """The identity-size case of the resident loader (gather -> flip -> normalize -> layout/dtype, the
     reference's normalize_gather_kernel operation): 1024 x 160x160 gathered from 20,000 resident
     images, fp32 and bf16 NCHW."""
@@ -693,7 +693,7 @@ def identity_leg(lib, torch, device, stream, peak, barrier, seed):
     g.manual_seed(seed + 5)
     data = torch.randint(0, 256, (n_ds, hw, hw, 3), dtype=torch.uint8, device=device, generator=g)
     res = {}
-    for dt in ("f32", "bf16"):
+    for dt in dtypes:
         batches = []
         for b in range(3):
             sel = np.random.default_rng([seed, b]).permutation(n_ds)[:bs].astype(np.int64)
@@ -783,8 +783,10 @@ def main():
                     help="dataset size of the resident_epoch workload (smaller for profiler captures)")
     ap.add_argument("--video-only", action="store_true",
                     help="run only the YUV 4:2:0 clip leg and print its JSON (used for profiling that kernel)")
-    ap.add_argument("--identity-only", action="store_true",
+    ap.add_argument("--identity-only", nargs="?", const="both", default=None, choices=["both", "f32", "bf16"],
                     help="run only the identity-size gather leg and print its JSON (used for profiling that kernel)")
+    ap.add_argument("--e2e-only", action="store_true",
+                    help="run only the host-image end-to-end leg and print its JSON (used for profiling the gather kernel)")
     ap.add_argument("--antialias", action="store_true", help="set the descriptor's antialias flag on the workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -830,7 +832,13 @@ def main():
         print(json.dumps(video_leg(torch, device, stream, peak, steps=max(3, min(args.steps, 30)))))
         return
     if args.identity_only:
-        print(json.dumps(identity_leg(lib, torch, device, stream, peak, barrier, args.seed)))
+        dts = ("f32", "bf16") if args.identity_only == "both" else (args.identity_only,)
+        print(json.dumps(identity_leg(lib, torch, device, stream, peak, barrier, args.seed, dtypes=dts)))
+        return
+    if args.e2e_only:
+        hs = make_host_workload(args.workload, args.seed, 2)
+        es, h2d, d2h = e2e_steps(hs, lib, stream, max(3, min(args.steps, 20)), 3, torch, device)
+        print(json.dumps({"img_per_s": max(3, min(args.steps, 20)) * hs[0].n / es, "h2d_bytes_per_step": h2d}))
         return
     sampler = ClockSampler(local_rank)
     sampler.start()

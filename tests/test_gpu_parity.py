@@ -4,6 +4,7 @@ edge cases the reference's own resize tests use."""
 import numpy as np
 import pytest
 
+from turboloader_b200 import _capi
 from turboloader_b200 import synthetic as S
 
 from helpers import check_bf16, check_f32, expected, run_gpu
@@ -184,3 +185,59 @@ def test_unflagged_launch_keeps_stream_order_behind_a_producer_kernel():
                           max_crop_w=int(wl.boxes[:, 2].max()))
         torch.cuda.synchronize()
         assert np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), want), f"repetition {rep}"
+
+
+def _jitter_run(wl, jit):
+    import torch
+    from oracle import oracle as O
+    table = torch.from_numpy(np.ascontiguousarray(jit, np.float32)).cuda()
+    res = run_gpu(wl, mutate=lambda d: setattr(d, "jitter", table.data_ptr()))
+    assert res["status"] == 0
+    ref = O.fused_batch(wl.src, wl.offsets, wl.sizes, wl.sel, wl.boxes, wl.flips, wl.dst_h, wl.dst_w, wl.mean, wl.std,
+                        jitter=jit)
+    if wl.channels_last:
+        ref = O.nchw_to_nhwc(ref)
+    return res["out"], (O.bf16_bits(ref) if wl.dtype == "bf16" else ref)
+
+
+def test_colour_jitter_matches_the_restatement_bit_for_bit():
+    """Per-sample (brightness, contrast, saturation) between the 8-bit code and the normalize, in the
+    order of the reference's train_transform shader (src/metal/metal_transforms.mm:111-115).  The
+    oracle is a CPU restatement of those lines (the shader itself cannot run here)."""
+    rs = np.random.RandomState(4)
+    wl = S.config2(n=40, seed=21, lo=60, hi=260, dst=96)
+    jit = rs.uniform(0.6, 1.4, size=(wl.n, 3)).astype(np.float32)
+    jit[0] = (1.0, 1.0, 1.0)
+    jit[1] = (3.0, 2.0, 0.0)   # saturates, then grey
+    jit[2] = (0.0, 1.0, 1.0)   # black before contrast
+    got, want = _jitter_run(wl, jit)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # bf16 NHWC, gather + uniform crop (two columns per lane and the ragged last strip)
+    wl3 = S.config3(seed=5, n_dataset=90, batch=33, batch_index=1, src=100, crop=90, dst=80)
+    wl3.channels_last = True
+    jit3 = rs.uniform(0.5, 1.5, size=(wl3.n, 3)).astype(np.float32)
+    got, want = _jitter_run(wl3, jit3)
+    assert check_bf16(got, want) == 0
+    # narrow output: one column per lane
+    wln = S.config2(n=9, seed=22, lo=30, hi=80, dst=24)
+    got, want = _jitter_run(wln, rs.uniform(0.7, 1.3, size=(9, 3)).astype(np.float32))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_identity_jitter_and_brightness():
+    """The reference's own two checks (tests/test_metal.py:205-228): identity factors reproduce the
+    plain transform within 1e-4, a brightness factor changes the output."""
+    wl = S.config2(n=6, seed=23, lo=100, hi=200, dst=64)
+    plain = run_gpu(wl)["out"]
+    ident, _ = _jitter_run(wl, np.ones((6, 3), np.float32))
+    assert np.abs(ident - plain).max() < 1e-4
+    bright, _ = _jitter_run(wl, np.tile(np.array([[1.5, 1.0, 1.0]], np.float32), (6, 1)))
+    assert np.abs(bright - plain).mean() > 0.01
+
+
+def test_jitter_needs_unit_range_and_the_bilinear_filter():
+    import torch
+    wl = S.config1(n=2, seed=1, src=32, dst=16)   # mean/std in 0..255 units
+    table = torch.ones((2, 3), device="cuda")
+    with pytest.raises(_capi.TurboLoaderB200Error):
+        run_gpu(wl, mutate=lambda d: setattr(d, "jitter", table.data_ptr()))

@@ -97,3 +97,51 @@ def test_a_dead_rank_does_not_block_the_others():
     for p in procs:
         p.join(timeout=30)
     assert procs[0].exitcode == 0 and procs[1].exitcode == 3
+
+
+def _direct_worker(rank, world, port, total, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import turboloader_b200 as t
+
+    # The host side of DataLoader(enable_distributed=True, shuffle=True, train_aug=True): this rank's
+    # block of the shuffled epoch and the crops of its samples.
+    sizes = np.stack([40 + np.arange(total) % 17, 50 + np.arange(total) % 23], 1).astype(np.int32)
+    order = t.direct_order(total, True, 9, 4, True, rank, world)
+    boxes, flips = t.pick_crops(9, 4, sizes[order], indices=order)
+    mine = [(int(i), boxes[k].tolist(), int(flips[k])) for k, i in enumerate(order)]
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine)
+    if rank == 0:
+        q.put(gathered)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_direct_batch_route_union_of_ranks_is_the_single_rank_epoch():
+    import turboloader_b200 as t
+    world, total = 2, 31
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_direct_worker, args=(r, world, port, total, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    gathered = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    sizes = np.stack([40 + np.arange(total) % 17, 50 + np.arange(total) % 23], 1).astype(np.int32)
+    whole = t.direct_order(total, True, 9, 4, False, 0, 1)
+    boxes, flips = t.pick_crops(9, 4, sizes[whole], indices=whole)
+    single = {int(i): (boxes[k].tolist(), int(flips[k])) for k, i in enumerate(whole)}
+    per = total // world
+    seen = []
+    for r, part in enumerate(gathered):
+        assert [i for i, _, _ in part] == whole[r * per:(r + 1) * per].tolist()  # equal blocks of the same shuffle
+        for i, b, f in part:
+            assert single[i] == (b, f)  # a sample's crop does not depend on the rank that serves it
+        seen += [i for i, _, _ in part]
+    assert len(set(seen)) == world * per

@@ -130,3 +130,33 @@ def test_antialias_golden_hashes():
         got = O.fused_batch(c["src"], c["offsets"], c["sizes"], c["sel"], c["boxes"], c["flips"], c["dst_h"], c["dst_w"],
                             MEAN, STD, True, antialias=True)
         assert hashlib.sha256(got.tobytes()).hexdigest() == gold[json.dumps(spec, sort_keys=True)]
+
+
+def test_colour_jitter_restatement():
+    """Colour jitter of the reference's train_transform shader (src/metal/metal_transforms.mm:111-115)
+    as restated on the 8-bit code: identity factors change nothing beyond rounding (the reference's own
+    check, tests/test_metal.py:205-217, allows 1e-4), brightness changes the output (:219-228), the
+    result is clamped to [0,1] before the normalize, and a hand-computed pixel matches."""
+    from turboloader_b200 import synthetic as S
+    wl = S.config2(n=5, seed=12, lo=40, hi=90, dst=32)
+    base = O.fused_batch(wl.src, wl.offsets, wl.sizes, wl.sel, wl.boxes, wl.flips, 32, 32, wl.mean, wl.std)
+    ident = O.fused_batch(wl.src, wl.offsets, wl.sizes, wl.sel, wl.boxes, wl.flips, 32, 32, wl.mean, wl.std,
+                          jitter=np.ones((5, 3), np.float32))
+    assert np.abs(ident - base).max() < 1e-4
+    bright = O.fused_batch(wl.src, wl.offsets, wl.sizes, wl.sel, wl.boxes, wl.flips, 32, 32, wl.mean, wl.std,
+                           jitter=np.tile(np.array([[1.5, 1.0, 1.0]], np.float32), (5, 1)))
+    assert np.abs(bright - base).mean() > 0.01
+    # clamp: everything saturates at rgb = 1 under a large brightness
+    sat = O.fused_batch(wl.src, wl.offsets, wl.sizes, wl.sel, wl.boxes, wl.flips, 32, 32, (0, 0, 0), (1, 1, 1),
+                        jitter=np.tile(np.array([[300.0, 1.0, 1.0]], np.float32), (5, 1)))
+    assert sat.max() == 1.0 and sat.min() >= 0.0
+    # one pixel by hand, every operation rounded to float32 on its own
+    img = np.array([[[200, 100, 50]]], np.uint8)
+    flat, offsets, sizes = S.pack_images([img])
+    jit = np.array([[1.1, 0.9, 1.3]], np.float32)
+    got = O.fused_batch(flat, offsets, sizes, None, None, None, 1, 1, (0, 0, 0), (1, 1, 1), jitter=jit)[0, :, 0, 0]
+    f = np.float32
+    rgb = [f(f(f(f(f(v) * f(1.0 / 255.0)) * jit[0, 0]) - f(0.5)) * jit[0, 1] + f(0.5)) for v in (200, 100, 50)]
+    lum = f(f(f(rgb[0] * f(0.299)) + f(rgb[1] * f(0.587))) + f(rgb[2] * f(0.114)))
+    want = [min(max(f(lum + f(f(c - lum) * jit[0, 2])), f(0)), f(1)) for c in rgb]
+    assert np.array_equal(got, np.array(want, np.float32))

@@ -113,11 +113,50 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
 // compute warp signals "done with raw buffer b" without blocking, the planner blocks (issuing
 // nothing) until all of them have.  Like __syncthreads, this waits only for warps of the same CTA,
 // all of which always get there: their own waits on asynchronous copies are bounded.
-__device__ __forceinline__ void named_arrive(int id, int threads) {
-    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+// The barrier number is an immediate (one barrier per raw buffer): with a run-time number the
+// compiler reserves all 16 barriers for the CTA, which caps the CTAs per SM.
+__device__ __forceinline__ void named_arrive(int buf, int threads) {
+    if (buf == 0)
+        asm volatile("bar.arrive 1, %0;" ::"r"(threads) : "memory");
+    else if (buf == 1)
+        asm volatile("bar.arrive 2, %0;" ::"r"(threads) : "memory");
+    else if (buf == 2)
+        asm volatile("bar.arrive 3, %0;" ::"r"(threads) : "memory");
+    else
+        asm volatile("bar.arrive 4, %0;" ::"r"(threads) : "memory");
 }
-__device__ __forceinline__ void named_sync(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+__device__ __forceinline__ void named_sync(int buf, int threads) {
+    if (buf == 0)
+        asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+    else if (buf == 1)
+        asm volatile("bar.sync 2, %0;" ::"r"(threads) : "memory");
+    else if (buf == 2)
+        asm volatile("bar.sync 3, %0;" ::"r"(threads) : "memory");
+    else
+        asm volatile("bar.sync 4, %0;" ::"r"(threads) : "memory");
+}
+// Shared-memory loads by 32-bit shared-window address (no 64-bit generic pointer arithmetic in
+// the inner loops).
+template <int IMM>
+__device__ __forceinline__ unsigned lds_u8(uint32_t addr) {
+    unsigned v;
+    asm volatile("ld.shared.u8 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
+    return v;
+}
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ int2 lds_i2(uint32_t addr) {
+    int2 v;
+    asm volatile("ld.shared.v2.s32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ int4 lds_i4(uint32_t addr) {
+    int4 v;
+    asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
 // simd_utils.hpp:100-103, with each operation rounded separately.
@@ -400,8 +439,6 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         return;
     }
 
-    const int4* meta = reinterpret_cast<const int4*>(smem + kSmemMeta);
-
     if (tid == 0) {
         for (int b = 0; b < kNBuf; ++b) mbar_init(smem_addr(smem + kSmemFull + 8 * b), 1);
         fence_proxy_async();
@@ -451,12 +488,12 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
         while (st.yb < ty1) {
             // Pass n reuses the raw buffer of pass n - kNBuf: block until every compute warp has
             // finished reading that buffer.
-            named_sync(1 + released % kNBuf, cta_threads);
+            named_sync(released % kNBuf, cta_threads);
             ++released;
             plan_and_issue(pc, st, smem, lane);
         }
         // Match the remaining hand-backs, so that no barrier is left half-way when the CTA retires.
-        for (; released < st.index; ++released) named_sync(1 + released % kNBuf, cta_threads);
+        for (; released < st.index; ++released) named_sync(released % kNBuf, cta_threads);
         return;
     }
 
@@ -531,27 +568,27 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
     char* o1 = o0 + chan_bytes;
     char* o2 = o1 + chan_bytes;
     constexpr int kColB = LAYOUT == 0 ? 32 * ESZ : 96 * ESZ;  // byte distance of column B's pixel
-    const float4* roww = reinterpret_cast<const float4*>(smem + kSmemRowW);
+    const uint32_t smem_base = smem_addr(smem);
+    uint32_t roww = smem_base + kSmemRowW;  // next output row's weights
 
     float2 hA[NP], hB[NP];
 #pragma unroll
     for (int i = 0; i < NP; ++i) hA[i] = hB[i] = f2(0.0f, 0.0f);
 
-    // H step: one staged source row -> the lane's horizontally interpolated values.
-    auto hstep = [&](const unsigned char* row, float2* h) {
-        const unsigned char* a0 = row + offA0;
-        const unsigned char* a1 = row + offA1;
+    // H step: one staged source row (shared-window address) -> the lane's horizontally interpolated values.
+    auto hstep = [&](uint32_t row, float2* h) {
+        const uint32_t a0 = row + offA0, a1 = row + offA1;
         if constexpr (CPL == 2) {
-            const unsigned char* b0 = row + offB0;
-            const unsigned char* b1 = row + offB1;
-#pragma unroll
-            for (int c = 0; c < 3; ++c) {
-                const float2 t0 = byte_product2(a0[c], b0[c], W0, NW0);
-                const float2 t1 = byte_product2(a1[c], b1[c], W1, NW1);
-                h[c] = add2_exact(t0, t1, one2);
-            }
+            const uint32_t b0 = row + offB0, b1 = row + offB1;
+            h[0] = add2_exact(byte_product2(lds_u8<0>(a0), lds_u8<0>(b0), W0, NW0),
+                              byte_product2(lds_u8<0>(a1), lds_u8<0>(b1), W1, NW1), one2);
+            h[1] = add2_exact(byte_product2(lds_u8<1>(a0), lds_u8<1>(b0), W0, NW0),
+                              byte_product2(lds_u8<1>(a1), lds_u8<1>(b1), W1, NW1), one2);
+            h[2] = add2_exact(byte_product2(lds_u8<2>(a0), lds_u8<2>(b0), W0, NW0),
+                              byte_product2(lds_u8<2>(a1), lds_u8<2>(b1), W1, NW1), one2);
         } else {
-            const unsigned p0 = a0[0], p1 = a0[1], p2 = a0[2], q0 = a1[0], q1 = a1[1], q2 = a1[2];
+            const unsigned p0 = lds_u8<0>(a0), p1 = lds_u8<1>(a0), p2 = lds_u8<2>(a0);
+            const unsigned q0 = lds_u8<0>(a1), q1 = lds_u8<1>(a1), q2 = lds_u8<2>(a1);
             h[0] = add2_exact(byte_product2(p0, p1, W0, NW0), byte_product2(q0, q1, W1, NW1), one2);
             h[1] = add2_exact(byte_product2(p2, p2, W0, NW0), byte_product2(q2, q2, W1, NW1), one2);
         }
@@ -665,22 +702,24 @@ fused_transform_kernel(const __grid_constant__ FusedParams p) {
             if (lane == 0 && p.status) atomicOr(p.status, kDevCopyTimeout);
             mbar_wait_bounded(full, full_parity);
         }
-        const int4 m = meta[i % kSlots];  // {new source rows, output rows before the first, last?, -}
-        const int2* srcrec = reinterpret_cast<const int2*>(smem + kSmemSrcRec) + (i % kSlots) * 32;
-        const int2* const srcend = srcrec + m.x;
+        const int slot = i % kSlots;
+        const int4 m = lds_i4(smem_base + kSmemMeta + 16 * slot);  // {new source rows, output rows before the first, last?, -}
+        uint32_t srcrec = smem_base + kSmemSrcRec + slot * 256;
+        const uint32_t srcend = srcrec + 8 * m.x;
 
-        for (int emit = m.y; emit > 0; --emit) vrow(*roww++);  // rows whose source rows came earlier
+        for (int emit = m.y; emit > 0; --emit, roww += 16) vrow(lds_f4(roww));  // rows whose source rows came earlier
         while (srcrec != srcend) {
-            const int2 rec = *srcrec++;  // {byte offset of the staged row, output rows ready after it}
+            const int2 rec = lds_i2(srcrec);  // {byte offset of the staged row, output rows ready after it}
+            srcrec += 8;
             if (next_in_b)
-                hstep(smem + rec.x, hB);
+                hstep(smem_base + rec.x, hB);
             else
-                hstep(smem + rec.x, hA);
+                hstep(smem_base + rec.x, hA);
             next_in_b = !next_in_b;
-            for (int emit = rec.y; emit > 0; --emit) vrow(*roww++);
+            for (int emit = rec.y; emit > 0; --emit, roww += 16) vrow(lds_f4(roww));
         }
         __syncwarp();                      // every lane is done reading raw buffer b
-        named_arrive(1 + b, cta_threads);  // hand it back to the planner
+        named_arrive(b, cta_threads);      // hand it back to the planner
         if (m.z) break;
     }
 }
