@@ -319,11 +319,11 @@ TLB_API int tlb_stream_status(tlb_stream_core* core, uint32_t* out_status);
 /* ---- resident epochs: one call per batch, no per-batch set-up on the host --------------------
  * The batch loop of the resident loader (turboloader/cuda_loader.py:512-535: one
  * normalize_resident(_gather)_batch call and one synchronisation per batch) as a pipeline: the
- * library owns a prefetch stream and a ring of `ring` output slots in caller-allocated memory, keeps
- * up to `ahead` batches enqueued beyond the one being handed out, and hands a batch over by making
- * the consumer's stream wait for it -- the host never blocks.  Launches are enqueued `group` at a
- * time, back to back, with TLB_FLAG_LAUNCH_OVERLAP (the prefetch stream carries nothing else, and
- * consecutive launches write different slots, so the flag's condition holds by construction).
+ * library owns a few prefetch streams and a ring of `ring` output slots in caller-allocated memory,
+ * keeps `ahead` batches enqueued beyond the one being handed out, and hands a batch over by making
+ * the consumer's stream wait for it -- the host never blocks.  Consecutive batches are enqueued on
+ * different streams (they never depend on one another), so the head of one batch fills the SMs
+ * that the tail of the previous one leaves idle.
  *
  * `first` describes batch 0 of the epoch exactly as tlb_fused_transform would take it: n = the
  * batch size; sel / boxes / flips / jitter (if given) point at epoch position 0 of tables that
@@ -331,10 +331,10 @@ TLB_API int tlb_stream_status(tlb_stream_core* core, uint32_t* out_status);
  * at position b * n and writes slot b % ring (slots are out_slot_bytes, index_slot_bytes and
  * label_slot_bytes apart).  With sel == NULL the dataset is read in order: batch b starts at image
  * b * n of `first->src` (uniform layout only).  The last batch is short unless drop_last.
- * A batch stays valid until `ring - ahead - group` further tlb_epoch_next calls have been made. */
+ * A batch stays valid until `ring - ahead - 1` further tlb_epoch_next calls have been made. */
 typedef struct tlb_epoch tlb_epoch;
 TLB_API tlb_epoch* tlb_epoch_create(const tlb_transform_desc* first, int64_t total, int32_t drop_last,
-                                    int64_t start_batch, int32_t ring, int32_t ahead, int32_t group,
+                                    int64_t start_batch, int32_t ring, int32_t ahead,
                                     int64_t out_slot_bytes, int64_t index_slot_bytes,
                                     int64_t label_slot_bytes);       /* NULL on error */
 /* Next batch: *batch = its number in the epoch, *n = its samples (0: epoch finished), *slot = the

@@ -186,3 +186,27 @@ def test_video_descriptor_from_python_and_no_device_error():
     with pytest.raises(_capi.TurboLoaderB200Error) as e:
         ops.enqueue_video(d, 0)
     assert e.value.code == 6  # TLB_ERR_NO_DEVICE: there is no CPU fallback
+
+
+def test_epoch_pipeline_rejects_bad_arguments_on_the_host():
+    """tlb_epoch_create validates its descriptor and pipeline geometry before any CUDA call."""
+    lib = _capi.load()
+    d = _desc(n=4, n_src=64)
+    d.sel = 0x4000
+    args = dict(total=64, drop_last=0, start=0, ring=8, ahead=3, out=4 * 3 * 16 * 16 * 4, idx=0, lab=0)
+
+    def create(desc=d, **kw):
+        a = dict(args, **kw)
+        return lib.tlb_epoch_create(C.byref(desc), a["total"], a["drop_last"], a["start"], a["ring"], a["ahead"],
+                                    a["out"], a["idx"], a["lab"])
+
+    assert not create(ring=4, ahead=3) and b"ring" in lib.tlb_last_error()   # no slot left for a valid batch
+    assert not create(ahead=0)
+    assert not create(total=0)
+    assert not create(out=0)
+    assert not create(start=-1)
+    seq = _desc(n=4, n_src=8)                                                  # in order, but total > n_src
+    assert not create(desc=seq) and b"n_src" in lib.tlb_last_error()
+    assert not create(desc=_desc(n=4, n_src=64, dst_h=0))
+    assert lib.tlb_epoch_next(None, None, None, None, None) == 1
+    lib.tlb_epoch_destroy(None)

@@ -164,7 +164,7 @@ def load() -> C.CDLL:
     lib.tlb_stream_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
     lib.tlb_epoch_create.restype = C.c_void_p
     lib.tlb_epoch_create.argtypes = [C.POINTER(TransformDesc), C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
-                                     C.c_int32, C.c_int64, C.c_int64, C.c_int64]
+                                     C.c_int64, C.c_int64, C.c_int64]
     lib.tlb_epoch_next.restype = C.c_int
     lib.tlb_epoch_next.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
                                    C.c_void_p]

@@ -126,7 +126,10 @@ int grow(Buffer& b, size_t need) {
 }
 
 // ---- planning ------------------------------------------------------------------------
-int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl) {
+// `streaming`: the launch is one of a stream of back-to-back batches (TLB_FLAG_LAUNCH_OVERLAP, or
+// the epoch pipeline): taller tiles halve the per-tile set-up, and the longer tail of a launch is
+// covered by the head of the next one.  A launch on its own finishes sooner with the shorter tiles.
+int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl, bool streaming = false) {
     const int W = d.dst_w, H = d.dst_h;
     const int esz = d.out_dtype == TLB_F32 ? 4 : 2;
     const bool base_ok = (reinterpret_cast<uintptr_t>(d.out) & 15u) == 0;
@@ -140,8 +143,8 @@ int make_plan(const tlb_transform_desc& d, int max_crop_w, tlb::Plan& pl) {
     pl.tile_cols = std::min(max_cols, round_up((W + pl.n_col_tiles - 1) / pl.n_col_tiles, strip_cols));
     pl.n_col_tiles = (W + pl.tile_cols - 1) / pl.tile_cols;
     pl.strips = pl.tile_cols / strip_cols;  // one compute warp per strip
-    // Row tiles of equal height, at most TLB_TILE_ROWS (default 64) rows each.
-    const int max_rows = std::clamp(env_int("TLB_TILE_ROWS", 64), 1, tlb::kMaxTileRows);
+    // Row tiles of equal height, at most TLB_TILE_ROWS (default 64, or 128 when streaming) rows each.
+    const int max_rows = std::clamp(env_int("TLB_TILE_ROWS", streaming ? 128 : 64), 1, tlb::kMaxTileRows);
     pl.n_row_tiles = (H + max_rows - 1) / max_rows;
     pl.tile_rows = (H + pl.n_row_tiles - 1) / pl.n_row_tiles;
     pl.n_row_tiles = (H + pl.tile_rows - 1) / pl.tile_rows;
@@ -239,7 +242,7 @@ int derive_max_crop_w(const tlb_transform_desc& d) {
 // descriptor's launch flags on (TLB_FLAG_LAUNCH_OVERLAP); every other entry point stages inputs in
 // the stream just before the kernel and launches in full stream order.
 int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool honour_flags = false,
-                bool per_image_region = false) {
+                bool per_image_region = false, bool streaming = false) {
     int dev;
     if (int rc = current_device(&dev)) return rc;
     if (int rc = ensure_prepared(g_dev[dev])) return rc;
@@ -267,7 +270,8 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
         if (e != cudaSuccess) return cuda_fail(e, "antialias_kernel launch");
         return TLB_OK;
     }
-    if (int rc = make_plan(d, max_crop_w, p.plan)) return rc;
+    if (honour_flags && (d.flags & TLB_FLAG_LAUNCH_OVERLAP)) streaming = true;
+    if (int rc = make_plan(d, max_crop_w, p.plan, streaming)) return rc;
     const unsigned lflags = (honour_flags && (d.flags & TLB_FLAG_LAUNCH_OVERLAP)) ? tlb::kLaunchOverlap : 0u;
     // Identity size (no resampling) on a uniform dataset: a plain streaming kernel does the job.
     const bool uniform = !d.boxes && !d.src_sizes && !d.src_offsets;
@@ -953,7 +957,7 @@ int tlb_fused_plan(const tlb_transform_desc* desc, int32_t* grid, int32_t* block
     const int mcw = derive_max_crop_w(*desc);
     if (mcw <= 0) return fail(TLB_ERR_INVALID_ARG, "max_crop_w is required");
     tlb::Plan pl{};
-    if (int rc = make_plan(*desc, mcw, pl)) return rc;
+    if (int rc = make_plan(*desc, mcw, pl, (desc->flags & TLB_FLAG_LAUNCH_OVERLAP) != 0)) return rc;
     if (grid) *grid = static_cast<int32_t>(pl.grid);
     if (block) *block = 32 * (pl.strips + 1);
     if (smem_bytes) *smem_bytes = pl.smem_bytes;
@@ -1487,53 +1491,52 @@ int tlb_stream_status(tlb_stream_core* core, uint32_t* out_status) {
 
 // ---- resident epochs ---------------------------------------------------------------------------
 // Replaces the per-batch call + synchronise loop of the reference's resident loader
-// (turboloader/cuda_loader.py:512-535) by a prefetching pipeline on a library-owned stream.
+// (turboloader/cuda_loader.py:512-535) by a prefetching pipeline on library-owned streams.
 struct tlb_epoch {
     int dev = 0;
     tlb_transform_desc first{};
     int max_crop_w = 0;
     int64_t total = 0, n_batches = 0;
     int64_t enqueued = 0, returned = 0;
-    int ring = 0, ahead = 0, group = 0;
+    int ring = 0, ahead = 0;
     int64_t out_slot = 0, idx_slot = 0, label_slot = 0;
-    cudaStream_t stream = nullptr;
+    std::vector<cudaStream_t> streams;  // batch b runs on streams[b % size]: consecutive batches are independent
     cudaEvent_t consumed = nullptr;
     std::vector<cudaEvent_t> ready;
 };
 
 namespace {
 
-int epoch_enqueue(tlb_epoch* e, int64_t count, void* consumer_stream) {
-    // Slots about to be overwritten were handed out at least ring - ahead - group calls ago: order the
-    // prefetch stream behind everything the consumer has enqueued so far, once per group.
+int epoch_enqueue(tlb_epoch* e, void* consumer_stream) {
+    const int64_t b = e->enqueued;
+    const int64_t pos = b * e->first.n;
+    const int slot = static_cast<int>(b % e->ring);
+    cudaStream_t st = e->streams[static_cast<size_t>(b % static_cast<int64_t>(e->streams.size()))];
+    // The slot about to be overwritten was handed out ring batches ago and its validity has run out:
+    // order this launch behind everything the consumer has enqueued so far.
     TLB_CUDA(cudaEventRecord(e->consumed, static_cast<cudaStream_t>(consumer_stream)));
-    TLB_CUDA(cudaStreamWaitEvent(e->stream, e->consumed, 0));
-    for (int64_t i = 0; i < count; ++i) {
-        const int64_t b = e->enqueued;
-        const int64_t pos = b * e->first.n;
-        const int slot = static_cast<int>(b % e->ring);
-        tlb_transform_desc d = e->first;
-        d.n = static_cast<int32_t>(std::min<int64_t>(e->first.n, e->total - pos));
-        if (d.sel) {
-            d.sel += pos;
-        } else {  // sequential: the batch is a contiguous slice of the uniform dataset
-            const uint64_t img = static_cast<uint64_t>(d.src_w) * d.src_h * 3;
-            d.src += pos * img;
-            d.src_bytes = static_cast<uint64_t>(d.n) * img;
-            d.n_src = d.n;
-            if (d.labels_in) d.labels_in += pos;
-        }
-        if (d.boxes) d.boxes += 4 * pos;
-        if (d.flips) d.flips += pos;
-        if (d.jitter) d.jitter += 3 * pos;
-        d.out = static_cast<char*>(d.out) + slot * e->out_slot;
-        if (d.out_indices) d.out_indices = reinterpret_cast<int64_t*>(reinterpret_cast<char*>(d.out_indices) + slot * e->idx_slot);
-        if (d.labels_out) d.labels_out = reinterpret_cast<int64_t*>(reinterpret_cast<char*>(d.labels_out) + slot * e->label_slot);
-        d.flags = TLB_FLAG_LAUNCH_OVERLAP;
-        if (int rc = launch_desc(d, e->max_crop_w, e->stream, /*honour_flags=*/true)) return rc;
-        TLB_CUDA(cudaEventRecord(e->ready[slot], e->stream));
-        e->enqueued = b + 1;
+    TLB_CUDA(cudaStreamWaitEvent(st, e->consumed, 0));
+    tlb_transform_desc d = e->first;
+    d.n = static_cast<int32_t>(std::min<int64_t>(e->first.n, e->total - pos));
+    if (d.sel) {
+        d.sel += pos;
+    } else {  // sequential: the batch is a contiguous slice of the uniform dataset
+        const uint64_t img = static_cast<uint64_t>(d.src_w) * d.src_h * 3;
+        d.src += pos * img;
+        d.src_bytes = static_cast<uint64_t>(d.n) * img;
+        d.n_src = d.n;
+        if (d.labels_in) d.labels_in += pos;
     }
+    if (d.boxes) d.boxes += 4 * pos;
+    if (d.flips) d.flips += pos;
+    if (d.jitter) d.jitter += 3 * pos;
+    d.out = static_cast<char*>(d.out) + slot * e->out_slot;
+    if (d.out_indices) d.out_indices = reinterpret_cast<int64_t*>(reinterpret_cast<char*>(d.out_indices) + slot * e->idx_slot);
+    if (d.labels_out) d.labels_out = reinterpret_cast<int64_t*>(reinterpret_cast<char*>(d.labels_out) + slot * e->label_slot);
+    d.flags = 0;
+    if (int rc = launch_desc(d, e->max_crop_w, st, false, false, /*streaming=*/true)) return rc;
+    TLB_CUDA(cudaEventRecord(e->ready[slot], st));
+    e->enqueued = b + 1;
     return TLB_OK;
 }
 
@@ -1542,15 +1545,15 @@ int epoch_enqueue(tlb_epoch* e, int64_t count, void* consumer_stream) {
 extern "C" {
 
 tlb_epoch* tlb_epoch_create(const tlb_transform_desc* first, int64_t total, int32_t drop_last, int64_t start_batch,
-                            int32_t ring, int32_t ahead, int32_t group, int64_t out_slot_bytes,
-                            int64_t index_slot_bytes, int64_t label_slot_bytes) {
+                            int32_t ring, int32_t ahead, int64_t out_slot_bytes, int64_t index_slot_bytes,
+                            int64_t label_slot_bytes) {
     if (check_common(first)) return nullptr;
     if (first->n <= 0 || total <= 0 || start_batch < 0) {
         fail(TLB_ERR_INVALID_ARG, "epoch: batch size, total and start_batch must be positive / non-negative");
         return nullptr;
     }
-    if (group < 1 || ahead < group || ring < ahead + group + 1) {
-        fail(TLB_ERR_INVALID_ARG, "epoch: need group >= 1, ahead >= group and ring >= ahead + group + 1 (got ring %d, ahead %d, group %d)", ring, ahead, group);
+    if (ahead < 1 || ring < ahead + 2) {
+        fail(TLB_ERR_INVALID_ARG, "epoch: need ahead >= 1 and ring >= ahead + 2 (got ring %d, ahead %d)", ring, ahead);
         return nullptr;
     }
     if (!first->sel && (first->src_offsets || first->src_sizes)) {
@@ -1579,14 +1582,15 @@ tlb_epoch* tlb_epoch_create(const tlb_transform_desc* first, int64_t total, int3
     e->total = total;
     e->n_batches = drop_last ? total / first->n : (total + first->n - 1) / first->n;
     e->enqueued = e->returned = std::min<int64_t>(start_batch, e->n_batches);
-    e->ring = ring; e->ahead = ahead; e->group = group;
+    e->ring = ring; e->ahead = ahead;
     e->out_slot = out_slot_bytes; e->idx_slot = index_slot_bytes; e->label_slot = label_slot_bytes;
     e->ready.assign(ring, nullptr);
-    bool ok = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess &&
-              cudaEventCreateWithFlags(&e->consumed, cudaEventDisableTiming) == cudaSuccess;
+    e->streams.assign(static_cast<size_t>(std::min(ahead + 1, 4)), nullptr);
+    bool ok = cudaEventCreateWithFlags(&e->consumed, cudaEventDisableTiming) == cudaSuccess;
+    for (auto& st : e->streams) ok = ok && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess;
     for (int i = 0; ok && i < ring; ++i) ok = cudaEventCreateWithFlags(&e->ready[i], cudaEventDisableTiming) == cudaSuccess;
     if (!ok) {
-        cuda_fail(cudaGetLastError(), "epoch: creating the prefetch stream and events");
+        cuda_fail(cudaGetLastError(), "epoch: creating the prefetch streams and events");
         tlb_epoch_destroy(e);
         return nullptr;
     }
@@ -1598,13 +1602,12 @@ int tlb_epoch_next(tlb_epoch* e, int64_t* batch, int32_t* n, int32_t* slot, void
     *n = 0;
     if (e->returned >= e->n_batches) return TLB_OK;  // epoch finished
     TLB_CUDA(cudaSetDevice(e->dev));
-    // Keep `ahead` batches in flight beyond the one handed out now, topping up a group at a time.
+    // Keep `ahead` batches in flight beyond the one handed out now.  Batch q overwrites the slot of
+    // batch q - ring; with q <= returned + ahead and ring >= ahead + 2 that batch was handed out at
+    // least two calls ago, i.e. its validity (ring - ahead - 1 further calls) has run out.
     const int64_t want = std::min<int64_t>(e->n_batches, e->returned + 1 + e->ahead);
-    // Batch q overwrites the slot of batch q - ring; with q <= returned + ahead and
-    // ring >= ahead + group + 1 that batch was handed out more than `group` calls ago, i.e. its
-    // validity (ring - ahead - group further calls) has run out.
-    if (e->enqueued <= e->returned || want - e->enqueued >= e->group || (want == e->n_batches && e->enqueued < want))
-        if (int rc = epoch_enqueue(e, want - e->enqueued, consumer_stream)) return rc;
+    while (e->enqueued < want)
+        if (int rc = epoch_enqueue(e, consumer_stream)) return rc;
     const int64_t b = e->returned;
     const int s = static_cast<int>(b % e->ring);
     TLB_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(consumer_stream), e->ready[s], 0));
@@ -1618,10 +1621,11 @@ int tlb_epoch_next(tlb_epoch* e, int64_t* batch, int32_t* n, int32_t* slot, void
 void tlb_epoch_destroy(tlb_epoch* e) {
     if (!e) return;
     cudaSetDevice(e->dev);
-    if (e->stream) {
-        cudaStreamSynchronize(e->stream);
-        cudaStreamDestroy(e->stream);
-    }
+    for (cudaStream_t st : e->streams)
+        if (st) {
+            cudaStreamSynchronize(st);
+            cudaStreamDestroy(st);
+        }
     for (cudaEvent_t ev : e->ready)
         if (ev) cudaEventDestroy(ev);
     if (e->consumed) cudaEventDestroy(e->consumed);

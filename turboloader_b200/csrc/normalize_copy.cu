@@ -21,6 +21,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cstdint>
+#include <cstdlib>
 #include <type_traits>
 
 #include "fused_params.h"
@@ -285,8 +286,9 @@ int launch_one(const FusedParams& p, cudaStream_t st) {
     constexpr int P = DTYPE == 0 ? 4 : 8;
     // Vector form: 8-byte aligned rows of whole 8-pixel groups and 16-byte aligned output chunks.
     const int cx = p.ubox[2] > 0 ? p.ubox[0] : 0;
-    const bool vec8 = p.plan.vec_ok && (reinterpret_cast<uintptr_t>(p.src) % 8 == 0) && p.src_w % 8 == 0 && cx % 8 == 0 &&
-                      p.dst_w % 8 == 0;
+    // (bf16 only: with fp32 output the scalar form above is already store-bound and measured faster.)
+    const bool vec8 = DTYPE == 1 && p.plan.vec_ok && (reinterpret_cast<uintptr_t>(p.src) % 8 == 0) && p.src_w % 8 == 0 &&
+                      cx % 8 == 0 && p.dst_w % 8 == 0 && std::getenv("TLB_IDENTITY_VEC8_OFF") == nullptr;
     const int groups = (p.dst_w + (vec8 ? 8 : P) - 1) / (vec8 ? 8 : P);
     const int bx = std::min(groups, 256);
     const int by = std::max(1, std::min(256 / bx, p.dst_h));

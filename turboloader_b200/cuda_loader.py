@@ -159,12 +159,11 @@ class CudaResidentLoader:
         plain = self.dtype == torch.float32 and not self.channels_last
         self._as_tensor = (not plain) if as_tensor is None else bool(as_tensor) or not plain
         self._labels = None if labels is None else torch.as_tensor(np.asarray(labels), dtype=torch.int64).to(self._device)
-        # Batches are prefetched on a stream of the library: `ring` output slots, `ahead` batches in
-        # flight beyond the one handed out, enqueued `group` at a time (so that launches overlap head to
-        # tail).  A batch stays valid for ring - ahead - group further batches (3 by default).
+        # Batches are prefetched on streams of the library: `ring` output slots, `ahead` batches in
+        # flight beyond the one handed out.  A batch stays valid for ring - ahead - 1 further batches
+        # (4 by default).
         self._ring_slots = max(3, int(ring))
-        self._group = 2 if self._ring_slots >= 6 else 1
-        self._ahead = max(self._group, (self._ring_slots - self._group) // 2)
+        self._ahead = max(1, (self._ring_slots - 1) // 2)
         self._ring = None
         self._jitter_fn = jitter  # callable(epoch, order) -> float32[len(order), 3] (brightness, contrast, saturation), or None
         self._epoch = 0
@@ -289,7 +288,7 @@ class CudaResidentLoader:
             start = self._resume_batches
             self._batches_served = start
             self._resume_batches = 0
-            plan = lib.tlb_epoch_create(C.byref(d), self._n, int(self.drop_last), start, R, self._ahead, self._group,
+            plan = lib.tlb_epoch_create(C.byref(d), self._n, int(self.drop_last), start, R, self._ahead,
                                         ring[0].numel() * ring.element_size(), 8 * bs, 8 * bs)
             if not plan:
                 raise _capi.TurboLoaderB200Error(1, lib.tlb_last_error().decode(errors="replace"))

@@ -80,8 +80,7 @@ class DirectBatchLoader:
             raise ValueError("dtype must be torch.float32 or torch.bfloat16")
         self._jitter_fn = jitter
         self._ring_slots = max(3, int(ring))
-        self._group = 2 if self._ring_slots >= 6 else 1
-        self._ahead = max(self._group, (self._ring_slots - self._group) // 2)
+        self._ahead = max(1, (self._ring_slots - 1) // 2)
         self._ring = None
         self._epoch = 0
         self._resume_batches = 0
@@ -182,7 +181,7 @@ class DirectBatchLoader:
             d.normalize_01 = 1
             d.antialias = int(self.antialias)
             d.status = self._status.data_ptr()
-            plan = lib.tlb_epoch_create(C.byref(d), total, int(self.drop_last), start, R, self._ahead, self._group,
+            plan = lib.tlb_epoch_create(C.byref(d), total, int(self.drop_last), start, R, self._ahead,
                                         ring[0].numel() * ring.element_size(), 0, 0)
             if not plan:
                 raise _capi.TurboLoaderB200Error(1, lib.tlb_last_error().decode(errors="replace"))
