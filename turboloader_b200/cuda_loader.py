@@ -165,6 +165,7 @@ class CudaResidentLoader:
         self._ring_slots = max(3, int(ring))
         self._ahead = max(1, (self._ring_slots - 1) // 2)
         self._ring = None
+        self._lookahead = None
         self._jitter_fn = jitter  # callable(epoch, order) -> float32[len(order), 3] (brightness, contrast, saturation), or None
         self._epoch = 0
         self._resume_batches = 0
@@ -205,21 +206,53 @@ class CudaResidentLoader:
             return np.zeros(self._n, dtype=np.uint8)
         return (np.random.default_rng([self.seed, e, 7]).random(self._n) < self.hflip_prob).astype(np.uint8)
 
-    def __iter__(self):
-        torch = self._torch
-        bs = self.batch_size
-        order = self.epoch_order()
-        aug_boxes = None
+    def _host_tables(self, epoch):
+        """(order, flips, RandomResizedCrop boxes or None) of an epoch -- everything that is drawn on
+        the host from (seed, epoch) alone."""
+        order = self.epoch_order(epoch)
         if self._train_aug:
             from .augment import pick_crops
             sizes = np.tile(np.array([[self._W, self._H]], dtype=np.int32), (self._n, 1))
-            aug_boxes, flips = pick_crops(self.seed, self._epoch, sizes, indices=order, hflip_prob=self.hflip_prob)
-        elif self._flips_fn is not None:
+            boxes, flips = pick_crops(self.seed, epoch, sizes, indices=order, hflip_prob=self.hflip_prob)
+            return order, flips, boxes
+        return order, self.epoch_flips(epoch), None
+
+    def _epoch_tables(self, epoch):
+        """The epoch's host tables, from the look-ahead if it already drew them; then the NEXT
+        epoch's tables are drawn on a helper thread while this epoch is being served, so that the
+        usual ``for e in range(E): set_epoch(e); for batch in loader`` loop pays the permutation of
+        a large dataset (milliseconds) only once."""
+        import threading
+
+        pending = self._lookahead
+        self._lookahead = None
+        tables = None
+        if pending is not None:
+            thread, box = pending
+            thread.join()
+            if box.get("key") == (epoch, self.seed, self.hflip_prob, self.shuffle, self._train_aug):
+                tables = box["tables"]
+        if tables is None:
+            tables = self._host_tables(epoch)
+        box = {}
+
+        def work(e=epoch + 1, key=(epoch + 1, self.seed, self.hflip_prob, self.shuffle, self._train_aug)):
+            box["tables"] = self._host_tables(e)
+            box["key"] = key
+
+        thread = threading.Thread(target=work, daemon=True)
+        thread.start()
+        self._lookahead = (thread, box)
+        return tables
+
+    def __iter__(self):
+        torch = self._torch
+        bs = self.batch_size
+        order, flips, aug_boxes = self._epoch_tables(self._epoch)
+        if self._flips_fn is not None:
             flips = np.ascontiguousarray(self._flips_fn(self._epoch, self._n, self._resume_batches), dtype=np.uint8)
             if flips.shape != (self._n,):
                 raise ValueError("flips callable must return one flag per epoch position")
-        else:
-            flips = self.epoch_flips()
         lib = _capi.load()
         with torch.cuda.device(self._device):
             # ---- whole-epoch tables on the device, once -----------------------------------------
