@@ -361,3 +361,24 @@ def test_resident_gather_is_bounded_by_the_allocation():
     got = torch.as_tensor(t._CudaArray(ptr, (3, 3, 24, 24)), device="cuda").cpu().numpy()
     want = _oracle_uniform(data, sel=np.array([3, 7], np.int64))
     assert np.array_equal(got[0], want[0]) and np.array_equal(got[2], want[1]) and (got[1] == 0).all()
+
+
+def test_cuda_array_speaks_dlpack():
+    """The float32 hand-off object implements __dlpack__ / __dlpack_device__ beside
+    __cuda_array_interface__: torch.from_dlpack adopts the same device memory without a copy."""
+    import torch
+    data = _dataset(12, 16)
+    gpu = torch.from_numpy(data).cuda()
+    ptr = t.cuda_normalize_resident(gpu.data_ptr(), 12, 16, 16)
+    arr = t._CudaArray(ptr, (12, 3, 16, 16))
+    assert arr.__dlpack_device__() == (2, torch.cuda.current_device())
+    via_dlpack = torch.from_dlpack(arr)
+    via_cai = torch.as_tensor(arr, device="cuda")
+    assert via_dlpack.data_ptr() == ptr == via_cai.data_ptr()
+    assert via_dlpack.dtype == torch.float32 and tuple(via_dlpack.shape) == (12, 3, 16, 16)
+    assert np.array_equal(via_dlpack.cpu().numpy(), _oracle_uniform(data))
+    # the loader's float32 batches are such objects; bf16 batches are torch tensors with their own __dlpack__
+    ld = t.CudaResidentLoader.from_array(data, batch_size=4)
+    first = next(iter(ld))
+    assert hasattr(first, "__dlpack__") and hasattr(first, "__cuda_array_interface__")
+    assert np.array_equal(torch.from_dlpack(first).cpu().numpy(), _oracle_uniform(data[:4]))
