@@ -12,6 +12,7 @@ struct AAPlan {
     int tile_cols;     // output columns per CTA = threads per CTA (multiple of 32, <= 256)
     int n_row_tiles, n_col_tiles;
     int smem_bytes;
+    int pair;          // 1: the packed two-columns-per-thread kernel (tile_cols / 2 threads per CTA)
     long long grid;
 };
 

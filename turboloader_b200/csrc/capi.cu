@@ -257,11 +257,20 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
         tlb::AAPlan a{};
         a.xt = tlb::aa_max_taps(max_crop_w, d.dst_w);
         a.yt = tlb::aa_max_taps(max_crop_h, d.dst_h);
-        a.tile_cols = std::min(256, round_up(d.dst_w, 32));
-        a.n_col_tiles = (d.dst_w + a.tile_cols - 1) / a.tile_cols;
+        // The packed kernel gives a thread two columns (tile_cols / 2 threads per CTA); its tables
+        // take 3x the column weights of the one-column kernel, so very wide filters get narrower tiles.
+        static const bool one_col = std::getenv("TLB_AA_ONE_COLUMN") != nullptr;
+        a.pair = one_col ? 0 : 1;
         a.tile_rows = std::min(32, d.dst_h);
         a.n_row_tiles = (d.dst_h + a.tile_rows - 1) / a.tile_rows;
-        a.smem_bytes = 4 * (a.xt * a.tile_cols + a.tile_rows * a.yt + 2 * a.tile_rows + a.yt * 3 * a.tile_cols);
+        a.tile_cols = std::min(256, round_up(d.dst_w, 32));
+        for (;;) {
+            const int xw_words = (a.pair ? 3 : 1) * a.xt * a.tile_cols;
+            a.smem_bytes = 4 * (xw_words + a.tile_rows * a.yt + 2 * a.tile_rows + a.yt * 3 * a.tile_cols);
+            if (a.smem_bytes <= tlb::kAAMaxSmem || a.tile_cols <= 32) break;
+            a.tile_cols = round_up(a.tile_cols / 2, 32);
+        }
+        a.n_col_tiles = (d.dst_w + a.tile_cols - 1) / a.tile_cols;
         if (a.smem_bytes > tlb::kAAMaxSmem)
             return fail(TLB_ERR_TOO_LARGE, "antialias: a %d-tap filter does not fit the shared-memory tables", std::max(a.xt, a.yt));
         a.grid = static_cast<long long>(d.n) * a.n_row_tiles * a.n_col_tiles;
