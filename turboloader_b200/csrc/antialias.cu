@@ -287,178 +287,271 @@ __device__ __forceinline__ float2 aa_add2_rz(float2 a, float2 b) {
     return d;
 }
 
+// Shared memory through 32-bit shared-window addresses: the ring and the tables are walked with
+// 32-bit adds instead of 64-bit generic pointers.  All of these are `volatile`, which keeps a
+// thread's ring stores and loads in program order.
+__device__ __forceinline__ uint32_t aa_smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ float4 aa_lds_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float aa_lds_f(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ int2 aa_lds_i2(uint32_t addr) {
+    int2 v;
+    asm volatile("ld.shared.v2.s32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ void aa_sts_f2(uint32_t addr, float2 v) {
+    asm volatile("st.shared.v2.f32 [%0+%1], {%2, %3};" ::"r"(addr), "n"(OFF), "f"(v.x), "f"(v.y));
+}
+template <int OFF>
+__device__ __forceinline__ float2 aa_lds_f2o(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2+%3];" : "=f"(v.x), "=f"(v.y) : "r"(addr), "n"(OFF));
+    return v;
+}
+
 struct PairCtx {
-    void* out;
     const unsigned char* img;      // the sample's image
     unsigned row_pitch;            // bytes per image row
     unsigned offA, offB;           // byte offset (from img) of the first pixel of each column's tap window, crop row 0
-    const float4* xw;              // this thread's weights: xw[q * xw_stride] = {wA, wB, -2^23 wA, -2^23 wB}
-    int xw_stride;
-    const float* yw;               // [rows][yt]
-    const int* yl;
-    const int* yc;
+    uint32_t xw;                   // this thread's weights: float4 {wA, wB, -2^23 wA, -2^23 wB} every xw_stride bytes
+    uint32_t xw_stride;
+    uint32_t yw;                   // [rows][yt] floats
+    uint32_t yrec;                 // [rows] int2 {last source row the output row taps, tap count}
     int yt, rows;
+    int first_src, end_src;        // source rows the tile taps: [first_src, end_src)
+    uint32_t ring;                 // this thread's 24 bytes of ring slot 0
     int slot_bytes;                // bytes between ring slots
-    unsigned char* myring;         // this thread's 24 bytes of slot 0
-    unsigned char* ring_end;       // ... of the slot past the last
+    int slots;                     // ring slots (>= the most vertical taps)
     int nt;                        // horizontal taps of this sample
     float one, pre, nkpre;
     float nmean[3], inv_std[3];
     bool validB;
-    long long oA, oB;              // element index of channel 0 of each column at tile row 0
-    long long row_step, chan_step; // elements to the next output row / channel
+    unsigned char* pA;             // channel 0 of column A at tile row 0
+    long long dB;                  // bytes from column A to column B
+    long long row_step, chan_step; // bytes to the next output row / channel
 };
 
-// The words of one source row's tap window for one column: NW aligned 32-bit words starting at the
-// word that holds the window's first byte, and the bit shift that realigns them.
-template <int NW>
+// The words of one source row's tap window for one column: aligned 32-bit words starting at the
+// word that holds the window's first byte, and the bit shift that realigns them.  Sized for the
+// widest unrolled filter; a narrower one uses the first words only.
+constexpr int kAAUnrolledTaps = 8;
+constexpr int kAAMaxWords = (3 * kAAUnrolledTaps + 3) / 4 + 1;
 struct RowWords {
-    unsigned w[NW];
+    unsigned w[kAAMaxWords];
     unsigned sh;
 };
 
-template <int NT, int NW>
-__device__ __forceinline__ void load_window(const unsigned char* imga, unsigned g, RowWords<NW>& r) {
-    // g = byte offset of the window from the 4-aligned `imga`.  Words 0..NW-2 always hold window bytes;
-    // the last one may lie wholly behind the window (it then feeds only shifted-out bits), so its
-    // address is clamped to the last word that does.
-    const unsigned first = g & ~3u;
-    const unsigned last = (g + 3u * NT - 1u) & ~3u;
-    const unsigned* wp = reinterpret_cast<const unsigned*>(imga + first);
+template <int NT>
+__device__ __forceinline__ void load_window(const unsigned char* imga, unsigned g, RowWords& r) {
+    // g = byte offset of the window from the 4-aligned `imga`.  Words 0..NS-1 always hold window
+    // bytes; the last one is fetched only when the window reaches into it (otherwise it would feed
+    // nothing but shifted-out bits, and might lie past the end of the image).
+    constexpr int NS = (3 * NT + 3) / 4;
+    const unsigned al = g & 3u;
+    const unsigned* wp = reinterpret_cast<const unsigned*>(imga + (g - al));
 #pragma unroll
-    for (int i = 0; i < NW - 1; ++i) r.w[i] = __ldg(wp + i);
-    r.w[NW - 1] = __ldg(reinterpret_cast<const unsigned*>(imga + min(first + 4u * (NW - 1), last)));
-    r.sh = (g & 3u) * 8u;
+    for (int i = 0; i < NS; ++i) r.w[i] = __ldg(wp + i);
+    r.w[NS] = 0u;
+    if (al + 3u * NT > 4u * NS) r.w[NS] = __ldg(wp + NS);
+    r.sh = al * 8u;
 }
 
-// Rows of one tile for a thread's column pair.  NT > 0: the sample has exactly NT horizontal taps;
-// the tap loop is unrolled, the window is fetched as aligned words (bytes picked by PRMT straight
-// into 2^23 + b) and the NEXT source row's words are requested before the current row is filtered,
-// so their latency hides behind a row of arithmetic.  NT == 0: any tap count, byte loads.
-template <int DTYPE, int NT>
-__device__ __forceinline__ void pair_rows(const PairCtx& c) {
-    constexpr int NS = (3 * NT + 3) / 4;   // words of window bytes
-    constexpr int NW = NS + 1;             // ... plus the one the realignment may need
+template <int DTYPE>
+__device__ __forceinline__ void put_at(unsigned char* ptr, float v) {
+    if constexpr (DTYPE == 0)
+        *reinterpret_cast<float*>(ptr) = v;
+    else
+        *reinterpret_cast<__nv_bfloat16*>(ptr) = __float2bfloat16_rn(v);
+}
+
+struct Acc3 {
+    float2 c0, c1, c2;
+};
+
+// Horizontal pass of one source row for a column pair whose sample has exactly NT taps.  `a`, `b`
+// hold the row's words on entry; they are realigned first, so that the same registers can take
+// the NEXT row's words (requested here, a row of arithmetic ahead of their use).
+template <int NT>
+__device__ __forceinline__ Acc3 hrow_words(const PairCtx& c, const unsigned char* imga, unsigned gA, unsigned gB,
+                                           int src, RowWords& a, RowWords& b, float2 one2) {
+    constexpr int NS = (3 * NT + 3) / 4;
+    unsigned sA[NS], sB[NS];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        sA[i] = __funnelshift_r(a.w[i], a.w[i + 1], a.sh);
+        sB[i] = __funnelshift_r(b.w[i], b.w[i + 1], b.sh);
+    }
+    if (src + 1 < c.end_src) {
+        const unsigned rowoff = static_cast<unsigned>(src + 1) * c.row_pitch;
+        load_window<NT>(imga, rowoff + gA, a);
+        load_window<NT>(imga, rowoff + gB, b);
+    }
+    Acc3 acc;
+    acc.c0 = acc.c1 = acc.c2 = make_float2(0.0f, 0.0f);
+    uint32_t wq = c.xw;
+#pragma unroll
+    for (int q = 0; q < NT; ++q, wq += c.xw_stride) {
+        const float4 w = aa_lds_f4(wq);
+        const float2 w2 = make_float2(w.x, w.y), nw2 = make_float2(w.z, w.w);
+        float2 px[3];
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) {
+            constexpr unsigned kHi = 0x4B000000u;
+            const int j = 3 * q + ch;
+            px[ch].x = __uint_as_float(__byte_perm(sA[j >> 2], kHi, 0x7440u | (j & 3)));
+            px[ch].y = __uint_as_float(__byte_perm(sB[j >> 2], kHi, 0x7440u | (j & 3)));
+        }
+        acc.c0 = aa_fma2(aa_fma2(px[0], w2, nw2), one2, acc.c0);
+        acc.c1 = aa_fma2(aa_fma2(px[1], w2, nw2), one2, acc.c1);
+        acc.c2 = aa_fma2(aa_fma2(px[2], w2, nw2), one2, acc.c2);
+    }
+    return acc;
+}
+
+// ... any tap count, byte loads, nothing requested ahead.
+__device__ __forceinline__ Acc3 hrow_bytes(const PairCtx& c, int src, float2 one2) {
+    const unsigned char* pa = c.img + c.offA + static_cast<unsigned long long>(src) * c.row_pitch;
+    const unsigned char* pb = c.img + c.offB + static_cast<unsigned long long>(src) * c.row_pitch;
+    uint32_t wq = c.xw;
+    Acc3 acc;
+    acc.c0 = acc.c1 = acc.c2 = make_float2(0.0f, 0.0f);
+#pragma unroll 2
+    for (int q = 0; q < c.nt; ++q, pa += 3, pb += 3, wq += c.xw_stride) {
+        const float4 w = aa_lds_f4(wq);
+        const float2 w2 = make_float2(w.x, w.y), nw2 = make_float2(w.z, w.w);
+        const unsigned a0 = __ldg(pa), a1 = __ldg(pa + 1), a2 = __ldg(pa + 2);
+        const unsigned b0 = __ldg(pb), b1 = __ldg(pb + 1), b2 = __ldg(pb + 2);
+        acc.c0 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a0 | 0x4B000000u), __uint_as_float(b0 | 0x4B000000u)), w2, nw2), one2, acc.c0);
+        acc.c1 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a1 | 0x4B000000u), __uint_as_float(b1 | 0x4B000000u)), w2, nw2), one2, acc.c1);
+        acc.c2 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a2 | 0x4B000000u), __uint_as_float(b2 | 0x4B000000u)), w2, nw2), one2, acc.c2);
+    }
+    return acc;
+}
+
+// Rows of one tile for a thread's column pair, as a walk down the SOURCE rows the tile taps: each
+// is filtered horizontally into the thread's ring slot, then every output row whose last tap row it
+// was is finished (vertical pass over the ring, rounding, normalize, store).  `mode` picks the
+// horizontal pass: 1..kAAUnrolledTaps = that many taps, unrolled, window fetched as aligned words
+// (bytes picked by PRMT straight into 2^23 + b); 0 = byte loads.  The choice is made per row by a
+// CTA-uniform branch so that the vertical pass exists once in the kernel's code: with one copy per
+// filter width the CTAs of a batch (whose samples differ in width) thrashed the instruction cache.
+template <int DTYPE>
+__device__ __forceinline__ void pair_rows(const PairCtx& c, const int mode) {
     const float2 one2 = make_float2(c.one, c.one);
     const float2 k2 = make_float2(8388608.0f, 8388608.0f);
+    const float2 half2 = make_float2(0.5f, 0.5f);
     const float2 pre2 = make_float2(c.pre, c.pre), nkpre2 = make_float2(c.nkpre, c.nkpre);
-    const int RR_bytes = static_cast<int>(c.ring_end - c.myring);
     const unsigned lowbits = static_cast<unsigned>(reinterpret_cast<unsigned long long>(c.img) & 3ull);
     const unsigned char* const imga = c.img - lowbits;
-    const int last_src = c.yl[c.rows - 1] + c.yc[c.rows - 1];  // one past the last source row the tile taps
+    const unsigned gA = lowbits + c.offA, gB = lowbits + c.offB;
 
-    int next_src = c.yl[0];               // next source row to filter horizontally
-    unsigned char* next_slot = c.myring;  // its ring slot
-    int lo_prev = c.yl[0];
-    unsigned char* lo_slot = c.myring;    // slot of the first tap row of the current output row
-    long long oA = c.oA, oB = c.oB;
-    RowWords<NW> nxtA, nxtB;
-    if constexpr (NT > 0) {
-        load_window<NT, NW>(imga, lowbits + c.offA + static_cast<unsigned>(next_src) * c.row_pitch, nxtA);
-        load_window<NT, NW>(imga, lowbits + c.offB + static_cast<unsigned>(next_src) * c.row_pitch, nxtB);
+    int src = c.first_src;        // source row being filtered
+    int slot = 0;                 // its ring slot, and the slot's byte offset
+    int slot_off = 0;
+    int r = 0;                    // next output row to finish
+    int2 rec = aa_lds_i2(c.yrec); // {its last tap row, its tap count}
+    uint32_t wrow = c.yw;         // its weights
+    unsigned char* pA = c.pA;
+
+    RowWords bufA, bufB;
+#pragma unroll
+    for (int i = 0; i < kAAMaxWords; ++i) bufA.w[i] = bufB.w[i] = 0u;
+    bufA.sh = bufB.sh = 0u;
+    {
+        const unsigned rowoff = static_cast<unsigned>(src) * c.row_pitch;
+        switch (mode) {
+            case 1: load_window<1>(imga, rowoff + gA, bufA); load_window<1>(imga, rowoff + gB, bufB); break;
+            case 2: load_window<2>(imga, rowoff + gA, bufA); load_window<2>(imga, rowoff + gB, bufB); break;
+            case 3: load_window<3>(imga, rowoff + gA, bufA); load_window<3>(imga, rowoff + gB, bufB); break;
+            case 4: load_window<4>(imga, rowoff + gA, bufA); load_window<4>(imga, rowoff + gB, bufB); break;
+            case 5: load_window<5>(imga, rowoff + gA, bufA); load_window<5>(imga, rowoff + gB, bufB); break;
+            case 6: load_window<6>(imga, rowoff + gA, bufA); load_window<6>(imga, rowoff + gB, bufB); break;
+            case 7: load_window<7>(imga, rowoff + gA, bufA); load_window<7>(imga, rowoff + gB, bufB); break;
+            case 8: load_window<8>(imga, rowoff + gA, bufA); load_window<8>(imga, rowoff + gB, bufB); break;
+            default: break;
+        }
     }
-    for (int r = 0; r < c.rows; ++r, oA += c.row_step, oB += c.row_step) {
-        const int lo = c.yl[r], n = c.yc[r];
-        lo_slot += (lo - lo_prev) * c.slot_bytes;  // lo never decreases, by less than a ring per step
-        lo_prev = lo;
-        if (lo_slot >= c.ring_end) lo_slot -= RR_bytes;
-        if (next_src < lo) {  // rows no output row of this tile taps
-            next_slot += (lo - next_src) * c.slot_bytes;
-            next_src = lo;
-            while (next_slot >= c.ring_end) next_slot -= RR_bytes;
-            if constexpr (NT > 0) {
-                load_window<NT, NW>(imga, lowbits + c.offA + static_cast<unsigned>(next_src) * c.row_pitch, nxtA);
-                load_window<NT, NW>(imga, lowbits + c.offB + static_cast<unsigned>(next_src) * c.row_pitch, nxtB);
-            }
+    for (;;) {
+        // ---- horizontal pass of source row `src` into its ring slot ------------------------------
+        Acc3 h;
+        switch (mode) {
+            case 1: h = hrow_words<1>(c, imga, gA, gB, src, bufA, bufB, one2); break;
+            case 2: h = hrow_words<2>(c, imga, gA, gB, src, bufA, bufB, one2); break;
+            case 3: h = hrow_words<3>(c, imga, gA, gB, src, bufA, bufB, one2); break;
+            case 4: h = hrow_words<4>(c, imga, gA, gB, src, bufA, bufB, one2); break;
+            case 5: h = hrow_words<5>(c, imga, gA, gB, src, bufA, bufB, one2); break;
+            case 6: h = hrow_words<6>(c, imga, gA, gB, src, bufA, bufB, one2); break;
+            case 7: h = hrow_words<7>(c, imga, gA, gB, src, bufA, bufB, one2); break;
+            case 8: h = hrow_words<8>(c, imga, gA, gB, src, bufA, bufB, one2); break;
+            default: h = hrow_bytes(c, src, one2); break;
         }
-        // ---- horizontal pass for the source rows this output row adds -------------------------
-        for (; next_src < lo + n; ++next_src) {
-            float2 acc0 = make_float2(0.0f, 0.0f), acc1 = acc0, acc2 = acc0;
-            if constexpr (NT > 0) {
-                const RowWords<NW> curA = nxtA, curB = nxtB;
-                if (next_src + 1 < last_src) {
-                    const unsigned rowoff = static_cast<unsigned>(next_src + 1) * c.row_pitch + lowbits;
-                    load_window<NT, NW>(imga, rowoff + c.offA, nxtA);
-                    load_window<NT, NW>(imga, rowoff + c.offB, nxtB);
-                }
-                unsigned sA[NS], sB[NS];
-#pragma unroll
-                for (int i = 0; i < NS; ++i) {
-                    sA[i] = __funnelshift_r(curA.w[i], curA.w[i + 1], curA.sh);
-                    sB[i] = __funnelshift_r(curB.w[i], curB.w[i + 1], curB.sh);
-                }
-                const float4* wq = c.xw;
-#pragma unroll
-                for (int q = 0; q < NT; ++q, wq += c.xw_stride) {
-                    const float4 w = *wq;
-                    const float2 w2 = make_float2(w.x, w.y), nw2 = make_float2(w.z, w.w);
-                    float2 px[3];
-#pragma unroll
-                    for (int ch = 0; ch < 3; ++ch) {
-                        constexpr unsigned kHi = 0x4B000000u;
-                        const int j = 3 * q + ch;
-                        px[ch].x = __uint_as_float(__byte_perm(sA[j >> 2], kHi, 0x7440u | (j & 3)));
-                        px[ch].y = __uint_as_float(__byte_perm(sB[j >> 2], kHi, 0x7440u | (j & 3)));
-                    }
-                    acc0 = aa_fma2(aa_fma2(px[0], w2, nw2), one2, acc0);
-                    acc1 = aa_fma2(aa_fma2(px[1], w2, nw2), one2, acc1);
-                    acc2 = aa_fma2(aa_fma2(px[2], w2, nw2), one2, acc2);
-                }
-            } else {
-                const unsigned char* pa = c.img + c.offA + static_cast<unsigned long long>(next_src) * c.row_pitch;
-                const unsigned char* pb = c.img + c.offB + static_cast<unsigned long long>(next_src) * c.row_pitch;
-                const float4* wq = c.xw;
+        {
+            const uint32_t at = c.ring + slot_off;
+            aa_sts_f2<0>(at, h.c0);
+            aa_sts_f2<8>(at, h.c1);
+            aa_sts_f2<16>(at, h.c2);
+        }
+        // ---- finish the output rows whose last tap row this was ----------------------------------
+        while (rec.x == src) {
+            const int n = rec.y;
+            int lo_slot = slot - (n - 1);
+            if (lo_slot < 0) lo_slot += c.slots;
+            const int n1 = min(n, c.slots - lo_slot);   // taps before the ring wraps
+            uint32_t vs = c.ring + lo_slot * c.slot_bytes;
+            uint32_t wq = wrow;
+            float2 v0 = make_float2(0.0f, 0.0f), v1 = v0, v2 = v0;
+            auto tap = [&]() {
+                const float w = aa_lds_f(wq);
+                const float2 w2 = make_float2(w, w);
+                const float2 s0 = aa_lds_f2o<0>(vs), s1 = aa_lds_f2o<8>(vs), s2 = aa_lds_f2o<16>(vs);
+                wq += 4;
+                vs += c.slot_bytes;
+                v0 = aa_fma2(aa_mul2(w2, s0), one2, v0);
+                v1 = aa_fma2(aa_mul2(w2, s1), one2, v1);
+                v2 = aa_fma2(aa_mul2(w2, s2), one2, v2);
+            };
 #pragma unroll 2
-                for (int q = 0; q < c.nt; ++q, pa += 3, pb += 3, wq += c.xw_stride) {
-                    const float4 w = *wq;
-                    const float2 w2 = make_float2(w.x, w.y), nw2 = make_float2(w.z, w.w);
-                    const unsigned a0 = __ldg(pa), a1 = __ldg(pa + 1), a2 = __ldg(pa + 2);
-                    const unsigned b0 = __ldg(pb), b1 = __ldg(pb + 1), b2 = __ldg(pb + 2);
-                    acc0 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a0 | 0x4B000000u), __uint_as_float(b0 | 0x4B000000u)), w2, nw2), one2, acc0);
-                    acc1 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a1 | 0x4B000000u), __uint_as_float(b1 | 0x4B000000u)), w2, nw2), one2, acc1);
-                    acc2 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a2 | 0x4B000000u), __uint_as_float(b2 | 0x4B000000u)), w2, nw2), one2, acc2);
-                }
+            for (int q = 0; q < n1; ++q) tap();
+            vs = c.ring;
+            for (int q = n1; q < n; ++q) tap();
+            // (uint8)max(0, min(255, acc + 0.5f))   simd_utils.hpp:2008-2009.  acc >= 0 (weights and pixels
+            // are), so only the upper clamp can act; the truncation is RZ(x + 2^23), and code * pre is
+            // fma(2^23 + code, pre, -2^23 pre), exactly RN(code * pre).
+            auto finish = [&](float2 v, int ch) {
+                float2 t = aa_fma2(v, one2, half2);
+                t.x = fminf(t.x, 255.0f);
+                t.y = fminf(t.y, 255.0f);
+                const float2 x = aa_fma2(aa_add2_rz(t, k2), pre2, nkpre2);
+                return aa_mul2(aa_fma2(x, one2, make_float2(c.nmean[ch], c.nmean[ch])),
+                               make_float2(c.inv_std[ch], c.inv_std[ch]));
+            };
+            const float2 o0 = finish(v0, 0), o1 = finish(v1, 1), o2 = finish(v2, 2);
+            put_at<DTYPE>(pA, o0.x);
+            put_at<DTYPE>(pA + c.chan_step, o1.x);
+            put_at<DTYPE>(pA + 2 * c.chan_step, o2.x);
+            if (c.validB) {
+                unsigned char* const pB = pA + c.dB;
+                put_at<DTYPE>(pB, o0.y);
+                put_at<DTYPE>(pB + c.chan_step, o1.y);
+                put_at<DTYPE>(pB + 2 * c.chan_step, o2.y);
             }
-            float2* slot = reinterpret_cast<float2*>(next_slot);
-            slot[0] = acc0;
-            slot[1] = acc1;
-            slot[2] = acc2;
-            next_slot += c.slot_bytes;
-            if (next_slot == c.ring_end) next_slot = c.myring;
+            ++r;
+            pA += c.row_step;
+            wrow += 4 * c.yt;
+            rec = r < c.rows ? aa_lds_i2(c.yrec + 8 * r) : make_int2(-1, 0);
         }
-        // ---- vertical pass, rounding, normalize, store --------------------------------------
-        float2 v0 = make_float2(0.0f, 0.0f), v1 = v0, v2 = v0;
-        const float* wr = c.yw + r * c.yt;
-        const unsigned char* vs = lo_slot;
-        for (int q = 0; q < n; ++q) {
-            const float w = wr[q];
-            const float2 w2 = make_float2(w, w);
-            const float2* slot = reinterpret_cast<const float2*>(vs);
-            vs += c.slot_bytes;
-            if (vs == c.ring_end) vs = c.myring;
-            v0 = aa_fma2(aa_mul2(w2, slot[0]), one2, v0);
-            v1 = aa_fma2(aa_mul2(w2, slot[1]), one2, v1);
-            v2 = aa_fma2(aa_mul2(w2, slot[2]), one2, v2);
-        }
-        // (uint8)max(0, min(255, acc + 0.5f))   simd_utils.hpp:2008-2009.  acc >= 0 (weights and pixels are),
-        // so only the upper clamp can act; the truncation is RZ(x + 2^23), and code * pre is
-        // fma(2^23 + code, pre, -2^23 pre), exactly RN(code * pre).
-        auto finish = [&](float2 v, int ch) {
-            float2 t = aa_fma2(v, one2, make_float2(0.5f, 0.5f));
-            t.x = fminf(t.x, 255.0f);
-            t.y = fminf(t.y, 255.0f);
-            const float2 x = aa_fma2(aa_add2_rz(t, k2), pre2, nkpre2);
-            return aa_mul2(aa_fma2(x, one2, make_float2(c.nmean[ch], c.nmean[ch])), make_float2(c.inv_std[ch], c.inv_std[ch]));
-        };
-        const float2 o0 = finish(v0, 0), o1 = finish(v1, 1), o2 = finish(v2, 2);
-        put<DTYPE>(c.out, oA, o0.x);
-        put<DTYPE>(c.out, oA + c.chan_step, o1.x);
-        put<DTYPE>(c.out, oA + 2 * c.chan_step, o2.x);
-        if (c.validB) {
-            put<DTYPE>(c.out, oB, o0.y);
-            put<DTYPE>(c.out, oB + c.chan_step, o1.y);
-            put<DTYPE>(c.out, oB + 2 * c.chan_step, o2.y);
-        }
+        if (r >= c.rows) break;
+        ++src;
+        slot_off += c.slot_bytes;
+        if (++slot == c.slots) slot = 0, slot_off = 0;
     }
 }
 
@@ -470,10 +563,10 @@ __global__ void __launch_bounds__(128) antialias_pair_kernel(const __grid_consta
     const int TC = a.tile_cols, TR = a.tile_rows, HT = TC / 2;  // HT = threads per CTA
     float4* const xw4 = reinterpret_cast<float4*>(smem);                   // [xt][HT] {wA, wB, -2^23 wA, -2^23 wB}
     unsigned char* const ring = reinterpret_cast<unsigned char*>(xw4 + a.xt * HT);  // [yt][HT] x 24 B: three float2 per thread
-    float* const scratch = reinterpret_cast<float*>(ring + a.yt * HT * 24);  // [xt][TC] unnormalized weights
-    float* const yw = scratch + a.xt * TC;                                 // [TR][yt]
-    int* const yl = reinterpret_cast<int*>(yw + TR * a.yt);                // [TR] first tap row
-    int* const yc = yl + TR;                                               // [TR] tap count
+    float* const scratch = reinterpret_cast<float*>(ring);                 // [xt][TC] unnormalized weights, dead before the ring is first written
+    const int ring_or_scratch = max(a.yt * HT * 24, a.xt * TC * 4);
+    int2* const yrec = reinterpret_cast<int2*>(ring + ring_or_scratch);     // [TR] {last tap row, tap count}
+    float* const yw = reinterpret_cast<float*>(yrec + TR);                 // [TR][yt]
 
     unsigned bid = blockIdx.x;
     const int ct = static_cast<int>(bid % static_cast<unsigned>(a.n_col_tiles));
@@ -576,27 +669,26 @@ __global__ void __launch_bounds__(128) antialias_pair_kernel(const __grid_consta
         aa_taps(ty0 + r, ch, yscale, ysup, ymax, yw + r * a.yt, 1, lo, n, wsum);
         if (wsum > 0.0f)
             for (int q = 0; q < n; ++q) yw[r * a.yt + q] = __fdiv_rn(yw[r * a.yt + q], wsum);
-        yl[r] = lo;
-        yc[r] = n;
+        yrec[r] = make_int2(lo + n - 1, n);
     }
     __syncthreads();
     if (!validA) return;
 
+    const int first_src = yrec[0].x - yrec[0].y + 1;
+    const int end_src = yrec[ty1 - ty0 - 1].x + 1;
     PairCtx c;
-    c.out = p.out;
     c.img = p.src + img_off;
     {
         // Ask L2 for the tile's whole source footprint now: every source row is a fresh DRAM line for
         // the thread that filters it, and the one-row register prefetch of the row loop covers an L2
         // hit, not a DRAM miss.  One request per 128-byte line that holds a byte some column taps.
-        const int r0 = yl[0], r1 = yl[ty1 - ty0 - 1] + yc[ty1 - ty0 - 1];
         const float cl = __fmul_rn(static_cast<float>(tx0), xscale) - xsup - 1.0f;
         const float cr = __fmul_rn(static_cast<float>(tx0 + tcw), xscale) + xsup + 1.0f;
         const int x0 = max(0, min(cw - 1, static_cast<int>(cl))), x1 = max(x0 + 1, min(cw, static_cast<int>(cr) + 1));
         const unsigned long long rowb = reinterpret_cast<unsigned long long>(c.img) +
                                         (static_cast<unsigned long long>(cy) * iw + cx + x0) * 3;
         const unsigned span = static_cast<unsigned>(x1 - x0) * 3u;
-        for (int rr = r0 + tid / 8; rr < r1; rr += blockDim.x / 8) {
+        for (int rr = first_src + tid / 8; rr < end_src; rr += blockDim.x / 8) {
             const unsigned long long b = rowb + static_cast<unsigned long long>(rr) * iw * 3;
             const unsigned long long e = b + span - 1;
             for (unsigned long long ln = (b & ~127ull) + 128ull * (tid & 7); ln <= e; ln += 128ull * 8)
@@ -606,16 +698,17 @@ __global__ void __launch_bounds__(128) antialias_pair_kernel(const __grid_consta
     c.row_pitch = static_cast<unsigned>(iw) * 3u;
     c.offA = static_cast<unsigned>((static_cast<long long>(cy) * iw + cx + firstA) * 3);
     c.offB = static_cast<unsigned>((static_cast<long long>(cy) * iw + cx + firstB) * 3);
-    c.xw = xw4 + tid;
-    c.xw_stride = HT;
-    c.yw = yw;
-    c.yl = yl;
-    c.yc = yc;
+    c.xw = aa_smem_u32(xw4 + tid);
+    c.xw_stride = static_cast<uint32_t>(HT) * 16u;
+    c.yw = aa_smem_u32(yw);
+    c.yrec = aa_smem_u32(yrec);
     c.yt = a.yt;
     c.rows = ty1 - ty0;
+    c.first_src = first_src;
+    c.end_src = end_src;
+    c.ring = aa_smem_u32(ring + tid * 24);
     c.slot_bytes = HT * 24;
-    c.myring = ring + tid * 24;
-    c.ring_end = c.myring + a.yt * c.slot_bytes;
+    c.slots = a.yt;
     c.nt = nt;
     c.one = p.one;
     c.pre = p.pre_scale;
@@ -625,21 +718,20 @@ __global__ void __launch_bounds__(128) antialias_pair_kernel(const __grid_consta
         c.inv_std[q] = p.inv_std[q];
     }
     c.validB = validB;
-    // where the two columns land after the flip, as element offsets of channel 0 at tile row 0
+    // where the two columns land after the flip
     const int xoA = flip ? (W - 1 - (tx0 + colA)) : tx0 + colA;
     const int xoB = flip ? (W - 1 - (tx0 + colB)) : tx0 + colB;
+    constexpr int kElem = DTYPE == 0 ? 4 : 2;
     if constexpr (LAYOUT == 0) {
-        const long long base = (static_cast<long long>(k) * 3 * H + ty0) * W;
-        c.oA = base + xoA;
-        c.oB = base + xoB;
-        c.row_step = W;
-        c.chan_step = static_cast<long long>(H) * W;
+        c.pA = static_cast<unsigned char*>(p.out) + ((static_cast<long long>(k) * 3 * H + ty0) * W + xoA) * kElem;
+        c.dB = static_cast<long long>(xoB - xoA) * kElem;
+        c.row_step = static_cast<long long>(W) * kElem;
+        c.chan_step = static_cast<long long>(H) * W * kElem;
     } else {
-        const long long base = (static_cast<long long>(k) * H + ty0) * W;
-        c.oA = (base + xoA) * 3;
-        c.oB = (base + xoB) * 3;
-        c.row_step = 3 * W;
-        c.chan_step = 1;
+        c.pA = static_cast<unsigned char*>(p.out) + ((static_cast<long long>(k) * H + ty0) * W + xoA) * 3 * kElem;
+        c.dB = static_cast<long long>(xoB - xoA) * 3 * kElem;
+        c.row_step = static_cast<long long>(W) * 3 * kElem;
+        c.chan_step = kElem;
     }
     // Word loads round the tap window out to 4-byte words; that must stay inside memory the caller
     // handed over: inside the image when images are separate allocations, inside the source range
@@ -649,17 +741,7 @@ __global__ void __launch_bounds__(128) antialias_pair_kernel(const __grid_consta
     const unsigned long long sa = reinterpret_cast<unsigned long long>(p.src);
     const bool words_ok = p.per_image_region ? ((ia & 3) == 0 && (ie & 3) == 0)
                                              : ((ia & ~3ull) >= sa && ((ie + 3) & ~3ull) <= sa + p.src_bytes);
-    switch (words_ok ? nt : 0) {
-        case 1: pair_rows<DTYPE, 1>(c); break;
-        case 2: pair_rows<DTYPE, 2>(c); break;
-        case 3: pair_rows<DTYPE, 3>(c); break;
-        case 4: pair_rows<DTYPE, 4>(c); break;
-        case 5: pair_rows<DTYPE, 5>(c); break;
-        case 6: pair_rows<DTYPE, 6>(c); break;
-        case 7: pair_rows<DTYPE, 7>(c); break;
-        case 8: pair_rows<DTYPE, 8>(c); break;
-        default: pair_rows<DTYPE, 0>(c); break;
-    }
+    pair_rows<DTYPE>(c, words_ok && nt <= kAAUnrolledTaps ? nt : 0);
 }
 
 std::atomic<unsigned long long> g_aa_launches{0};

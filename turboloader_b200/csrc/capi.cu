@@ -265,8 +265,11 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
         a.n_row_tiles = (d.dst_h + a.tile_rows - 1) / a.tile_rows;
         a.tile_cols = std::min(256, round_up(d.dst_w, 32));
         for (;;) {
-            const int xw_words = (a.pair ? 3 : 1) * a.xt * a.tile_cols;
-            a.smem_bytes = 4 * (xw_words + a.tile_rows * a.yt + 2 * a.tile_rows + a.yt * 3 * a.tile_cols);
+            // one column: weights [xt][cols], ring [yt][3][cols]; pair: weights [xt][cols/2] x 16 B, then
+            // the ring sharing its bytes with the [xt][cols] table the weights are normalized from
+            const int xw_words = (a.pair ? 2 : 1) * a.xt * a.tile_cols;
+            const int ring_words = a.pair ? std::max(a.yt * 3, a.xt) * a.tile_cols : a.yt * 3 * a.tile_cols;
+            a.smem_bytes = 4 * (xw_words + a.tile_rows * a.yt + 2 * a.tile_rows + ring_words);
             if (a.smem_bytes <= tlb::kAAMaxSmem || a.tile_cols <= 32) break;
             a.tile_cols = round_up(a.tile_cols / 2, 32);
         }
