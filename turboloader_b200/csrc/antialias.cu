@@ -633,43 +633,73 @@ __global__ void __launch_bounds__(128) antialias_pair_kernel(const __grid_consta
     }
 
     // ---- taps: each thread builds the tables of its two columns; one thread per tile row -------
-    // nt = horizontal taps the loop runs for every column of this sample; a column's own taps sit at
-    // positions [shift, shift + n) of that window, whose first pixel is lo - shift >= 0.
-    const int nt = min(xmax, cw);
+    // Taps whose weight is exactly zero are dropped from the front and the back of every table: the
+    // reference multiplies them in, but w = +0 times a non-negative pixel is +0 and acc + (+0) is acc,
+    // so the sums keep every bit.  The tap bounds lo = floor(c - s), hi = ceil(c + s) reach up to one
+    // pixel past the filter's support on either side; without them a column has at most ceil(2 s)
+    // taps instead of ceil(2 s) + 2 -- three instead of five for a mild downscale.
+    // nt = taps the horizontal loop runs for every column of this tile (the most any of its columns
+    // kept); a column's own taps sit at positions [shift, shift + n) of that window, whose first
+    // pixel is lo - shift >= 0.
+    __shared__ int s_nt;
+    if (tid == 0) s_nt = 1;
+    __syncthreads();
     const int colA = tid, colB = tid + HT;
     const bool validA = colA < tcw, validB = colB < tcw;
+    struct ColTaps {
+        int lo, n, z0;   // first kept tap (crop-local pixel), kept taps, dropped in front
+        float wsum;
+    } tA{0, 0, 0, 0.0f}, tB{0, 0, 0, 0.0f};
+    {
+        auto taps_of = [&](int col, ColTaps& t) {
+            int lo, n;
+            aa_taps(tx0 + col, cw, xscale, xsup, xmax, scratch + col, TC, lo, n, t.wsum);
+            int z0 = 0, z1 = n;
+            while (z0 < n - 1 && scratch[z0 * TC + col] == 0.0f) ++z0;
+            while (z1 > z0 + 1 && scratch[(z1 - 1) * TC + col] == 0.0f) --z1;
+            t.lo = lo + z0;
+            t.n = z1 - z0;
+            t.z0 = z0;
+            atomicMax(&s_nt, t.n);
+        };
+        if (validA) taps_of(colA, tA);
+        if (validB) taps_of(colB, tB);
+    }
+    for (int r = tid; r < ty1 - ty0; r += blockDim.x) {
+        float wsum;
+        int lo, n;
+        float* const w = yw + r * a.yt;
+        aa_taps(ty0 + r, ch, yscale, ysup, ymax, w, 1, lo, n, wsum);
+        int z0 = 0, z1 = n;
+        while (z0 < n - 1 && w[z0] == 0.0f) ++z0;
+        while (z1 > z0 + 1 && w[z1 - 1] == 0.0f) --z1;
+        for (int q = z0; q < z1; ++q) w[q - z0] = wsum > 0.0f ? __fdiv_rn(w[q], wsum) : w[q];
+        yrec[r] = make_int2(lo + z1 - 1, z1 - z0);
+    }
+    __syncthreads();
+    const int nt = s_nt;
     int firstA = 0, firstB = 0;  // first pixel of each column's tap window (crop-local)
     {
-        auto build = [&](int col, bool valid, int& first, int half) {
-            int lo = 0, n = 0, shift = 0;
-            float wsum = 0.0f;
+        auto fill = [&](int col, bool valid, const ColTaps& t, int& first, int half) {
+            int shift = 0;
             if (valid) {
-                aa_taps(tx0 + col, cw, xscale, xsup, xmax, scratch + col, TC, lo, n, wsum);
-                first = max(0, min(lo, cw - nt));
-                shift = lo - first;
+                first = max(0, min(t.lo, cw - nt));   // nt <= cw: no column keeps more taps than the crop has pixels
+                shift = t.lo - first;
             }
             for (int q = 0; q < nt; ++q) {
                 const int j = q - shift;
                 float w = 0.0f;
-                if (valid && j >= 0 && j < n) {
-                    w = scratch[j * TC + col];
-                    if (wsum > 0.0f) w = __fdiv_rn(w, wsum);
+                if (valid && j >= 0 && j < t.n) {
+                    w = scratch[(j + t.z0) * TC + col];
+                    if (t.wsum > 0.0f) w = __fdiv_rn(w, t.wsum);
                 }
                 float* e = reinterpret_cast<float*>(xw4 + q * HT + tid);
                 e[half] = w;
                 e[2 + half] = __fmul_rn(-8388608.0f, w);
             }
         };
-        build(colA, validA, firstA, 0);
-        build(colB, validB, firstB, 1);
-    }
-    for (int r = tid; r < ty1 - ty0; r += blockDim.x) {
-        float wsum;
-        int lo, n;
-        aa_taps(ty0 + r, ch, yscale, ysup, ymax, yw + r * a.yt, 1, lo, n, wsum);
-        if (wsum > 0.0f)
-            for (int q = 0; q < n; ++q) yw[r * a.yt + q] = __fdiv_rn(yw[r * a.yt + q], wsum);
-        yrec[r] = make_int2(lo + n - 1, n);
+        fill(colA, validA, tA, firstA, 0);
+        fill(colB, validB, tB, firstB, 1);
     }
     __syncthreads();
     if (!validA) return;
