@@ -372,16 +372,20 @@ __device__ __forceinline__ void put_at(unsigned char* ptr, float v) {
         *reinterpret_cast<__nv_bfloat16*>(ptr) = __float2bfloat16_rn(v);
 }
 
-struct Acc3 {
-    float2 c0, c1, c2;
-};
+// The horizontal sums of one source row go to the thread's ring slot.
+__device__ __forceinline__ void ring_store(uint32_t at, float2 c0, float2 c1, float2 c2) {
+    aa_sts_f2<0>(at, c0);
+    aa_sts_f2<8>(at, c1);
+    aa_sts_f2<16>(at, c2);
+}
 
-// Horizontal pass of one source row for a column pair whose sample has exactly NT taps.  `a`, `b`
+// Horizontal pass of one source row for a column pair whose tile has exactly NT taps.  `a`, `b`
 // hold the row's words on entry; they are realigned first, so that the same registers can take
-// the NEXT row's words (requested here, a row of arithmetic ahead of their use).
+// the NEXT row's words (requested here, a row of arithmetic ahead of their use).  The first tap
+// starts the sums (0 + x is x), the others add to them in tap order.
 template <int NT>
-__device__ __forceinline__ Acc3 hrow_words(const PairCtx& c, const unsigned char* imga, unsigned gA, unsigned gB,
-                                           int src, RowWords& a, RowWords& b, float2 one2) {
+__device__ __forceinline__ void hrow_words(const PairCtx& c, const unsigned char* imga, unsigned gA, unsigned gB,
+                                           int src, RowWords& a, RowWords& b, float2 one2, uint32_t ring_at) {
     constexpr int NS = (3 * NT + 3) / 4;
     unsigned sA[NS], sB[NS];
 #pragma unroll
@@ -394,8 +398,7 @@ __device__ __forceinline__ Acc3 hrow_words(const PairCtx& c, const unsigned char
         load_window<NT>(imga, rowoff + gA, a);
         load_window<NT>(imga, rowoff + gB, b);
     }
-    Acc3 acc;
-    acc.c0 = acc.c1 = acc.c2 = make_float2(0.0f, 0.0f);
+    float2 acc0, acc1, acc2;
     uint32_t wq = c.xw;
 #pragma unroll
     for (int q = 0; q < NT; ++q, wq += c.xw_stride) {
@@ -409,31 +412,36 @@ __device__ __forceinline__ Acc3 hrow_words(const PairCtx& c, const unsigned char
             px[ch].x = __uint_as_float(__byte_perm(sA[j >> 2], kHi, 0x7440u | (j & 3)));
             px[ch].y = __uint_as_float(__byte_perm(sB[j >> 2], kHi, 0x7440u | (j & 3)));
         }
-        acc.c0 = aa_fma2(aa_fma2(px[0], w2, nw2), one2, acc.c0);
-        acc.c1 = aa_fma2(aa_fma2(px[1], w2, nw2), one2, acc.c1);
-        acc.c2 = aa_fma2(aa_fma2(px[2], w2, nw2), one2, acc.c2);
+        if (q == 0) {
+            acc0 = aa_fma2(px[0], w2, nw2);
+            acc1 = aa_fma2(px[1], w2, nw2);
+            acc2 = aa_fma2(px[2], w2, nw2);
+        } else {
+            acc0 = aa_fma2(aa_fma2(px[0], w2, nw2), one2, acc0);
+            acc1 = aa_fma2(aa_fma2(px[1], w2, nw2), one2, acc1);
+            acc2 = aa_fma2(aa_fma2(px[2], w2, nw2), one2, acc2);
+        }
     }
-    return acc;
+    ring_store(ring_at, acc0, acc1, acc2);
 }
 
 // ... any tap count, byte loads, nothing requested ahead.
-__device__ __forceinline__ Acc3 hrow_bytes(const PairCtx& c, int src, float2 one2) {
+__device__ __forceinline__ void hrow_bytes(const PairCtx& c, int src, float2 one2, uint32_t ring_at) {
     const unsigned char* pa = c.img + c.offA + static_cast<unsigned long long>(src) * c.row_pitch;
     const unsigned char* pb = c.img + c.offB + static_cast<unsigned long long>(src) * c.row_pitch;
     uint32_t wq = c.xw;
-    Acc3 acc;
-    acc.c0 = acc.c1 = acc.c2 = make_float2(0.0f, 0.0f);
+    float2 acc0 = make_float2(0.0f, 0.0f), acc1 = acc0, acc2 = acc0;
 #pragma unroll 2
     for (int q = 0; q < c.nt; ++q, pa += 3, pb += 3, wq += c.xw_stride) {
         const float4 w = aa_lds_f4(wq);
         const float2 w2 = make_float2(w.x, w.y), nw2 = make_float2(w.z, w.w);
         const unsigned a0 = __ldg(pa), a1 = __ldg(pa + 1), a2 = __ldg(pa + 2);
         const unsigned b0 = __ldg(pb), b1 = __ldg(pb + 1), b2 = __ldg(pb + 2);
-        acc.c0 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a0 | 0x4B000000u), __uint_as_float(b0 | 0x4B000000u)), w2, nw2), one2, acc.c0);
-        acc.c1 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a1 | 0x4B000000u), __uint_as_float(b1 | 0x4B000000u)), w2, nw2), one2, acc.c1);
-        acc.c2 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a2 | 0x4B000000u), __uint_as_float(b2 | 0x4B000000u)), w2, nw2), one2, acc.c2);
+        acc0 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a0 | 0x4B000000u), __uint_as_float(b0 | 0x4B000000u)), w2, nw2), one2, acc0);
+        acc1 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a1 | 0x4B000000u), __uint_as_float(b1 | 0x4B000000u)), w2, nw2), one2, acc1);
+        acc2 = aa_fma2(aa_fma2(make_float2(__uint_as_float(a2 | 0x4B000000u), __uint_as_float(b2 | 0x4B000000u)), w2, nw2), one2, acc2);
     }
-    return acc;
+    ring_store(ring_at, acc0, acc1, acc2);
 }
 
 // Rows of one tile for a thread's column pair, as a walk down the SOURCE rows the tile taps: each
@@ -480,25 +488,17 @@ __device__ __forceinline__ void pair_rows(const PairCtx& c, const int mode) {
         }
     }
     for (;;) {
-        // ---- horizontal pass of source row `src` into its ring slot ------------------------------
-        Acc3 h;
-        switch (mode) {
-            case 1: h = hrow_words<1>(c, imga, gA, gB, src, bufA, bufB, one2); break;
-            case 2: h = hrow_words<2>(c, imga, gA, gB, src, bufA, bufB, one2); break;
-            case 3: h = hrow_words<3>(c, imga, gA, gB, src, bufA, bufB, one2); break;
-            case 4: h = hrow_words<4>(c, imga, gA, gB, src, bufA, bufB, one2); break;
-            case 5: h = hrow_words<5>(c, imga, gA, gB, src, bufA, bufB, one2); break;
-            case 6: h = hrow_words<6>(c, imga, gA, gB, src, bufA, bufB, one2); break;
-            case 7: h = hrow_words<7>(c, imga, gA, gB, src, bufA, bufB, one2); break;
-            case 8: h = hrow_words<8>(c, imga, gA, gB, src, bufA, bufB, one2); break;
-            default: h = hrow_bytes(c, src, one2); break;
-        }
-        {
-            const uint32_t at = c.ring + slot_off;
-            aa_sts_f2<0>(at, h.c0);
-            aa_sts_f2<8>(at, h.c1);
-            aa_sts_f2<16>(at, h.c2);
-        }
+        // ---- horizontal pass of source row `src` into its ring slot (commonest widths first) -------
+        const uint32_t ring_at = c.ring + slot_off;
+        if (mode == 3) hrow_words<3>(c, imga, gA, gB, src, bufA, bufB, one2, ring_at);
+        else if (mode == 2) hrow_words<2>(c, imga, gA, gB, src, bufA, bufB, one2, ring_at);
+        else if (mode == 4) hrow_words<4>(c, imga, gA, gB, src, bufA, bufB, one2, ring_at);
+        else if (mode == 5) hrow_words<5>(c, imga, gA, gB, src, bufA, bufB, one2, ring_at);
+        else if (mode == 6) hrow_words<6>(c, imga, gA, gB, src, bufA, bufB, one2, ring_at);
+        else if (mode == 7) hrow_words<7>(c, imga, gA, gB, src, bufA, bufB, one2, ring_at);
+        else if (mode == 8) hrow_words<8>(c, imga, gA, gB, src, bufA, bufB, one2, ring_at);
+        else if (mode == 1) hrow_words<1>(c, imga, gA, gB, src, bufA, bufB, one2, ring_at);
+        else hrow_bytes(c, src, one2, ring_at);
         // ---- finish the output rows whose last tap row this was ----------------------------------
         while (rec.x == src) {
             const int n = rec.y;
@@ -507,20 +507,26 @@ __device__ __forceinline__ void pair_rows(const PairCtx& c, const int mode) {
             const int n1 = min(n, c.slots - lo_slot);   // taps before the ring wraps
             uint32_t vs = c.ring + lo_slot * c.slot_bytes;
             uint32_t wq = wrow;
-            float2 v0 = make_float2(0.0f, 0.0f), v1 = v0, v2 = v0;
+            float2 v0, v1, v2;
+            {   // the first tap starts the sums (0 + x is x)
+                const float w = aa_lds_f(wq);
+                const float2 w2 = make_float2(w, w);
+                v0 = aa_mul2(w2, aa_lds_f2o<0>(vs));
+                v1 = aa_mul2(w2, aa_lds_f2o<8>(vs));
+                v2 = aa_mul2(w2, aa_lds_f2o<16>(vs));
+            }
             auto tap = [&]() {
+                wq += 4;
+                vs += c.slot_bytes;
                 const float w = aa_lds_f(wq);
                 const float2 w2 = make_float2(w, w);
                 const float2 s0 = aa_lds_f2o<0>(vs), s1 = aa_lds_f2o<8>(vs), s2 = aa_lds_f2o<16>(vs);
-                wq += 4;
-                vs += c.slot_bytes;
                 v0 = aa_fma2(aa_mul2(w2, s0), one2, v0);
                 v1 = aa_fma2(aa_mul2(w2, s1), one2, v1);
                 v2 = aa_fma2(aa_mul2(w2, s2), one2, v2);
             };
-#pragma unroll 2
-            for (int q = 0; q < n1; ++q) tap();
-            vs = c.ring;
+            for (int q = 1; q < n1; ++q) tap();
+            vs = c.ring - c.slot_bytes;
             for (int q = n1; q < n; ++q) tap();
             // (uint8)max(0, min(255, acc + 0.5f))   simd_utils.hpp:2008-2009.  acc >= 0 (weights and pixels
             // are), so only the upper clamp can act; the truncation is RZ(x + 2^23), and code * pre is

@@ -261,7 +261,8 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
         // take 3x the column weights of the one-column kernel, so very wide filters get narrower tiles.
         static const bool one_col = std::getenv("TLB_AA_ONE_COLUMN") != nullptr;
         a.pair = one_col ? 0 : 1;
-        a.tile_rows = std::min(32, d.dst_h);
+        static const int aa_rows = env_int("TLB_AA_TILE_ROWS", 32);
+        a.tile_rows = std::min(std::max(aa_rows, 1), d.dst_h);
         a.n_row_tiles = (d.dst_h + a.tile_rows - 1) / a.tile_rows;
         a.tile_cols = std::min(256, round_up(d.dst_w, 32));
         for (;;) {
