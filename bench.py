@@ -885,8 +885,9 @@ def main():
                    "l2": f"per-step traffic {(rd + wr) / 1e6:.0f} MB exceeds the 126 MB L2; {args.sets} distinct "
                          "input/output sets are cycled"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": ncu_traffic(wl.name), "peak_source": peak_src,
-                     "algorithmic_bytes_per_launch": rd + wr, "kernel": "fused_transform_kernel"},
+                     "traffic": ncu_traffic(("antialias_" if args.antialias else "") + wl.name), "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": rd + wr,
+                     "kernel": "antialias_pair_kernel" if args.antialias else "fused_transform_kernel"},
         "gpu_launches": int(launches),
     }
     if cores is not None:
@@ -996,7 +997,7 @@ def main():
         except Exception as e:
             line["loader_epoch"] = {"error": repr(e)}
         # The opt-in antialiased (triangle filter) resize on the default workload: same inputs, the
-        # descriptor's antialias flag set.  Quality path: 3-4x the arithmetic of the bilinear kernel.
+        # descriptor's antialias flag set.  Quality path: about twice the arithmetic of the bilinear kernel.
         try:
             torch.cuda.empty_cache()
             bb = make_device_batches(args.workload, seed, device, 2)
@@ -1006,7 +1007,7 @@ def main():
             r, w = bb[0].wl.algorithmic_bytes()
             line["antialias"] = {"workload": args.workload, "img_per_s": 20 * bb[0].wl.n / s,
                                  "GB_per_s": (r + w) / (s / 20) / 1e9, "frac_of_peak": (r + w) / (s / 20) / 1e9 / peak,
-                                 "kernel": "antialias_kernel"}
+                                 "kernel": "antialias_pair_kernel"}
             del bb
         except Exception as e:
             line["antialias"] = {"error": repr(e)}

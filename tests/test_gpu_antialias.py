@@ -66,3 +66,50 @@ def test_invalid_samples_are_zero_filled_and_reported():
     assert (res["out"][3] == 0).all()
     keep = [i for i in range(8) if i != 3]
     assert np.array_equal(res["out"][keep], want[keep])
+
+
+def test_tiny_crops_odd_widths_and_two_column_tiles():
+    """Crops narrower than the filter (the tap window is the whole crop row), an output width that is
+    no multiple of 32 (the second column of some threads does not exist), and an output wide enough
+    for two column tiles of which the second is mostly empty."""
+    wl = S.config2(seed=21, n=12, lo=20, hi=60, dst=40)
+    wl.dst_w = 50
+    for i, (w, h) in enumerate([(1, 1), (2, 3), (3, 2), (1, 7), (5, 1), (4, 4)]):
+        wl.boxes[i] = (i % 3, (i + 1) % 4, w, h)
+    _check(wl)
+    wide = S.config2(seed=22, n=3, lo=200, hi=400, dst=20)
+    wide.dst_w = 300
+    _check(wide)
+    wide.dtype, wide.channels_last = "bf16", True
+    _check(wide)
+
+
+@pytest.mark.parametrize("pad", [1, 2, 3])
+def test_source_off_the_word_grid(pad):
+    """The packed kernel fetches tap windows as aligned 32-bit words.  A source that starts 1..3 bytes
+    off the word grid sends its first image (words would start before the buffer) and its last one
+    (words would end after it) through byte loads, and every other image through realigned words."""
+    wl = S.config2(seed=23 + pad, n=10, lo=50, hi=130, dst=48)
+    _check(wl, src_pad_front=pad)
+
+
+def test_one_column_kernel_still_matches():
+    """The packed kernel and the one-column kernel it replaced are the same function."""
+    import subprocess, sys, textwrap
+    code = textwrap.dedent("""
+        import numpy as np
+        from turboloader_b200 import synthetic as S
+        import sys; sys.path.insert(0, 'tests')
+        from helpers import expected_antialias, run_gpu
+        def aa(d):
+            d.antialias = 1; d.max_crop_h = 0
+        wl = S.config2(seed=29, n=8, lo=80, hi=300, dst=64)
+        out = run_gpu(wl, mutate=aa)["out"]
+        assert np.array_equal(out.view(np.uint32), expected_antialias(wl).view(np.uint32))
+        print("ok")
+    """)
+    import os
+    env = dict(os.environ, TLB_AA_ONE_COLUMN="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]

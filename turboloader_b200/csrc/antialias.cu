@@ -66,6 +66,7 @@ template <int DTYPE, int LAYOUT>
 __global__ void __launch_bounds__(256) antialias_kernel(const __grid_constant__ FusedParams p,
                                                         const __grid_constant__ AAPlan a) {
     extern __shared__ __align__(16) unsigned char smem[];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see the packed kernel
     const int tid = threadIdx.x;
     const int TC = a.tile_cols, TR = a.tile_rows;
     float* const xw = reinterpret_cast<float*>(smem);                      // [xt][TC]
@@ -565,6 +566,9 @@ template <int DTYPE, int LAYOUT>
 __global__ void __launch_bounds__(128) antialias_pair_kernel(const __grid_constant__ FusedParams p,
                                                              const __grid_constant__ AAPlan a) {
     extern __shared__ __align__(16) unsigned char smem[];
+    // Lets a launch made with programmatic stream serialization start behind this one as soon as
+    // every CTA of this one has been scheduled; a no-op for any other launch.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int tid = threadIdx.x;
     const int TC = a.tile_cols, TR = a.tile_rows, HT = TC / 2;  // HT = threads per CTA
     float4* const xw4 = reinterpret_cast<float4*>(smem);                   // [xt][HT] {wA, wB, -2^23 wA, -2^23 wB}
@@ -783,11 +787,23 @@ __global__ void __launch_bounds__(128) antialias_pair_kernel(const __grid_consta
 std::atomic<unsigned long long> g_aa_launches{0};
 
 template <int DTYPE, int LAYOUT>
-int launch_one(const FusedParams& p, const AAPlan& a, cudaStream_t st) {
+int launch_one(const FusedParams& p, const AAPlan& a, cudaStream_t st, unsigned flags) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(a.grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(a.pair ? a.tile_cols / 2 : a.tile_cols));
+    cfg.dynamicSmemBytes = static_cast<size_t>(a.smem_bytes);
+    cfg.stream = st;
+    // Same contract as the bilinear kernel's launch: with kLaunchOverlap the launch may start while
+    // the kernel before it in the stream drains its last CTAs; it never waits on that kernel.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & kLaunchOverlap) ? 1 : 0;
     if (a.pair)
-        antialias_pair_kernel<DTYPE, LAYOUT><<<static_cast<unsigned>(a.grid), a.tile_cols / 2, a.smem_bytes, st>>>(p, a);
+        cudaLaunchKernelEx(&cfg, antialias_pair_kernel<DTYPE, LAYOUT>, p, a);
     else
-        antialias_kernel<DTYPE, LAYOUT><<<static_cast<unsigned>(a.grid), a.tile_cols, a.smem_bytes, st>>>(p, a);
+        cudaLaunchKernelEx(&cfg, antialias_kernel<DTYPE, LAYOUT>, p, a);
     g_aa_launches.fetch_add(1, std::memory_order_relaxed);
     return static_cast<int>(cudaGetLastError());
 }
@@ -818,10 +834,10 @@ int prepare_antialias() {
     return e;
 }
 
-int launch_antialias(const FusedParams& p, const AAPlan& a, int out_dtype, int out_layout, void* stream) {
+int launch_antialias(const FusedParams& p, const AAPlan& a, int out_dtype, int out_layout, void* stream, unsigned flags) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (out_dtype == 0) return out_layout == 0 ? launch_one<0, 0>(p, a, st) : launch_one<0, 1>(p, a, st);
-    return out_layout == 0 ? launch_one<1, 0>(p, a, st) : launch_one<1, 1>(p, a, st);
+    if (out_dtype == 0) return out_layout == 0 ? launch_one<0, 0>(p, a, st, flags) : launch_one<0, 1>(p, a, st, flags);
+    return out_layout == 0 ? launch_one<1, 0>(p, a, st, flags) : launch_one<1, 1>(p, a, st, flags);
 }
 
 unsigned long long antialias_launch_count() { return g_aa_launches.load(std::memory_order_relaxed); }

@@ -279,7 +279,8 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
             return fail(TLB_ERR_TOO_LARGE, "antialias: a %d-tap filter does not fit the shared-memory tables", std::max(a.xt, a.yt));
         a.grid = static_cast<long long>(d.n) * a.n_row_tiles * a.n_col_tiles;
         if (a.grid > 0x7fffffffll) return fail(TLB_ERR_TOO_LARGE, "antialias: too many tiles for one launch");
-        cudaError_t e = static_cast<cudaError_t>(tlb::launch_antialias(p, a, d.out_dtype, d.out_layout, stream));
+        const unsigned aflags = (honour_flags && (d.flags & TLB_FLAG_LAUNCH_OVERLAP)) ? tlb::kLaunchOverlap : 0u;
+        cudaError_t e = static_cast<cudaError_t>(tlb::launch_antialias(p, a, d.out_dtype, d.out_layout, stream, aflags));
         if (e != cudaSuccess) return cuda_fail(e, "antialias_kernel launch");
         return TLB_OK;
     }
