@@ -1001,13 +1001,21 @@ def main():
         try:
             torch.cuda.empty_cache()
             bb = make_device_batches(args.workload, seed, device, 2)
-            for b in bb:
-                b.desc.antialias = 1
-            s = time_steps(bb, lib, stream, 20, 3, torch, barrier)
             r, w = bb[0].wl.algorithmic_bytes()
-            line["antialias"] = {"workload": args.workload, "img_per_s": 20 * bb[0].wl.n / s,
-                                 "GB_per_s": (r + w) / (s / 20) / 1e9, "frac_of_peak": (r + w) / (s / 20) / 1e9 / peak,
-                                 "kernel": "antialias_pair_kernel"}
+            aa = {"workload": args.workload, "kernel": "antialias_pair_kernel",
+                  "traffic": ncu_traffic("antialias_" + args.workload)}
+            for on in (True, False):  # as `value` (launches overlap head to tail), then every launch serialized
+                for b in bb:
+                    b.desc.antialias = 1
+                    b.set_overlap(on)
+                s = time_steps(bb, lib, stream, 20, 3, torch, barrier)
+                fig = {"img_per_s": 20 * bb[0].wl.n / s, "GB_per_s": (r + w) / (s / 20) / 1e9,
+                       "frac_of_peak": (r + w) / (s / 20) / 1e9 / peak}
+                if on:
+                    aa.update(fig)
+                else:
+                    aa["serialized"] = fig
+            line["antialias"] = aa
             del bb
         except Exception as e:
             line["antialias"] = {"error": repr(e)}
