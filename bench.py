@@ -552,12 +552,56 @@ def time_steps_repeated(batches, lib, stream, steps, warmup, torch, barrier, rep
     return out
 
 
-def rank_cores(rank, world):
-    """A disjoint set of host cores for this rank (the allowed cores split into `world` blocks)."""
-    cores = sorted(os.sched_getaffinity(0))
-    per = max(1, len(cores) // world)
-    mine = cores[rank * per:(rank + 1) * per] or cores
-    return mine
+def _cpulist(text):
+    out = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        out.update(range(int(lo), int(hi or lo) + 1))
+    return out
+
+
+def gpu_numa_node(torch, index):
+    """NUMA node the GPU's PCIe slot hangs off (sysfs), or None when the host does not say."""
+    try:
+        pr = torch.cuda.get_device_properties(index)
+        addr = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{addr}/numa_node") as f:
+            node = int(f.read().strip())
+        return node if node >= 0 else None
+    except Exception:
+        return None
+
+
+def rank_cores(rank, world, torch=None):
+    """A disjoint set of host cores for this rank.  When the host tells which NUMA node each GPU
+    is attached to, a rank gets cores of ITS GPU's node (split among the ranks that share the
+    node), so that the pinned buffers it allocates and fills afterwards are local to the PCIe root
+    its GPU reads them through; otherwise the allowed cores are split into `world` equal blocks.
+    Returns (cores, numa node or None)."""
+    allowed = sorted(os.sched_getaffinity(0))
+    per = max(1, len(allowed) // world)
+    fallback = allowed[rank * per:(rank + 1) * per] or allowed
+    if torch is None:
+        return fallback, None
+    try:
+        nodes = [gpu_numa_node(torch, r) for r in range(world)]
+        if any(n is None for n in nodes):
+            return fallback, None
+        chosen = {}
+        for node in sorted(set(nodes)):
+            with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+                local = sorted(_cpulist(f.read()) & set(allowed))
+            sharers = [r for r in range(world) if nodes[r] == node]
+            share = len(local) // len(sharers)
+            if share < 1:
+                return fallback, None
+            for i, r in enumerate(sharers):
+                chosen[r] = local[i * share:(i + 1) * share]
+        return chosen[rank], nodes[rank]
+    except Exception:
+        return fallback, None
 
 
 def sharded_scaling_leg(args, lib, torch, device, stream, rank, world, dist, barrier, peak, epochs=7):
@@ -803,11 +847,12 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     cores = None
+    numa_node = None
     all_cores = os.sched_getaffinity(0)
     if world > 1:
         # Every rank feeds its GPU from its own block of host cores.
         try:
-            cores = rank_cores(local_rank, world)
+            cores, numa_node = rank_cores(local_rank, world, torch)
             os.sched_setaffinity(0, cores)
         except OSError:
             cores = None
@@ -936,6 +981,7 @@ def main():
                            "h2d_GB_per_s_per_rank_alone": [round(float(v), 2) for v in alone.tolist()],
                            "h2d_GB_per_s_per_rank_together": [round(float(v), 2) for v in tog.tolist()],
                            "host_cores_per_rank": len(cores) if cores else None,
+                           "numa_node_of_rank0": numa_node,
                            "note": "no collective is involved: the ranks share the host's memory system and PCIe "
                                    "root ports; compare each rank's rate alone with its rate when all ranks run"}
         if rank == 0:

@@ -105,11 +105,15 @@ def test_host_to_device_streaming_entry():
     assert check_bf16(out.view(torch.int16).cpu().numpy().view(np.uint16), expected(wl)) == 0
 
 
-def test_pinned_host_images_are_gathered_by_the_gpu():
-    """Images in page-locked host memory take the GPU-side gather path (no host packing); the
-    result must equal the oracle exactly, for odd widths, any alignment, all output forms."""
+@pytest.mark.parametrize("direct", [True, False])
+def test_pinned_host_images_need_no_host_packing(direct, monkeypatch):
+    """Images in page-locked host memory are read by the GPU itself: by default the fused kernel
+    pulls the crop rows straight out of the mapped host images (one launch per call); with
+    TLB_HOST_DIRECT=0 a gather kernel packs them into device memory first (two launches).  Either
+    way the result must equal the oracle exactly, for odd widths, any alignment, all output forms."""
     import torch
     lib = _capi.load()
+    monkeypatch.setenv("TLB_HOST_DIRECT", "1" if direct else "0")
     for seed, dtype, layout, cl in [(41, _capi.TLB_F32, _capi.TLB_NCHW, False), (42, _capi.TLB_BF16, _capi.TLB_NHWC, True)]:
         wl = S.config2(seed=seed, n=14, lo=33, hi=131, dst=56)
         wl.dtype, wl.channels_last = ("f32" if dtype == _capi.TLB_F32 else "bf16"), cl
@@ -134,13 +138,43 @@ def test_pinned_host_images_are_gathered_by_the_gpu():
                                                          C.c_void_p(torch.cuda.current_stream().cuda_stream))
             assert rc == 0, lib.tlb_last_error()
         torch.cuda.synchronize()
-        assert t.launch_count() - before == 6  # gather + fused transform per call
+        assert t.launch_count() - before == (3 if direct else 6)
         assert int(status.item()) == 0
         want = expected(wl)
         if dtype == _capi.TLB_F32:
             assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
         else:
             assert check_bf16(out.view(torch.int16).cpu().numpy().view(np.uint16), want) == 0
+
+
+def test_separately_pinned_host_images_whole_and_edge_crops():
+    """Every image in its own page-locked allocation (as a decoder pool hands them out), with crops
+    that touch the first and the last byte of their image: the direct path may not read a byte
+    outside an image, and must still produce the oracle's bits."""
+    import torch
+    lib = _capi.load()
+    wl = S.config2(seed=43, n=9, lo=17, hi=90, dst=40)
+    for i in range(wl.n):  # whole image, top-left corner, bottom-right corner, ...
+        w, h = int(wl.sizes[i, 0]), int(wl.sizes[i, 1])
+        wl.boxes[i] = [(0, 0, w, h), (0, 0, max(1, w // 2), max(1, h // 3)), (w - max(1, w // 3), h - max(1, h // 2), max(1, w // 3), max(1, h // 2))][i % 3]
+    pins, refs, crops = [], (_capi.ImageRef * wl.n)(), (_capi.CropParams * wl.n)()
+    for i in range(wl.n):
+        w, h = int(wl.sizes[i, 0]), int(wl.sizes[i, 1])
+        o = int(wl.offsets[i])
+        pimg = torch.from_numpy(wl.src[o:o + w * h * 3].copy()).pin_memory()
+        pins.append(pimg)
+        refs[i].data, refs[i].w, refs[i].h = pimg.data_ptr(), w, h
+        crops[i].x, crops[i].y, crops[i].w, crops[i].h = (float(v) for v in wl.boxes[i])
+        crops[i].flip = int(wl.flips[i])
+    out = torch.empty((wl.n, 3, 40, 40), dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = lib.tlb_crop_resize_normalize_to_device(refs, crops, wl.n, 40, 40, _capi.f3(wl.mean), _capi.f3(wl.std), 1,
+                                                 out.data_ptr(), _capi.TLB_F32, _capi.TLB_NCHW, status.data_ptr(),
+                                                 C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, lib.tlb_last_error()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), expected(wl).view(np.uint32))
 
 
 def test_resident_loader_reference_contract():

@@ -401,6 +401,8 @@ int to_int_boxes(const tlb_image_ref* imgs, const tlb_crop_params* crops, int n,
 
 // Packs the crop rectangle of every host image (rows of cw*3 bytes, 16-byte aligned starts)
 // plus the per-sample tables into one pinned buffer and uploads and launches it chunk by chunk.
+bool allocation_range(const void* p, unsigned long long* base_out, size_t* size_out);
+
 int host_images_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crops, int n, int dst_h, int dst_w,
                           const float mean[3], const float std_[3], int normalize_01, void* out_dev, int out_dtype,
                           int out_layout, uint32_t* status_dev, cudaStream_t stream) {
@@ -422,21 +424,40 @@ int host_images_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crop
         size_t gpix = 0;
         unsigned max_rows = 1;
         int gmax_cw = 1;
+        // An image that lies inside the mapped allocation found for the one before it needs no
+        // query of its own: a decoded batch usually sits in one or a few page-locked buffers, and
+        // one driver query per image was a twentieth of the whole call.
+        unsigned long long known_lo = 0, known_hi = 0, known_delta = 0;  // host range; device - host address
         for (int i = 0; i < n && mapped; ++i) {
-            cudaPointerAttributes attr{};
-            if (cudaPointerGetAttributes(&attr, imgs[i].data) != cudaSuccess) {
-                cudaGetLastError();
-                mapped = false;
-                break;
-            }
-            if ((attr.type != cudaMemoryTypeHost && attr.type != cudaMemoryTypeManaged) || !attr.devicePointer) {
-                mapped = false;
-                break;
+            const unsigned long long hp = reinterpret_cast<unsigned long long>(imgs[i].data);
+            const unsigned long long img_bytes = static_cast<unsigned long long>(imgs[i].w) * imgs[i].h * 3ull;
+            unsigned long long dp;
+            if (hp >= known_lo && hp + img_bytes <= known_hi) {
+                dp = hp + known_delta;
+            } else {
+                cudaPointerAttributes attr{};
+                if (cudaPointerGetAttributes(&attr, imgs[i].data) != cudaSuccess) {
+                    cudaGetLastError();
+                    mapped = false;
+                    break;
+                }
+                if ((attr.type != cudaMemoryTypeHost && attr.type != cudaMemoryTypeManaged) || !attr.devicePointer) {
+                    mapped = false;
+                    break;
+                }
+                dp = reinterpret_cast<unsigned long long>(attr.devicePointer);
+                unsigned long long base = 0;
+                size_t size = 0;
+                known_lo = known_hi = 0;
+                if (attr.type == cudaMemoryTypeHost && allocation_range(attr.devicePointer, &base, &size)) {
+                    known_delta = dp - hp;
+                    known_lo = base - known_delta;
+                    known_hi = known_lo + size;
+                }
             }
             const IntBox& b = boxes[i];
             const unsigned wpad = (static_cast<unsigned>(b.w) + 15u) & ~15u;  // packed row = whole pixels, 16-byte multiple
-            items[i].src = reinterpret_cast<unsigned long long>(attr.devicePointer) +
-                           (static_cast<unsigned long long>(b.y) * imgs[i].w + b.x) * 3ull;
+            items[i].src = dp + (static_cast<unsigned long long>(b.y) * imgs[i].w + b.x) * 3ull;
             items[i].dst_off = gpix;
             items[i].src_pitch = static_cast<unsigned>(imgs[i].w) * 3u;
             items[i].row_bytes = static_cast<unsigned>(b.w) * 3u;
@@ -446,7 +467,80 @@ int host_images_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crop
             max_rows = std::max(max_rows, static_cast<unsigned>(b.h));
             gmax_cw = std::max(gmax_cw, b.w);
         }
+        if (mapped && env_int("TLB_HOST_DIRECT", 1) != 0) {
+            // Default: no staging at all.  The fused kernel's planner warps pull exactly the crop rows
+            // they need out of the mapped host images with the same bulk copies they use on device
+            // memory, so the transform runs at the rate the rows cross PCIe and the packed copy of the
+            // crops in device memory (written, then read once) never exists.  The images are separate
+            // host allocations: one base (the lowest address) plus offsets, and the kernel is told that
+            // no load may leave an image.  Only the four small tables are uploaded.
+            unsigned long long lo = ~0ull, hi = 0;
+            int max_w = 1, max_h = 1;
+            for (int i = 0; i < n; ++i) {
+                const unsigned long long a = items[i].src - (static_cast<unsigned long long>(boxes[i].y) * imgs[i].w + boxes[i].x) * 3ull;
+                lo = std::min(lo, a);
+                hi = std::max(hi, a + static_cast<unsigned long long>(imgs[i].w) * imgs[i].h * 3ull);
+                max_w = std::max(max_w, imgs[i].w);
+                max_h = std::max(max_h, imgs[i].h);
+            }
+            const size_t box_tab = 0;
+            const size_t off_tab = box_tab + 16 * size_t(n);
+            const size_t size_tab = off_tab + 8 * size_t(n);
+            const size_t flip_tab = size_tab + 8 * size_t(n);
+            const size_t tab_bytes = flip_tab + size_t(n);
+            std::unique_lock<std::mutex> lk(st.mu);
+            Buffer& buf = st.params[st.params_next];
+            st.params_next = (st.params_next + 1) % 4;
+            if (int rc = grow(buf, tab_bytes)) return rc;
+            lk.unlock();
+            auto* hb = static_cast<unsigned char*>(buf.host);
+            auto* db = static_cast<unsigned char*>(buf.dev);
+            auto* h_box = reinterpret_cast<int*>(hb + box_tab);
+            auto* h_off = reinterpret_cast<long long*>(hb + off_tab);
+            auto* h_size = reinterpret_cast<int*>(hb + size_tab);
+            for (int i = 0; i < n; ++i) {
+                h_box[4 * i] = boxes[i].x;
+                h_box[4 * i + 1] = boxes[i].y;
+                h_box[4 * i + 2] = boxes[i].w;
+                h_box[4 * i + 3] = boxes[i].h;
+                const unsigned long long a = items[i].src - (static_cast<unsigned long long>(boxes[i].y) * imgs[i].w + boxes[i].x) * 3ull;
+                h_off[i] = static_cast<long long>(a - lo);
+                h_size[2 * i] = imgs[i].w;
+                h_size[2 * i + 1] = imgs[i].h;
+                hb[flip_tab + i] = static_cast<unsigned char>(boxes[i].flip);
+            }
+            TLB_CUDA(cudaMemcpyAsync(db, hb, tab_bytes, cudaMemcpyHostToDevice, stream));
+            tlb_transform_desc d{};
+            d.src = reinterpret_cast<const uint8_t*>(lo);
+            d.src_bytes = hi - lo;
+            d.n_src = n;
+            d.src_offsets = reinterpret_cast<const int64_t*>(db + off_tab);
+            d.src_sizes = reinterpret_cast<const int32_t*>(db + size_tab);
+            d.src_w = max_w;
+            d.src_h = max_h;
+            d.n = n;
+            d.boxes = reinterpret_cast<const int32_t*>(db + box_tab);
+            d.flips = db + flip_tab;
+            d.dst_h = dst_h;
+            d.dst_w = dst_w;
+            d.out = out_dev;
+            d.out_dtype = out_dtype;
+            d.out_layout = out_layout;
+            for (int ch = 0; ch < 3; ++ch) {
+                d.mean[ch] = mean[ch];
+                d.std[ch] = std_[ch];
+            }
+            d.normalize_01 = normalize_01;
+            d.max_crop_w = gmax_cw;
+            d.status = status_dev;
+            int rc = check_common(&d);
+            if (rc == TLB_OK) rc = launch_desc(d, gmax_cw, stream, false, /*per_image_region=*/true);
+            TLB_CUDA(cudaEventRecord(buf.done, stream));
+            buf.pending = true;
+            return rc;
+        }
         if (mapped) {
+            // TLB_HOST_DIRECT=0: a gather kernel packs the crop rows into device memory first.
             // Buffer layout: host half holds [boxes | offsets | sizes | flips | gather items]; the device
             // half holds the same tables followed by the gathered pixels.
             const size_t box_tab = 0;
@@ -642,8 +736,8 @@ int sync_host_form(const tlb_image_ref* imgs, const tlb_crop_params* crops, int 
 // Bytes that are readable from `p` to the end of the device allocation that contains it (the
 // driver's cuMemGetAddressRange, reached through the runtime's entry-point lookup so that the
 // library needs no link-time dependency on the driver).  Returns false when the driver cannot
-// tell (not a device allocation of the current context).
-bool readable_extent(const void* p, size_t* bytes) {
+// tell (not an allocation of the current context).
+bool allocation_range(const void* p, unsigned long long* base_out, size_t* size_out) {
     using Fn = int (*)(unsigned long long*, size_t*, unsigned long long);
     static Fn fn = [] {
         void* sym = nullptr;
@@ -660,7 +754,16 @@ bool readable_extent(const void* p, size_t* bytes) {
     size_t size = 0;
     const unsigned long long a = reinterpret_cast<unsigned long long>(p);
     if (fn(&base, &size, a) != 0 || a < base || a >= base + size) return false;
-    *bytes = static_cast<size_t>(base + size - a);
+    *base_out = base;
+    *size_out = size;
+    return true;
+}
+
+bool readable_extent(const void* p, size_t* bytes) {
+    unsigned long long base = 0;
+    size_t size = 0;
+    if (!allocation_range(p, &base, &size)) return false;
+    *bytes = static_cast<size_t>(base + size - reinterpret_cast<unsigned long long>(p));
     return true;
 }
 
