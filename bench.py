@@ -952,8 +952,8 @@ def main():
                               "frac_of_peak": (rd + wr) / (s_ser / args.steps) / 1e9 / peak, "per": "rank"}
     if not args.no_extras and args.workload in ("variable_rrc", "fixed_resize", "highres_nhwc"):
         host_sets = [b.wl for b in batches]
-        path = ("tlb_crop_resize_normalize_to_device: pinned host pixels -> GPU-side gather of the crop rows over "
-                "PCIe -> fused kernel; status word read back")
+        path = ("tlb_crop_resize_normalize_to_device: pinned host pixels -> the fused kernel pulls the crop rows "
+                "over PCIe itself (no staging copy); status word read back")
         if world == 1:
             es, h2d, d2h = e2e_steps(host_sets, lib, stream, e_steps, 3, torch, device)
             line["e2e"] = {"value": e_steps * wl.n / es, "unit": UNIT, "h2d_bytes_per_step": h2d,

@@ -177,11 +177,13 @@ TLB_API int tlb_crop_resize_normalize_batch(const tlb_image_ref* imgs, const tlb
                                             int32_t n, int32_t dst_h, int32_t dst_w,
                                             const float mean[3], const float std_[3], float* out_host);
 
-/* Host images in, DEVICE batch out: packs the crop rows of every image into a pinned
- * staging ring, uploads them on `stream`, runs the fused kernel into `out_dev`
- * (dtype/layout as given) and returns without synchronising.  The streaming
- * counterpart of CudaStreamCore's H2D + kernel slot (cuda_transforms.cu:629-780)
- * for the crop/resize path. */
+/* Host images in, DEVICE batch out, on `stream`, without synchronising.  When every image
+ * lies in page-locked, device-mapped host memory the fused kernel reads the crop rows
+ * straight out of the host images across PCIe (nothing is staged; the images must stay
+ * valid and unchanged until the work on `stream` has finished).  Otherwise the crop rows
+ * are packed into a pinned staging ring and uploaded first.  `out_dev` takes the batch
+ * in the given dtype/layout.  The streaming counterpart of CudaStreamCore's H2D + kernel
+ * slot (cuda_transforms.cu:629-780) for the crop/resize path. */
 TLB_API int tlb_crop_resize_normalize_to_device(const tlb_image_ref* imgs, const tlb_crop_params* crops,
                                                 int32_t n, int32_t dst_h, int32_t dst_w,
                                                 const float mean[3], const float std_[3],
