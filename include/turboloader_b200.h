@@ -106,8 +106,8 @@ typedef struct tlb_transform_desc {
                                /*   and the normalize, in the shader's order (:111-115):     */
                                /*   rgb*=b; rgb=(rgb-0.5)*c+0.5; lum=(0.299r+0.587g)+0.114b; */
                                /*   rgb=lum+(rgb-lum)*s; clamp to [0,1].  Every operation is */
-                               /*   rounded separately.  Needs normalize_01 = 1; bilinear    */
-                               /*   filter only.                                             */
+                               /*   rounded separately.  Needs normalize_01 = 1; works with  */
+                               /*   either filter.                                           */
 
     /* -- launch flags (tlb_fused_transform only; the other entry points ignore them) ---- */
     uint32_t flags;            /* OR of TLB_FLAG_*                                           */

@@ -326,6 +326,20 @@ TLO_API int tlo_fused_batch_jitter(const uint8_t* src, const int64_t* offsets, c
     return 0;
 }
 
+/* ... and with the antialiased resize in front of the jitter (the reference has both options on
+ * its training path: direct_batch_loader.hpp:229-231 picks the filter, the shader jitters the
+ * resized 8-bit image). */
+TLO_API int tlo_fused_batch_aa_jitter(const uint8_t* src, const int64_t* offsets, const int32_t* sizes,
+                                      int64_t n_src, const int64_t* sel, const int32_t* boxes,
+                                      const uint8_t* flips, int n, int dh, int dw, const float* mean,
+                                      const float* std_, const float* jitter, float* out) {
+    g_antialias = 1;
+    const int rc = tlo_fused_batch_jitter(src, offsets, sizes, n_src, sel, boxes, flips, n, dh, dw, mean, std_,
+                                          jitter, out);
+    g_antialias = 0;
+    return rc;
+}
+
 /* NCHW f32 -> NHWC f32 (same values, permuted). */
 TLO_API void tlo_nchw_to_nhwc(const float* in, float* out, int n, int h, int w) {
     size_t hw = (size_t)h * w;

@@ -84,6 +84,8 @@ def _load(impl: str) -> C.CDLL:
         lib.tlo_fused_batch_jitter.restype = C.c_int
         lib.tlo_fused_batch_jitter.argtypes = [_u8p, _i64p, _i32p, C.c_int64, _i64p, _i32p, _u8p, C.c_int,
                                                C.c_int, C.c_int, _f32p, _f32p, _f32p, _f32p]
+        lib.tlo_fused_batch_aa_jitter.restype = C.c_int
+        lib.tlo_fused_batch_aa_jitter.argtypes = lib.tlo_fused_batch_jitter.argtypes
         lib.tlo_resize_bilinear_u8.restype = None
         lib.tlo_resize_bilinear_u8.argtypes = [_u8p, _u8p, C.c_int, C.c_int, C.c_int, C.c_int]
         lib.tlo_f32_to_bf16_array.restype = None
@@ -146,10 +148,11 @@ def fused_batch(src, offsets, sizes, sel, boxes, flips, dst_h, dst_w, mean, std,
             _ptr(boxes, _i32p), _ptr(flips, _u8p), n, dst_h, dst_w, _ptr(mean, _f32p),
             _ptr(std, _f32p), int(bool(normalize_01)), _ptr(out, _f32p)]
     if jitter is not None:
-        if impl != "port" or antialias or not normalize_01:
-            raise ValueError("jitter: C restatement only, bilinear filter, normalize_01")
+        if impl != "port" or not normalize_01:
+            raise ValueError("jitter: C restatement only, normalize_01")
         jitter = np.ascontiguousarray(jitter, dtype=np.float32).reshape(n, 3)
-        rc = lib.tlo_fused_batch_jitter(*args[:12], _ptr(jitter, _f32p), _ptr(out, _f32p))
+        fn = lib.tlo_fused_batch_aa_jitter if antialias else lib.tlo_fused_batch_jitter
+        rc = fn(*args[:12], _ptr(jitter, _f32p), _ptr(out, _f32p))
     elif antialias:
         rc = (lib.tlo_fused_batch_aa(*args, 1) if impl == "port"
               else lib.tlref_fused_batch_aa(*args, int(threads), 1))

@@ -74,7 +74,6 @@ def test_plan_is_computed_without_a_gpu():
     (dict(dst_h=0), 1), (dict(out_dtype=7), 1), (dict(out_layout=3), 1), (dict(src=None), 1), (dict(n_src=0), 1),
     (dict(std=_capi.f3((1, 0, 1))), 1), (dict(n=9), 3), (dict(uniform_box=(C.c_int32 * 4)(30, 0, 8, 8)), 2),
     (dict(src_w=0, src_h=0), 1), (dict(flags=2), 1), (dict(jitter=0x3000, normalize_01=0), 1),
-    (dict(jitter=0x3000, normalize_01=1, antialias=1), 1),
 ])
 def test_invalid_descriptors_are_rejected_on_the_host(kw, code):
     lib = _capi.load()

@@ -113,3 +113,31 @@ def test_one_column_kernel_still_matches():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
+def test_colour_jitter_after_the_antialiased_resize():
+    """Per-sample (brightness, contrast, saturation) applied to the antialiased 8-bit image before the
+    normalize; oracle: the C restatement of both (the shader lines src/metal/metal_transforms.mm:111-115
+    after resize_triangle_antialias)."""
+    import torch
+    rs = np.random.RandomState(9)
+    for wl in (S.config2(seed=31, n=16, lo=60, hi=260, dst=72), S.config4(seed=32, n=5, src=96, dst=80)):
+        jit = rs.uniform(0.6, 1.4, size=(wl.n, 3)).astype(np.float32)
+        jit[0] = (1.0, 1.0, 1.0)
+        jit[1] = (3.0, 2.0, 0.0)   # saturates, then grey
+        table = torch.from_numpy(jit).cuda()
+
+        def mutate(d):
+            _aa(d)
+            d.jitter = table.data_ptr()
+
+        res = run_gpu(wl, mutate=mutate)
+        assert res["status"] == 0
+        want = O.fused_batch(wl.src, wl.offsets, wl.sizes, wl.sel, wl.boxes, wl.flips, wl.dst_h, wl.dst_w, wl.mean, wl.std,
+                             antialias=True, jitter=jit)
+        if wl.channels_last:
+            want = O.nchw_to_nhwc(want)
+        if wl.dtype == "f32":
+            assert np.array_equal(res["out"].view(np.uint32), want.view(np.uint32))
+        else:
+            assert check_bf16(res["out"], O.bf16_bits(want)) == 0

@@ -235,7 +235,7 @@ def test_identity_jitter_and_brightness():
     assert np.abs(bright - plain).mean() > 0.01
 
 
-def test_jitter_needs_unit_range_and_the_bilinear_filter():
+def test_jitter_needs_unit_range():
     import torch
     wl = S.config1(n=2, seed=1, src=32, dst=16)   # mean/std in 0..255 units
     table = torch.ones((2, 3), device="cuda")

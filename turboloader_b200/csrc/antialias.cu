@@ -334,6 +334,8 @@ struct PairCtx {
     int nt;                        // horizontal taps of this sample
     float one, pre, nkpre;
     float nmean[3], inv_std[3];
+    bool jit;                      // colour jitter (brightness jb, contrast jc, saturation js) before the normalize
+    float jb, jc, js;
     bool validB;
     unsigned char* pA;             // channel 0 of column A at tile row 0
     long long dB;                  // bytes from column A to column B
@@ -532,15 +534,35 @@ __device__ __forceinline__ void pair_rows(const PairCtx& c, const int mode) {
             // (uint8)max(0, min(255, acc + 0.5f))   simd_utils.hpp:2008-2009.  acc >= 0 (weights and pixels
             // are), so only the upper clamp can act; the truncation is RZ(x + 2^23), and code * pre is
             // fma(2^23 + code, pre, -2^23 pre), exactly RN(code * pre).
-            auto finish = [&](float2 v, int ch) {
+            auto code01 = [&](float2 v) {
                 float2 t = aa_fma2(v, one2, half2);
                 t.x = fminf(t.x, 255.0f);
                 t.y = fminf(t.y, 255.0f);
-                const float2 x = aa_fma2(aa_add2_rz(t, k2), pre2, nkpre2);
+                return aa_fma2(aa_add2_rz(t, k2), pre2, nkpre2);
+            };
+            float2 x0 = code01(v0), x1 = code01(v1), x2 = code01(v2);
+            if (c.jit) {
+                // Colour jitter on rgb = code/255 in the order of the reference's train_transform shader
+                // (src/metal/metal_transforms.mm:111-115), every operation rounded separately: brightness,
+                // contrast about 0.5, saturation as lum + (rgb-lum)*s with lum = (0.299 r + 0.587 g) + 0.114 b,
+                // clamp to [0,1].  Same sequence as in the bilinear kernel.
+                auto jitter1 = [&](float& r, float& g, float& b) {
+                    r = __fadd_rn(__fmul_rn(__fsub_rn(__fmul_rn(r, c.jb), 0.5f), c.jc), 0.5f);
+                    g = __fadd_rn(__fmul_rn(__fsub_rn(__fmul_rn(g, c.jb), 0.5f), c.jc), 0.5f);
+                    b = __fadd_rn(__fmul_rn(__fsub_rn(__fmul_rn(b, c.jb), 0.5f), c.jc), 0.5f);
+                    const float lum = __fadd_rn(__fadd_rn(__fmul_rn(r, 0.299f), __fmul_rn(g, 0.587f)), __fmul_rn(b, 0.114f));
+                    r = fminf(fmaxf(__fadd_rn(lum, __fmul_rn(__fsub_rn(r, lum), c.js)), 0.0f), 1.0f);
+                    g = fminf(fmaxf(__fadd_rn(lum, __fmul_rn(__fsub_rn(g, lum), c.js)), 0.0f), 1.0f);
+                    b = fminf(fmaxf(__fadd_rn(lum, __fmul_rn(__fsub_rn(b, lum), c.js)), 0.0f), 1.0f);
+                };
+                jitter1(x0.x, x1.x, x2.x);
+                jitter1(x0.y, x1.y, x2.y);
+            }
+            auto normalize = [&](float2 x, int ch) {
                 return aa_mul2(aa_fma2(x, one2, make_float2(c.nmean[ch], c.nmean[ch])),
                                make_float2(c.inv_std[ch], c.inv_std[ch]));
             };
-            const float2 o0 = finish(v0, 0), o1 = finish(v1, 1), o2 = finish(v2, 2);
+            const float2 o0 = normalize(x0, 0), o1 = normalize(x1, 1), o2 = normalize(x2, 2);
             put_at<DTYPE>(pA, o0.x);
             put_at<DTYPE>(pA + c.chan_step, o1.x);
             put_at<DTYPE>(pA + 2 * c.chan_step, o2.x);
@@ -756,6 +778,13 @@ __global__ void __launch_bounds__(128) antialias_pair_kernel(const __grid_consta
     for (int q = 0; q < 3; ++q) {
         c.nmean[q] = -p.mean[q];
         c.inv_std[q] = p.inv_std[q];
+    }
+    c.jit = p.jitter != nullptr;
+    c.jb = c.jc = c.js = 1.0f;
+    if (c.jit) {
+        c.jb = p.jitter[3 * static_cast<long long>(k)];
+        c.jc = p.jitter[3 * static_cast<long long>(k) + 1];
+        c.js = p.jitter[3 * static_cast<long long>(k) + 2];
     }
     c.validB = validB;
     // where the two columns land after the flip

@@ -191,7 +191,6 @@ int check_common(const tlb_transform_desc* d) {
     if (d->labels_out && !d->labels_in) return fail(TLB_ERR_INVALID_ARG, "labels_out given without labels_in");
     if (d->jitter && !d->normalize_01)
         return fail(TLB_ERR_INVALID_ARG, "colour jitter works on rgb in [0,1]: it needs normalize_01 = 1 (mean/std in [0,1] units)");
-    if (d->jitter && d->antialias) return fail(TLB_ERR_INVALID_ARG, "colour jitter is not available with the antialiased filter");
     if (d->flags & ~static_cast<uint32_t>(TLB_FLAG_LAUNCH_OVERLAP)) return fail(TLB_ERR_INVALID_ARG, "unknown bits in flags: 0x%x", d->flags);
     if (!d->boxes && d->uniform_box[2] != 0) {
         const int* b = d->uniform_box;
@@ -261,6 +260,7 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
         // take 3x the column weights of the one-column kernel, so very wide filters get narrower tiles.
         static const bool one_col = std::getenv("TLB_AA_ONE_COLUMN") != nullptr;
         a.pair = one_col ? 0 : 1;
+        if (!a.pair && d.jitter) return fail(TLB_ERR_INVALID_ARG, "colour jitter needs the packed antialias kernel (TLB_AA_ONE_COLUMN is set)");
         static const int aa_rows = env_int("TLB_AA_TILE_ROWS", 32);
         a.tile_rows = std::min(std::max(aa_rows, 1), d.dst_h);
         a.n_row_tiles = (d.dst_h + a.tile_rows - 1) / a.tile_rows;
