@@ -166,6 +166,8 @@ class CudaResidentLoader:
         self._ahead = max(1, (self._ring_slots - 1) // 2)
         self._ring = None
         self._lookahead = None
+        self._stage = {}        # (table name, parity) -> page-locked staging tensor
+        self._stage_parity = 0
         self._jitter_fn = jitter  # callable(epoch, order) -> float32[len(order), 3] (brightness, contrast, saturation), or None
         self._epoch = 0
         self._resume_batches = 0
@@ -256,8 +258,24 @@ class CudaResidentLoader:
         lib = _capi.load()
         with torch.cuda.device(self._device):
             # ---- whole-epoch tables on the device, once -----------------------------------------
-            d_order = torch.from_numpy(order).to(self._device) if self.shuffle else None
-            d_flips = torch.from_numpy(flips).to(self._device) if (self.hflip_prob > 0.0 or self._flips_fn is not None) else None
+            # Host table -> device through page-locked staging that the loader keeps (two sets, used by
+            # alternate epochs): a copy into it and an asynchronous upload, ordered before the first
+            # launch (which waits for the consumer stream's position), instead of a blocking copy from
+            # pageable memory per table.
+            self._stage_parity ^= 1
+
+            def upload(name, host):
+                host = np.ascontiguousarray(host)
+                slot = (name, self._stage_parity)
+                buf = self._stage.get(slot)
+                if buf is None or buf.shape != host.shape or buf.dtype != torch.from_numpy(host).dtype:
+                    buf = torch.empty(host.shape, dtype=torch.from_numpy(host).dtype, pin_memory=True)
+                    self._stage[slot] = buf
+                buf.numpy()[...] = host
+                return buf.to(self._device, non_blocking=True)
+
+            d_order = upload("order", order) if self.shuffle else None
+            d_flips = upload("flips", flips) if (self.hflip_prob > 0.0 or self._flips_fn is not None) else None
             d_boxes = None
             if self._boxes_fn is not None or aug_boxes is not None:
                 b = aug_boxes if aug_boxes is not None else \
@@ -267,7 +285,7 @@ class CudaResidentLoader:
                 if (b[:, 2] <= 0).any() or (b[:, 3] <= 0).any() or (b[:, 0] < 0).any() or (b[:, 1] < 0).any() or \
                         (b[:, 0] + b[:, 2] > self._W).any() or (b[:, 1] + b[:, 3] > self._H).any():
                     raise ValueError("a crop box leaves the stored image")
-                d_boxes = torch.from_numpy(b).to(self._device)
+                d_boxes = upload("boxes", b)
                 max_cw = int(b[:, 2].max())
             else:
                 max_cw = self._box[2]
@@ -276,7 +294,7 @@ class CudaResidentLoader:
                 j = np.ascontiguousarray(self._jitter_fn(self._epoch, order), dtype=np.float32).reshape(-1, 3)
                 if j.shape[0] != self._n:
                     raise ValueError("jitter callable must return one (brightness, contrast, saturation) per epoch position")
-                d_jit = torch.from_numpy(j).to(self._device)
+                d_jit = upload("jitter", j)
             # ---- output ring: slot s of every buffer belongs to batch b with b % ring == s --------
             R = self._ring_slots
             shape = (bs, self._oh, self._ow, 3) if self.channels_last else (bs, 3, self._oh, self._ow)
