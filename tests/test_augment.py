@@ -43,3 +43,18 @@ def test_fallback_is_the_clamped_central_crop():
     assert 0.2 < flips.mean() < 0.3
     with pytest.raises(ValueError):
         t.pick_crops(1, 0, [[0, 10]])
+
+
+def test_a_whole_epoch_drawn_on_all_cores_equals_the_serial_draw():
+    """Large tables are drawn on several host threads (each sample has its own generator); the result
+    must not depend on how the samples were split."""
+    import numpy as np
+    from turboloader_b200.augment import pick_crops
+    rs = np.random.RandomState(3)
+    n = 40_000
+    sizes = rs.randint(20, 600, size=(n, 2)).astype(np.int32)
+    order = rs.permutation(n).astype(np.int64)
+    boxes, flips = pick_crops(7, 2, sizes, indices=order, hflip_prob=0.5)
+    for i0 in range(0, n, 3000):  # below the threshold at which threads are used
+        b, f = pick_crops(7, 2, sizes[i0:i0 + 3000], indices=order[i0:i0 + 3000], hflip_prob=0.5)
+        assert np.array_equal(b, boxes[i0:i0 + 3000]) and np.array_equal(f, flips[i0:i0 + 3000])

@@ -12,6 +12,7 @@
 #include <cstdint>
 #include <numeric>
 #include <random>
+#include <thread>
 #include <vector>
 
 #include "../../include/turboloader_b200.h"
@@ -115,7 +116,11 @@ int64_t tlb_pick_crops(int32_t seed, int32_t epoch, const int64_t* indices, cons
                        float hflip_prob, int32_t* boxes_out, uint8_t* flips_out) {
     if (n < 0 || !sizes_wh || !boxes_out) return -1;
     const float lo = std::log(3.0f / 4.0f), hi = std::log(4.0f / 3.0f);
-    for (int64_t i = 0; i < n; ++i) {
+    // Every sample has its own generator, so the samples of a whole epoch are drawn on all host cores:
+    // seeding a 64-bit Mersenne twister and regenerating its state costs ~1 us per sample, which for an
+    // epoch of a million images would otherwise hold the loader back for a second.
+    auto draw = [&](int64_t i0, int64_t i1) -> int64_t {
+    for (int64_t i = i0; i < i1; ++i) {
         const int w = sizes_wh[2 * i], h = sizes_wh[2 * i + 1];
         if (w <= 0 || h <= 0) return -(i + 2);
         const uint64_t idx = static_cast<uint64_t>(indices ? indices[i] : i);
@@ -156,6 +161,24 @@ int64_t tlb_pick_crops(int32_t seed, int32_t epoch, const int64_t* indices, cons
         boxes_out[4 * i + 3] = bh;
         if (flips_out) flips_out[i] = flip ? 1 : 0;
     }
+    return 0;
+    };
+    constexpr int64_t kPerThread = 4096;
+    unsigned threads = std::thread::hardware_concurrency();
+    threads = static_cast<unsigned>(std::min<int64_t>(std::min<unsigned>(threads ? threads : 1u, 32u), (n + kPerThread - 1) / kPerThread));
+    if (threads <= 1) {
+        const int64_t rc = draw(0, n);
+        return rc < 0 ? rc : n;
+    }
+    std::vector<int64_t> rcs(threads, 0);
+    std::vector<std::thread> pool;
+    const int64_t chunk = (n + threads - 1) / threads;
+    for (unsigned t = 1; t < threads; ++t)
+        pool.emplace_back([&, t] { rcs[t] = draw(std::min<int64_t>(n, t * chunk), std::min<int64_t>(n, (t + 1) * chunk)); });
+    rcs[0] = draw(0, std::min<int64_t>(n, chunk));
+    for (auto& th : pool) th.join();
+    for (int64_t rc : rcs)
+        if (rc < 0) return rc;  // chunks are in index order: the first failing chunk holds the first bad sample
     return n;
 }
 
