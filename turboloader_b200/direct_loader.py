@@ -82,6 +82,7 @@ class DirectBatchLoader:
         self._ring_slots = max(3, int(ring))
         self._ahead = max(1, (self._ring_slots - 1) // 2)
         self._ring = None
+        self._lookahead = None
         self._epoch = 0
         self._resume_batches = 0
         self._served = 0
@@ -126,13 +127,49 @@ class DirectBatchLoader:
         order = self.epoch_order(e)
         return pick_crops(self.seed, e, self._sizes[order], indices=order, hflip_prob=self.hflip_prob)
 
+    def _host_tables(self, epoch):
+        """(order, boxes or None, flips or None) of an epoch: everything drawn on the host from
+        (seed, epoch, rank) alone."""
+        order = self.epoch_order(epoch)
+        if not self.train_aug:
+            return order, None, None
+        boxes, flips = pick_crops(self.seed, epoch, self._sizes[order], indices=order, hflip_prob=self.hflip_prob)
+        return order, boxes, flips
+
+    def _epoch_tables(self, epoch):
+        """This epoch's host tables, from the look-ahead if it drew them already; the NEXT epoch's are
+        then drawn on a helper thread while this one is served (the shuffle of a large epoch and its
+        crop rects take longer on the host than the epoch takes on the GPU)."""
+        import threading
+
+        key = lambda e: (e, self.seed, self.shuffle, self.train_aug, self.hflip_prob, self.distributed,
+                         self.world_rank, self.world_size)
+        pending, self._lookahead = self._lookahead, None
+        tables = None
+        if pending is not None:
+            thread, box = pending
+            thread.join()
+            if box.get("key") == key(epoch):
+                tables = box["tables"]
+        if tables is None:
+            tables = self._host_tables(epoch)
+        box = {}
+
+        def work(e=epoch + 1, k=key(epoch + 1)):
+            box["tables"] = self._host_tables(e)
+            box["key"] = k
+
+        thread = threading.Thread(target=work, daemon=True)
+        thread.start()
+        self._lookahead = (thread, box)
+        return tables
+
     # ---- iteration -----------------------------------------------------------------------------------
     def __iter__(self):
         torch = self._torch
         lib = _capi.load()
         bs = self.batch_size
-        order = self.epoch_order()
-        boxes, flips = self.epoch_crops()
+        order, boxes, flips = self._epoch_tables(self._epoch)
         total = int(order.size)
         start = self._resume_batches
         self._resume_batches = 0
