@@ -10,12 +10,17 @@
 //     separately rounded products, first tap first;
 //   * code = (uint8)clamp(acc + 0.5f), then the same flip / normalize as the bilinear kernel.
 //
-// Work split: a CTA owns a tile of output rows x output columns of one sample; a thread owns one
-// column of the RESIZED image for both passes, so the two passes need no synchronisation: the
-// horizontal results of the source rows an output row taps sit in a shared-memory ring indexed by
-// source row, written and read by the same thread.  Every source row of the tile's footprint is
-// filtered horizontally once.  Column weights live in shared memory ([tap][column], conflict-free),
-// row weights in a small per-tile table.
+// Two kernels compute it.  antialias_pair_kernel (the default) gives a thread TWO columns of the
+// resized image in packed fp32, walks down the source rows a tile taps, drops the taps whose weight
+// is exactly zero (bit-neutral), fetches tap windows as aligned words and asks for the next row and
+// for the tile's whole footprint ahead of use; it is described where it is defined.
+// antialias_kernel is the first, one-column form, kept as a cross-check (TLB_AA_ONE_COLUMN):
+// a CTA owns a tile of output rows x output columns of one sample; a thread owns one column of the
+// RESIZED image for both passes, so the two passes need no synchronisation: the horizontal results
+// of the source rows an output row taps sit in a shared-memory ring indexed by source row, written
+// and read by the same thread.  Every source row of the tile's footprint is filtered horizontally
+// once.  Column weights live in shared memory ([tap][column], conflict-free), row weights in a small
+// per-tile table.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
