@@ -262,12 +262,14 @@ __global__ void __launch_bounds__(256) antialias_kernel(const __grid_constant__ 
 // Same filter, same order of operations, organised like the bilinear kernel: a thread owns output
 // columns t and t + TC/2 of the tile and carries them as the two halves of packed fp32 values, so
 // every multiply and add of the filter is issued once per column PAIR.  Per horizontal tap and
-// pair: six byte loads, six ORs (2^23 + byte), three packed FMAs for the products
+// pair: six bytes picked out of realigned 32-bit words by PRMT straight into 2^23 + byte (byte loads
+// for filters wider than the unrolled ones), three packed FMAs for the products
 // fma(2^23 + b, w, -2^23 w) == RN(b w) and three for the running sums (fma(prod, 1, acc), the exact
 // packed add); the weights of the pair sit in shared memory as {wA, wB, -2^23 wA, -2^23 wB}.
-// The tap loop has the SAMPLE's tap bound as its trip count for every column; a column with fewer
-// taps gets zero weights in front or behind (adding +0 changes no bit), and its tap window is shifted
-// left where it would leave the crop, so no load ever leaves the crop row.
+// The tap loop has the TILE's tap count (the most any of its columns kept after the zero-weight
+// taps were dropped) as its trip count for every column; a column with fewer taps gets zero weights
+// in front or behind (adding +0 changes no bit), and its tap window is shifted left where it would
+// leave the crop, so no load ever leaves the crop row.
 __device__ __forceinline__ float2 aa_fma2(float2 a, float2 b, float2 c) {
     float2 d;
     asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
