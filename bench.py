@@ -726,6 +726,48 @@ def loader_epoch_leg(args, torch, device, peak, n_images):
             "epochs_timed": len(times), "timing": "max(CUDA events on the consumer stream, host wall clock) per epoch, median"}
 
 
+def direct_loader_leg(args, torch, device, peak, n_images=32768):
+    """The product API of the variable-size route (what DataLoader(image_size=224, train_aug=True)
+    runs): DirectBatchLoader over a device-resident store of 256x256 images, epoch order from
+    tlb_direct_order, RandomResizedCrop rects and flips from tlb_pick_crops, -> 224x224 bf16 NCHW,
+    batches of 1024; CUDA events around the epoch on the consumer's stream."""
+    import turboloader_b200 as t
+
+    g = torch.Generator(device=device)
+    g.manual_seed(args.seed + 5)
+    store = torch.randint(0, 256, (n_images * 256 * 256 * 3,), dtype=torch.uint8, device=device, generator=g)
+    offsets = np.arange(n_images, dtype=np.int64) * (256 * 256 * 3)
+    sizes = np.tile(np.array([[256, 256]], np.int32), (n_images, 1))
+    ld = t.DirectBatchLoader((store, offsets, sizes), 1024, 224, 224, mean=(0.485, 0.456, 0.406), std=(0.229, 0.224, 0.225),
+                             shuffle=True, seed=args.seed, train_aug=True, dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream()
+    times, read = [], 0
+    for ep in range(5):
+        ld.set_epoch(ep)
+        boxes, _ = ld.epoch_crops(ep)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record(stream)
+        nb = 0
+        for x, meta in ld:
+            nb += 1
+        stop.record(stream)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        if ep > 0:
+            times.append(max(start.elapsed_time(stop) / 1e3, wall))
+            read = int((boxes[:, 2].astype(np.int64) * boxes[:, 3] * 3).sum())
+    if ld.device_status() != 0:
+        raise SystemExit("bench.py: device status word is non-zero (direct_loader_epoch)")
+    med = statistics.median(times)
+    total = read + n_images * (8 + 16 + 1 + 16 + 3 * 224 * 224 * 2)
+    del store
+    return {"api": "for x, meta in DirectBatchLoader(..., train_aug=True)", "images": n_images, "batches": nb,
+            "img_per_s": n_images / med, "GB_per_s": total / med / 1e9, "frac_of_peak": total / med / 1e9 / peak,
+            "epochs_timed": len(times), "timing": "max(CUDA events on the consumer stream, host wall clock) per epoch, median"}
+
+
 def identity_leg(lib, torch, device, stream, peak, barrier, seed, dtypes=("f32", "bf16")):
     """The identity-size case of the resident loader (gather -> flip -> normalize -> layout/dtype, the
     reference's normalize_gather_kernel operation): 1024 x 160x160 gathered from 20,000 resident
@@ -1042,6 +1084,14 @@ def main():
                 line["loader_epoch"]["vs_raw_launch_loop"] = line["loader_epoch"]["img_per_s"] / others["resident_epoch"]["img_per_s"]
         except Exception as e:
             line["loader_epoch"] = {"error": repr(e)}
+        try:
+            torch.cuda.empty_cache()
+            line["direct_loader_epoch"] = direct_loader_leg(args, torch, device, peak)
+            ss = line.get("sharded_scaling") or {}
+            if ss.get("img_per_s"):
+                line["direct_loader_epoch"]["vs_raw_launch_loop"] = line["direct_loader_epoch"]["img_per_s"] / ss["img_per_s"]
+        except Exception as e:
+            line["direct_loader_epoch"] = {"error": repr(e)}
         # The opt-in antialiased (triangle filter) resize on the default workload: same inputs, the
         # descriptor's antialias flag set.  Quality path: about twice the arithmetic of the bilinear kernel.
         try:

@@ -154,3 +154,26 @@ def test_ranks_partition_the_epoch():
         assert mine == order[r * 11:(r + 1) * 11]  # 45 // 4 = 11 per rank, the tail is dropped
         seen += mine
     assert len(set(seen)) == 44
+
+
+def test_store_already_on_the_device_gives_the_same_batches():
+    """The packed store may be a uint8 tensor that already lives on the GPU (no upload); two epochs
+    with train_aug must equal the ones served from the same store given as a host array."""
+    import torch
+    rs = np.random.RandomState(5)
+    sizes = rs.randint(30, 90, size=(37, 2)).astype(np.int32)
+    nbytes = sizes[:, 0].astype(np.int64) * sizes[:, 1] * 3
+    offsets = np.concatenate([[0], np.cumsum(nbytes)[:-1]]).astype(np.int64)
+    packed = rs.randint(0, 256, size=int(nbytes.sum()), dtype=np.uint8)
+    kw = dict(mean=(0.485, 0.456, 0.406), std=(0.229, 0.224, 0.225), shuffle=True, seed=11, train_aug=True)
+    host = t.DirectBatchLoader((packed, offsets, sizes), 8, 32, 40, **kw)
+    dev = t.DirectBatchLoader((torch.from_numpy(packed).cuda(), offsets, sizes), 8, 32, 40, **kw)
+    for ep in range(2):
+        host.set_epoch(ep)
+        dev.set_epoch(ep)
+        a = [(x.clone(), m["indices"]) for x, m in host]
+        b = [(x.clone(), m["indices"]) for x, m in dev]
+        assert len(a) == len(b) == 5
+        for (xa, ia), (xb, ib) in zip(a, b):
+            assert np.array_equal(ia, ib) and torch.equal(xa, xb)
+    assert host.device_status() == 0 and dev.device_status() == 0

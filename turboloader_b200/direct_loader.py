@@ -33,7 +33,8 @@ class DirectBatchLoader:
                  distributed=False, world_rank=0, world_size=1, drop_last=False, antialias=False, train_aug=False,
                  hflip_prob=0.5, dtype=None, channels_last=False, jitter=None, ring=8, device=None):
         """``images``: a sequence of HWC uint8 RGB arrays (any sizes), or a tuple
-        ``(packed uint8 buffer, int64 offsets, int32 sizes[n,2] as (w,h))``.  ``mean``/``std`` in
+        ``(packed uint8 buffer, int64 offsets, int32 sizes[n,2] as (w,h))`` whose buffer is a host
+        array or a uint8 tensor already on the device.  ``mean``/``std`` in
         [0,1] units (None: plain [0,1] floats, as the reference without a Normalize).  ``jitter``:
         optional callable ``(epoch, order) -> float32[len(order), 3]`` of per-sample (brightness,
         contrast, saturation) factors."""
@@ -43,9 +44,16 @@ class DirectBatchLoader:
             raise RuntimeError("DirectBatchLoader needs an sm_100 CUDA device and the built C-ABI library.")
         self._torch = torch
         self._device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        resident = None  # a store that is already a device tensor is used where it lies
         if isinstance(images, tuple) and len(images) == 3 and np.ndim(images[1]) == 1:
             packed, offsets, sizes = images
-            packed = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1)
+            if torch.is_tensor(packed) and packed.is_cuda:
+                if packed.dtype != torch.uint8:
+                    raise ValueError("a device-resident store must be a uint8 tensor")
+                resident = packed.contiguous().view(-1)
+                self._device = resident.device
+            else:
+                packed = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1)
             offsets = np.ascontiguousarray(offsets, dtype=np.int64)
             sizes = np.ascontiguousarray(sizes, dtype=np.int32).reshape(-1, 2)
         else:
@@ -63,7 +71,7 @@ class DirectBatchLoader:
             raise ValueError("the store is empty or holds an image without pixels")
         self._n = int(sizes.shape[0])
         self._sizes = sizes
-        self._src = torch.from_numpy(packed).to(self._device)
+        self._src = resident if resident is not None else torch.from_numpy(packed).to(self._device)
         self._offsets = torch.from_numpy(offsets).to(self._device)
         self._d_sizes = torch.from_numpy(sizes).to(self._device)
         self.batch_size = int(batch_size)
