@@ -271,10 +271,14 @@ typedef struct tlb_video_desc {
     void* out;                /* DEVICE, caller-allocated (n,3,dst_h,dst_w) */
     int32_t out_dtype;        /* TLB_F32 / TLB_BF16 */
     uint32_t* status;         /* DEVICE word OR-ed with TLB_DEV_COPY_TIMEOUT if a bounded wait gave up; or NULL */
+    uint32_t flags;           /* OR of TLB_FLAG_*: TLB_FLAG_LAUNCH_OVERLAP as for the image kernels (it takes
+                                 effect for batches of at most 256 frames in at most 32 clips, whose tables
+                                 travel in the kernel's parameter block instead of being uploaded first) */
 } tlb_video_desc;
 
-/* Asynchronous form on the caller's stream: uploads the small address/crop tables through a
- * pinned ring and launches once; no synchronisation. */
+/* Asynchronous form on the caller's stream: one launch, no synchronisation.  The small address /
+ * crop tables ride in the kernel's parameters (up to 256 frames in 32 clips) or are uploaded
+ * through a pinned ring first (larger batches). */
 TLB_API int tlb_video_yuv420(const tlb_video_desc* desc, void* stream);
 /* The reference's two pointer-returning forms, same arguments and lifetime rule: the result is
  * a library-owned float32 (n,3,dst_h,dst_w) device buffer, double-buffered, valid until the next

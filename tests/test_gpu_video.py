@@ -68,14 +68,18 @@ class Frames:
         return (self.y_ptrs, self.cb_ptrs, self.cr_ptrs, self.y_stride, self.c_stride, self.c_px, self.w, self.h)
 
 
-@pytest.fixture(params=["direct", "staged"], autouse=True)
+@pytest.fixture(params=["direct", "direct-uploaded-tables", "staged"], autouse=True)
 def kernel_choice(request, monkeypatch):
-    """Every test runs against both kernels: the direct-load one (default) and the shared-memory
-    staged one (TLB_VIDEO_STAGED=1)."""
+    """Every test runs against the direct-load kernel with its tables in the kernel parameters (the
+    default for small batches), the same kernel with the tables uploaded to device memory (what
+    larger batches get; TLB_VIDEO_INLINE_TABLES=0), and the shared-memory staged kernel
+    (TLB_VIDEO_STAGED=1)."""
+    monkeypatch.delenv("TLB_VIDEO_STAGED", raising=False)
+    monkeypatch.delenv("TLB_VIDEO_INLINE_TABLES", raising=False)
     if request.param == "staged":
         monkeypatch.setenv("TLB_VIDEO_STAGED", "1")
-    else:
-        monkeypatch.delenv("TLB_VIDEO_STAGED", raising=False)
+    elif request.param == "direct-uploaded-tables":
+        monkeypatch.setenv("TLB_VIDEO_INLINE_TABLES", "0")
     return request.param
 
 
@@ -114,6 +118,26 @@ def test_upscale_and_windows_touching_the_frame_edges():
         got = f.run(33, 47, crops=crops, flips=np.array([flip], np.int32)).cpu().numpy()
         for i in range(3):
             assert np.array_equal(_bits(got[i]), _bits(f.oracle(i, 33, 47, crop=tuple(crops[0]), flip=bool(flip))))
+
+
+def test_back_to_back_launches_with_the_overlap_flag():
+    """TLB_FLAG_LAUNCH_OVERLAP: consecutive launches into their own outputs may overlap head to tail;
+    every one of them must still produce the oracle's bits."""
+    import torch
+    f = Frames(6, 72, 100, nv12=True, smooth=False, seed=33)
+    crops = np.array([[4.0, 3.0, 80.0, 60.0], [10.0, 8.0, 50.0, 40.0]], np.float32)
+    flips = np.array([0, 1], np.int32)
+    outs = [torch.full((6, 3, 48, 64), -9.0, device="cuda") for _ in range(4)]
+    for out in outs:
+        t.video_yuv420(f.y_ptrs, f.cb_ptrs, f.cr_ptrs, y_stride=f.y_stride, c_stride=f.c_stride, c_px_stride=f.c_px,
+                       src_w=f.w, src_h=f.h, out=out, mean=MEAN, std=STD, crops=crops, flips=flips, clip_len=3,
+                       launch_overlap=True)
+    torch.cuda.synchronize()
+    want = [f.oracle(i, 48, 64, crop=tuple(crops[i // 3]), flip=bool(flips[i // 3])) for i in range(6)]
+    for out in outs:
+        got = out.cpu().numpy()
+        for i in range(6):
+            assert np.array_equal(_bits(got[i]), _bits(want[i])), f"frame {i}"
 
 
 def test_bf16_output_is_the_rounded_fp32_result():

@@ -79,6 +79,7 @@ class VideoDesc(C.Structure):
         ("out", C.c_void_p),
         ("out_dtype", C.c_int32),
         ("status", C.c_void_p),
+        ("flags", C.c_uint32),
     ]
 
 

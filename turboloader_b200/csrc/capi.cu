@@ -1265,6 +1265,7 @@ int check_video(const tlb_video_desc* d) {
     for (int i = 0; i < d->n; ++i)
         if (!d->y_ptrs[i] || !d->cb_ptrs[i] || !d->cr_ptrs[i])
             return fail(TLB_ERR_INVALID_ARG, "video: frame %d has a NULL plane address", i);
+    if (d->flags & ~static_cast<uint32_t>(TLB_FLAG_LAUNCH_OVERLAP)) return fail(TLB_ERR_INVALID_ARG, "video: unknown bits in flags: 0x%x", d->flags);
     if (d->crops) {
         const int clips = d->clip_len > 0 ? (d->n + d->clip_len - 1) / d->clip_len : 1;
         for (int i = 0; i < 4 * clips; ++i)
@@ -1280,6 +1281,42 @@ int video_enqueue(const tlb_video_desc& d, void* stream) {
     if (int rc = ensure_prepared(st)) return rc;
     const size_t n = static_cast<size_t>(d.n);
     const size_t clips = d.crops ? (d.clip_len > 0 ? (n + d.clip_len - 1) / d.clip_len : 1) : 0;
+    const bool staged = env_int("TLB_VIDEO_STAGED", 0) != 0;
+    if (!staged && n <= static_cast<size_t>(tlb::kVideoInlineFrames) && clips <= static_cast<size_t>(tlb::kVideoInlineClips) &&
+        env_int("TLB_VIDEO_INLINE_TABLES", 1) != 0) {
+        // Small batch: the tables travel in the parameter block; nothing is uploaded, no staging
+        // buffer is touched, and the launch follows the previous one in its stream directly.
+        static thread_local tlb::VideoParams p;  // ~7 KB: kept off the stack
+        p = tlb::VideoParams{};
+        p.inline_tables = 1;
+        for (size_t i = 0; i < n; ++i) {
+            p.in.planes[i] = reinterpret_cast<const unsigned char*>(d.y_ptrs[i]);
+            p.in.planes[n + i] = reinterpret_cast<const unsigned char*>(d.cb_ptrs[i]);
+            p.in.planes[2 * n + i] = reinterpret_cast<const unsigned char*>(d.cr_ptrs[i]);
+        }
+        p.has_crops = clips ? 1 : 0;
+        p.has_flips = (clips && d.flips) ? 1 : 0;
+        for (size_t i = 0; i < clips; ++i) {
+            p.in.crops[i] = make_float4(d.crops[4 * i], d.crops[4 * i + 1], d.crops[4 * i + 2], d.crops[4 * i + 3]);
+            p.in.flips[i] = d.flips ? (d.flips[i] != 0) : 0;
+        }
+        p.n = d.n;
+        p.clip_len = d.clip_len;
+        p.y_stride = d.y_stride; p.c_stride = d.c_stride; p.c_px_stride = d.c_px_stride;
+        p.src_w = d.src_w; p.src_h = d.src_h; p.dst_w = d.dst_w; p.dst_h = d.dst_h;
+        p.bt709 = d.bt709 ? 1 : 0;
+        for (int c = 0; c < 3; ++c) {
+            p.mean[c] = d.mean[c];
+            p.inv_std[c] = 1.0f / d.std[c];  // cuda_transforms.cu:392 computes the reciprocal on the host, in fp32
+        }
+        p.one = 1.0f;
+        p.out = d.out;
+        p.status = d.status;
+        const unsigned lflags = (d.flags & TLB_FLAG_LAUNCH_OVERLAP) ? tlb::kLaunchOverlap : 0u;
+        cudaError_t e = static_cast<cudaError_t>(tlb::launch_video(p, d.out_dtype, stream, lflags));
+        if (e != cudaSuccess) return cuda_fail(e, "yuv420_kernel launch");
+        return TLB_OK;
+    }
     const size_t off_crop = (3 * n * sizeof(void*) + 15) & ~static_cast<size_t>(15);
     const size_t off_flip = off_crop + clips * 16;
     const size_t total = off_flip + clips * 4;
@@ -1319,8 +1356,8 @@ int video_enqueue(const tlb_video_desc& d, void* stream) {
     p.one = 1.0f;
     p.out = d.out;
     p.status = d.status;
-    p.use_staged = env_int("TLB_VIDEO_STAGED", 0);
-    cudaError_t e = static_cast<cudaError_t>(tlb::launch_video(p, d.out_dtype, stream));
+    p.use_staged = staged ? 1 : 0;
+    cudaError_t e = static_cast<cudaError_t>(tlb::launch_video(p, d.out_dtype, stream, 0u));
     TLB_CUDA(cudaEventRecord(buf.done, cs));
     buf.pending = true;
     if (e != cudaSuccess) return cuda_fail(e, "yuv420_kernel launch");

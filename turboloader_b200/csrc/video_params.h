@@ -5,6 +5,18 @@
 
 namespace tlb {
 
+// A batch of at most kVideoInlineFrames frames in at most kVideoInlineClips clips carries its
+// address and crop tables inside the kernel's parameter block: no table upload precedes the
+// launch, so consecutive launches are kernel-after-kernel in their stream (and may overlap head to
+// tail when the caller allows it).  Larger batches upload the tables to device memory as before.
+constexpr int kVideoInlineFrames = 256;
+constexpr int kVideoInlineClips = 32;
+struct VideoTables {
+    const unsigned char* planes[3 * kVideoInlineFrames];  // [0,n) Y, [n,2n) Cb, [2n,3n) Cr
+    float4 crops[kVideoInlineClips];
+    int flips[kVideoInlineClips];
+};
+
 struct VideoParams {
     const unsigned char* const* planes;  // DEVICE array of 3n plane addresses: [0,n) Y, [n,2n) Cb, [2n,3n) Cr
     const float4* crops;                 // DEVICE array, one window (x, y, w, h in source pixels) per clip;
@@ -20,12 +32,16 @@ struct VideoParams {
     unsigned* status;                    // optional device word, OR-ed with 8 if a staging copy never completed
     int stage_rows;                      // set by launch_video: output rows per CTA of the staged kernel
     int use_staged;                      // non-zero: use the shared-memory staged kernel when the frame fits
+    int inline_tables;                   // non-zero: planes / crops / flips are read from `in` (direct kernel only)
+    int has_crops, has_flips;            // with inline tables: which of them are given
+    VideoTables in;
 };
 
 constexpr int kVideoStageMaxBytes = 200 * 1024;  // most dynamic shared memory the staged kernel may ask for
 
 int prepare_video();                                           // once per device: shared-memory opt-in
-int launch_video(VideoParams p, int out_dtype, void* stream);  // returns a cudaError_t value
+// flags: kLaunchOverlap of fused_params.h or 0; returns a cudaError_t value
+int launch_video(const VideoParams& p, int out_dtype, void* stream, unsigned flags);
 unsigned long long video_launch_count();
 
 }  // namespace tlb

@@ -32,6 +32,7 @@
 #include <atomic>
 #include <cstdint>
 
+#include "fused_params.h"
 #include "video_params.h"
 
 namespace tlb {
@@ -212,18 +213,27 @@ __device__ __forceinline__ void prefetch_line(const void* p) { asm volatile("pre
 template <int DTYPE>
 __global__ void __launch_bounds__(256) yuv420_direct_kernel(const __grid_constant__ VideoParams p) {
     __shared__ DirectPair pairs[kDirectRows / 2];
+    // Lets a launch made with programmatic stream serialization start behind this one as soon as
+    // every CTA of this one has been scheduled; a no-op for any other launch.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int t = blockIdx.y;                     // frame
     const int r0 = blockIdx.x * kDirectRows;      // first output row of this CTA
     const int rows = min(kDirectRows, p.dst_h - r0);
     const int W = p.dst_w, H = p.dst_h;
     const int cw = (p.src_w + 1) / 2, ch = (p.src_h + 1) / 2;
-    const bool use_crop = p.crops != nullptr;
+    // Tables in the parameter block (small batches) or in device memory: either way behind pointers
+    // (the parameter is __grid_constant__, so its members have addresses).
+    const bool inl = p.inline_tables != 0;
+    const unsigned char* const* const planes = inl ? p.in.planes : p.planes;
+    const float4* const crops = inl ? (p.has_crops ? p.in.crops : nullptr) : p.crops;
+    const int* const flips = inl ? (p.has_flips ? p.in.flips : nullptr) : p.flips;
+    const bool use_crop = crops != nullptr;
     float4 crop = make_float4(0.f, 0.f, 0.f, 0.f);
     bool flip = false;
     if (use_crop) {
         const int clip = p.clip_len > 0 ? t / p.clip_len : 0;
-        crop = p.crops[clip];
-        flip = p.flips ? p.flips[clip] != 0 : false;
+        crop = crops[clip];
+        flip = flips ? flips[clip] != 0 : false;
     }
     if (threadIdx.x < kDirectRows) {
         // Rows past the end of the frame repeat the last row (their results are never stored).
@@ -246,9 +256,9 @@ __global__ void __launch_bounds__(256) yuv420_direct_kernel(const __grid_constan
         (&pt.w.cdy.x)[h] = cdy;
         (&pt.w.icdy.x)[h] = 1.0f - cdy;
     }
-    const unsigned char* __restrict__ yp = p.planes[t];
-    const unsigned char* __restrict__ cbp = p.planes[p.n + t];
-    const unsigned char* __restrict__ crp = p.planes[2 * p.n + t];
+    const unsigned char* __restrict__ yp = planes[t];
+    const unsigned char* __restrict__ cbp = planes[p.n + t];
+    const unsigned char* __restrict__ crp = planes[2 * p.n + t];
     __syncthreads();
 
     const Consts c = make_consts(p);
@@ -556,13 +566,14 @@ int prepare_video() {
     return e;
 }
 
-int launch_video(VideoParams p, int out_dtype, void* stream) {
+int launch_video(const VideoParams& pin, int out_dtype, void* stream, unsigned flags) {
+    VideoParams p = pin;
     const int threads = std::min(256, ((p.dst_w + 31) / 32) * 32);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Rows per CTA of the staged kernel: as many (even, at most kStageMaxRows) as keep the staging
     // buffer near 40 KB, so that several CTAs share an SM and overlap copy with arithmetic.
     int rows = 0;
-    if (p.use_staged) {
+    if (p.use_staged && !p.inline_tables) {
         for (int r = kStageMaxRows; r >= 2; r -= 2) {
             if (video_stage_bytes(p, r) <= (r == 2 ? kVideoStageMaxBytes : 40 * 1024)) {
                 rows = r;
@@ -579,11 +590,21 @@ int launch_video(VideoParams p, int out_dtype, void* stream) {
         else
             yuv420_staged_kernel<1><<<grid, threads, smem, st>>>(p);
     } else {
-        const dim3 grid(static_cast<unsigned>((p.dst_h + kDirectRows - 1) / kDirectRows), static_cast<unsigned>(p.n));
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>((p.dst_h + kDirectRows - 1) / kDirectRows), static_cast<unsigned>(p.n));
+        cfg.blockDim = dim3(static_cast<unsigned>(threads));
+        cfg.stream = st;
+        // Same contract as the image kernels: with kLaunchOverlap the launch may start while the
+        // kernel before it in the stream drains its last CTAs; it never waits on that kernel.
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = (flags & kLaunchOverlap) ? 1 : 0;
         if (out_dtype == 0)
-            yuv420_direct_kernel<0><<<grid, threads, 0, st>>>(p);
+            cudaLaunchKernelEx(&cfg, yuv420_direct_kernel<0>, p);
         else
-            yuv420_direct_kernel<1><<<grid, threads, 0, st>>>(p);
+            cudaLaunchKernelEx(&cfg, yuv420_direct_kernel<1>, p);
     }
     g_video_launches.fetch_add(1, std::memory_order_relaxed);
     return static_cast<int>(cudaGetLastError());

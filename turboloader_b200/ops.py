@@ -69,9 +69,12 @@ def cuda_video_clip_yuv420(y_ptrs, cb_ptrs, cr_ptrs, y_stride, c_stride, c_px_st
 
 
 def make_video_desc(y_ptrs, cb_ptrs, cr_ptrs, *, y_stride, c_stride, c_px_stride, src_w, src_h, out, crops=None,
-                    flips=None, clip_len=0, bt709=False, mean=IMAGENET_MEAN, std=IMAGENET_STD, status=None):
+                    flips=None, clip_len=0, bt709=False, mean=IMAGENET_MEAN, std=IMAGENET_STD, status=None,
+                    launch_overlap=False):
     """Fill a ``tlb_video_desc``; the returned struct keeps its host arrays alive (``_keep``) and can
-    be enqueued any number of times with ``enqueue_video``."""
+    be enqueued any number of times with ``enqueue_video``.  ``launch_overlap`` sets
+    ``TLB_FLAG_LAUNCH_OVERLAP`` (the caller states that the kernel before this one in the stream
+    neither writes this call's frames nor touches its output)."""
     import numpy as np
     import torch
 
@@ -101,6 +104,7 @@ def make_video_desc(y_ptrs, cb_ptrs, cr_ptrs, *, y_stride, c_stride, c_px_stride
     d.out_dtype = _capi.TLB_F32 if out.dtype == torch.float32 else _capi.TLB_BF16
     if status is not None:
         d.status = _dev_ptr(status, torch.int32, "status")
+    d.flags = _capi.FLAG_LAUNCH_OVERLAP if launch_overlap else 0
     d._keep = keep + [out, status]
     return d
 
