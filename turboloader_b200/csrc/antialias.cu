@@ -510,7 +510,7 @@ __device__ __forceinline__ void pair_rows(const PairCtx& c, const int mode) {
         else if (mode == 1) hrow_words<1>(c, imga, gA, gB, src, bufA, bufB, one2, ring_at);
         else hrow_bytes(c, src, one2, ring_at);
         // ---- finish the output rows whose last tap row this was ----------------------------------
-        while (rec.x == src) {
+        while (rec.x <= src) {  // == for every table the tap rule can produce (last tap rows never decrease)
             const int n = rec.y;
             int lo_slot = slot - (n - 1);
             if (lo_slot < 0) lo_slot += c.slots;
@@ -582,10 +582,10 @@ __device__ __forceinline__ void pair_rows(const PairCtx& c, const int mode) {
             ++r;
             pA += c.row_step;
             wrow += 4 * c.yt;
-            rec = r < c.rows ? aa_lds_i2(c.yrec + 8 * r) : make_int2(-1, 0);
+            rec = r < c.rows ? aa_lds_i2(c.yrec + 8 * r) : make_int2(0x7fffffff, 0);  // no row left: never matches
         }
         if (r >= c.rows) break;
-        ++src;
+        if (++src >= c.end_src) break;  // never walks past the rows the tile taps, whatever the tables say
         slot_off += c.slot_bytes;
         if (++slot == c.slots) slot = 0, slot_off = 0;
     }
