@@ -297,7 +297,7 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
     const int cw = d.uniform_box[2] > 0 ? d.uniform_box[2] : d.src_w;
     const int ch = d.uniform_box[2] > 0 ? d.uniform_box[3] : d.src_h;
     if (uniform && !d.jitter && cw == d.dst_w && ch == d.dst_h && env_int("TLB_IDENTITY_FAST", 1) != 0) {
-        cudaError_t ce = static_cast<cudaError_t>(tlb::launch_normalize_copy(p, d.out_dtype, d.out_layout, stream));
+        cudaError_t ce = static_cast<cudaError_t>(tlb::launch_normalize_copy(p, d.out_dtype, d.out_layout, stream, lflags));
         if (ce != cudaSuccess) return cuda_fail(ce, "normalize_copy_kernel launch");
         return TLB_OK;
     }

@@ -84,7 +84,7 @@ unsigned long long launch_count();
 
 // Implemented in normalize_copy.cu: the identity-size case (crop size == output size, uniform
 // dataset, no per-sample boxes).  Returns a cudaError_t as int.
-int launch_normalize_copy(const FusedParams& p, int out_dtype, int out_layout, void* stream);
+int launch_normalize_copy(const FusedParams& p, int out_dtype, int out_layout, void* stream, unsigned flags);
 unsigned long long normalize_copy_launch_count();
 
 }  // namespace tlb

@@ -59,6 +59,9 @@ __device__ __forceinline__ void put_chunk(void* out, long long idx, const float*
 
 template <int DTYPE, int LAYOUT>
 __global__ void __launch_bounds__(256) normalize_copy_kernel(const __grid_constant__ FusedParams p) {
+    // Lets a launch made with programmatic stream serialization start behind this one as soon as
+    // every CTA of this one has been scheduled; a no-op for any other launch.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int P = DTYPE == 0 ? 4 : 8;  // pixels per thread
     const int k = blockIdx.x;              // sample
     const int W = p.dst_w, H = p.dst_h;
@@ -242,6 +245,9 @@ __device__ __forceinline__ void vec_rows(const FusedParams& p, const unsigned ch
 
 template <int DTYPE, int LAYOUT>
 __global__ void __launch_bounds__(256) normalize_copy_vec_kernel(const __grid_constant__ FusedParams p) {
+    // Lets a launch made with programmatic stream serialization start behind this one as soon as
+    // every CTA of this one has been scheduled; a no-op for any other launch.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int k = blockIdx.x;  // sample
     const long long s = p.sel ? p.sel[k] : static_cast<long long>(k);
     unsigned bad = 0;
@@ -282,7 +288,7 @@ __global__ void __launch_bounds__(256) normalize_copy_vec_kernel(const __grid_co
 std::atomic<unsigned long long> g_copy_launches{0};
 
 template <int DTYPE, int LAYOUT>
-int launch_one(const FusedParams& p, cudaStream_t st) {
+int launch_one(const FusedParams& p, cudaStream_t st, unsigned flags) {
     constexpr int P = DTYPE == 0 ? 4 : 8;
     // Vector form: 8-byte aligned rows of whole 8-pixel groups and 16-byte aligned output chunks.
     const int cx = p.ubox[2] > 0 ? p.ubox[0] : 0;
@@ -295,20 +301,31 @@ int launch_one(const FusedParams& p, cudaStream_t st) {
     const dim3 block(static_cast<unsigned>(bx), static_cast<unsigned>(by));
     const int rows_per_cta = by * kRowsPerThread;
     const dim3 grid(static_cast<unsigned>(p.n), static_cast<unsigned>((p.dst_h + rows_per_cta - 1) / rows_per_cta));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = st;
+    // Same contract as the resampling kernels: with kLaunchOverlap the launch may start while the
+    // kernel before it in the stream drains its last CTAs; it never waits on that kernel.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & kLaunchOverlap) ? 1 : 0;
     if (vec8)
-        normalize_copy_vec_kernel<DTYPE, LAYOUT><<<grid, block, 0, st>>>(p);
+        cudaLaunchKernelEx(&cfg, normalize_copy_vec_kernel<DTYPE, LAYOUT>, p);
     else
-        normalize_copy_kernel<DTYPE, LAYOUT><<<grid, block, 0, st>>>(p);
+        cudaLaunchKernelEx(&cfg, normalize_copy_kernel<DTYPE, LAYOUT>, p);
     g_copy_launches.fetch_add(1, std::memory_order_relaxed);
     return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace
 
-int launch_normalize_copy(const FusedParams& p, int out_dtype, int out_layout, void* stream) {
+int launch_normalize_copy(const FusedParams& p, int out_dtype, int out_layout, void* stream, unsigned flags) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (out_dtype == 0) return out_layout == 0 ? launch_one<0, 0>(p, st) : launch_one<0, 1>(p, st);
-    return out_layout == 0 ? launch_one<1, 0>(p, st) : launch_one<1, 1>(p, st);
+    if (out_dtype == 0) return out_layout == 0 ? launch_one<0, 0>(p, st, flags) : launch_one<0, 1>(p, st, flags);
+    return out_layout == 0 ? launch_one<1, 0>(p, st, flags) : launch_one<1, 1>(p, st, flags);
 }
 
 unsigned long long normalize_copy_launch_count() { return g_copy_launches.load(std::memory_order_relaxed); }
