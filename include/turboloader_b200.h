@@ -114,8 +114,9 @@ typedef struct tlb_transform_desc {
 } tlb_transform_desc;
 
 /* TLB_FLAG_LAUNCH_OVERLAP: launch with programmatic stream serialization.  When the work directly
- * before this call in its stream is another fused-transform launch, this one may start while that
- * one drains its last CTAs, so consecutive batches leave no SM idle between them.  The kernel does
+ * before this call in its stream is another launch of this library's transform kernels (bilinear,
+ * antialiased, identity-size, video), this one may start while that one drains its last CTAs, so
+ * consecutive batches leave no SM idle between them.  The kernel does
  * not wait for its predecessor; by setting the flag the caller states that a KERNEL placed directly
  * before this call in the same stream neither writes this call's inputs (pixels, tables) nor reads
  * or writes its outputs.  Copies, memsets and event waits always keep full stream order.  A stream
