@@ -266,8 +266,14 @@ int launch_desc(const tlb_transform_desc& d, int max_crop_w, void* stream, bool 
         static const bool one_col = std::getenv("TLB_AA_ONE_COLUMN") != nullptr;
         a.pair = one_col ? 0 : 1;
         if (!a.pair && d.jitter) return fail(TLB_ERR_INVALID_ARG, "colour jitter needs the packed antialias kernel (TLB_AA_ONE_COLUMN is set)");
-        static const int aa_rows = env_int("TLB_AA_TILE_ROWS", 32);
-        a.tile_rows = std::min(std::max(aa_rows, 1), d.dst_h);
+        // Row tiles of equal height: at most 32 rows for a launch on its own (more CTAs, shorter tail),
+        // at most 64 for one of a stream of overlapping launches (the next launch covers the tail, and
+        // the per-tile tables are built half as often).
+        static const int aa_rows = env_int("TLB_AA_TILE_ROWS", 0);
+        const bool overlapping = streaming || (honour_flags && (d.flags & TLB_FLAG_LAUNCH_OVERLAP));
+        const int max_rows = std::min(std::max(aa_rows > 0 ? aa_rows : (overlapping ? 64 : 32), 1), d.dst_h);
+        a.n_row_tiles = (d.dst_h + max_rows - 1) / max_rows;
+        a.tile_rows = (d.dst_h + a.n_row_tiles - 1) / a.n_row_tiles;
         a.n_row_tiles = (d.dst_h + a.tile_rows - 1) / a.tile_rows;
         a.tile_cols = std::min(256, round_up(d.dst_w, 32));
         for (;;) {
