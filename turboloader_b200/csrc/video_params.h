@@ -31,6 +31,7 @@ struct VideoParams {
     void* out;                           // (n, 3, dst_h, dst_w)
     unsigned* status;                    // optional device word, OR-ed with 8 if a staging copy never completed
     int stage_rows;                      // set by launch_video: output rows per CTA of the staged kernel
+    int direct_rows;                     // set by launch_video: output rows per CTA of the direct kernel (even, <= 32)
     int use_staged;                      // non-zero: use the shared-memory staged kernel when the frame fits
     int inline_tables;                   // non-zero: planes / crops / flips are read from `in` (direct kernel only)
     int has_crops, has_flips;            // with inline tables: which of them are given
