@@ -703,7 +703,7 @@ def loader_epoch_leg(args, torch, device, peak, n_images):
                                          drop_last=True)
     stream = torch.cuda.current_stream()
     times = []
-    for ep in range(4):
+    for ep in range(8):  # the first epoch warms up; median of the other seven
         ld.set_epoch(ep)
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
